@@ -1,0 +1,143 @@
+/* C ABI of libxattn_b200: Blackwell (sm_100a) attention kernels behind the
+ * operator table of ifm-ai/xattn.
+ *
+ * The reference reaches its native code through a pybind module whose ops take
+ * and return torch tensors (csrc/xattn_extension.cc:9-20, csrc/bindings.h:11-15).
+ * This header is the replacement boundary: plain pointers, sizes, element
+ * strides and a CUDA stream; no torch types.  Every pointer is a DEVICE pointer
+ * unless the comment says otherwise.  The callee never allocates: outputs and
+ * workspaces are provided by the caller (the reference allocates outputs inside
+ * the op, csrc/causal_attention/launch.cu:1099-1105; here the Python shim does).
+ *
+ * Every entry point returns 0 on success and a negative XATTN_E_* code on
+ * failure; xattn_b200_last_error() gives the message for the calling thread.
+ * Kernels never trap: a device-side wait that runs out of time stores a code
+ * in the caller's `status` word (checked with xattn_b200_check_status()).
+ */
+#ifndef XATTN_B200_H_
+#define XATTN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define XATTN_B200_ABI_VERSION 1
+
+enum {
+  XATTN_OK = 0,
+  XATTN_E_INVALID = -1,      /* bad argument (shape, alignment, dtype)      */
+  XATTN_E_UNSUPPORTED = -2,  /* valid request this build cannot run         */
+  XATTN_E_CUDA = -3,         /* a CUDA runtime / driver call failed         */
+  XATTN_E_DEVICE = -4        /* a kernel reported a device-side status code */
+};
+
+enum { XATTN_DTYPE_F16 = 0, XATTN_DTYPE_BF16 = 1 };
+
+/* Visibility of keys to the left of a query (tests/_reference.py:50-59,
+ * csrc/attention/hopper/semantics/visibility.h:17-180). */
+enum { XATTN_VIS_FULL = 0, XATTN_VIS_WINDOW = 1, XATTN_VIS_CHUNK = 2 };
+
+typedef void* xattn_stream_t; /* cudaStream_t */
+
+int xattn_b200_abi_version(void);
+const char* xattn_b200_last_error(void);
+
+/* ------------------------------------------------------------------------
+ * Mask plan.  Every variant of the reference (causal / window / chunk,
+ * segment ids, BOS runs, per-segment reset positions, strict past, short
+ * right-aligned Q, packed varlen) makes the keys visible to one query row a
+ * single interval [lo, hi) of key indices.  The plan stores that interval per
+ * (batch, query row) plus per-tile summaries the kernels use to pick and skip
+ * key tiles.  It replaces csrc/attention/hopper/mask.h:197-442,563-713,
+ * hopper/block.h:17-179, csrc/attention/partition/segment_index.h:113-391 and
+ * the pre-pass kernels of hopper/fwd_template.cuh:186-202 and
+ * hopper/bwd_template.cuh:115-239.
+ *
+ * Layout of the plan buffer (int32 words), with nQT = ceil(Lq/128),
+ * nKT = ceil(Lk/128):
+ *   row_lo   [B][Lq]
+ *   row_hi   [B][Lq]
+ *   q_tiles  [B][nQT][4]   (min lo, max hi, max lo, min hi)
+ *   k_tiles  [B][nKT][2]   (first query tile, last query tile + 1)
+ * ---------------------------------------------------------------------- */
+size_t xattn_b200_plan_bytes(int64_t batch, int64_t q_len, int64_t k_len);
+
+typedef struct {
+  int64_t batch, q_len, k_len;   /* k_len counts previous K/V too              */
+  int visibility;                /* XATTN_VIS_*                                */
+  int64_t span;                  /* window radius / chunk size                 */
+  int strict_past;               /* 1: key position < query position           */
+  int reset_positions;           /* 1: positions restart per segment run       */
+  const int64_t* q_segment;      /* [B][q_len] or NULL (ids nondecreasing in k)*/
+  const int64_t* k_segment;      /* [B][k_len] or NULL                         */
+  int64_t q_segment_stride;      /* elements between batch rows                */
+  int64_t k_segment_stride;
+  int32_t* plan;                 /* xattn_b200_plan_bytes() bytes              */
+} XattnPlanArgs;
+
+/* Builds the plan for dense [B, L, H, D] inputs.
+ * Replaces AttentionSegmentFwdSpanKernel (hopper/fwd_template.cuh:186-202),
+ * the worklist / interval kernels (hopper/bwd_template.cuh:115-239) and
+ * FlashSCABuildDenseResetChunkPositionsKernel
+ * (csrc/flash_sca/hopper/sliding_chunk_attention.cu:1942-1965). */
+int xattn_b200_build_plan(const XattnPlanArgs* args, xattn_stream_t stream);
+
+typedef struct {
+  int64_t total_q, total_k;      /* packed token counts                        */
+  int64_t num_q_seqs, num_k_seqs;/* cu_seqlens lengths minus one               */
+  const int32_t* cu_seqlens_q;   /* [num_q_seqs + 1]                           */
+  const int32_t* cu_seqlens_k;   /* [num_k_seqs + 1]                           */
+  int visibility;
+  int64_t span;
+  int strict_past;
+  int32_t* plan;                 /* plan_bytes(1, total_q, total_k)            */
+} XattnVarlenPlanArgs;
+
+/* Builds the plan for packed [T, H, D] inputs: sequence r of Q is paired with
+ * sequence r + (num_k_seqs - num_q_seqs) of K, right-aligned, positions restart
+ * per sequence (csrc/attention/sequence/varlen_metadata.h:17-69,
+ * csrc/causal_attention/launch.cu:1455-1695). */
+int xattn_b200_build_varlen_plan(const XattnVarlenPlanArgs* args, xattn_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Forward.  Replaces causal_flash_attn_fwd / flash_swa_fwd / flash_sca_fwd and
+ * their strict-past, component and varlen forms
+ * (csrc/causal_flash_attn/causal_flash_attn.cc:49-122, csrc/flash_swa/flash_swa.cc:106-178,
+ * csrc/flash_sca/sliding_chunk_attention.cc:531-902) — one kernel, the variant
+ * is in the plan.  Launch contract follows AttentionFwdParams
+ * (csrc/attention/hopper/fwd_params.h:10-87).
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  int dtype;                     /* XATTN_DTYPE_*                              */
+  int64_t batch, q_len, k_len;
+  int64_t q_heads, kv_heads;
+  int64_t qk_dim, v_dim;         /* multiples of 8, <= 256                     */
+  const void* q;                 /* [B][q_len][Hq][D]  element strides below   */
+  const void* k;                 /* [B][k_len][Hkv][D]                         */
+  const void* v;                 /* [B][k_len][Hkv][V]                         */
+  int64_t q_strides[3];          /* batch, row, head (last dim contiguous)     */
+  int64_t k_strides[3];
+  int64_t v_strides[3];
+  float scale;                   /* > 0                                        */
+  int high_precision;            /* 1: subtract-before-scale softmax, exact
+                                    reciprocal (hopper/fwd_template.cuh:228-239,
+                                    cuda/softmax.h:103-111)                    */
+  const int32_t* plan;
+  void* y;                       /* [B][q_len][Hq][V] contiguous, input dtype  */
+  float* lse;                    /* [B][Hq][q_len]                             */
+  float* y_state;                /* optional FP32 copy of y, same shape, or NULL */
+  int32_t* status;               /* one word, zero on entry                    */
+} XattnFwdArgs;
+
+int xattn_b200_fwd(const XattnFwdArgs* args, xattn_stream_t stream);
+
+/* Reads `status` back (synchronises the stream).  0 when the word is zero. */
+int xattn_b200_check_status(const int32_t* status, xattn_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XATTN_B200_H_ */

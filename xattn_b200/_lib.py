@@ -1,0 +1,102 @@
+"""ctypes binding of libxattn_b200.so (the C ABI in include/xattn_b200.h).
+
+There is no CPU or eager fallback: if the library is missing or cannot be
+loaded, every native call raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+from typing import Optional
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libxattn_b200.so")
+
+XATTN_DTYPE_F16, XATTN_DTYPE_BF16 = 0, 1
+VIS_FULL, VIS_WINDOW, VIS_CHUNK = 0, 1, 2
+
+
+class PlanArgs(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int64), ("q_len", C.c_int64), ("k_len", C.c_int64),
+        ("visibility", C.c_int), ("span", C.c_int64),
+        ("strict_past", C.c_int), ("reset_positions", C.c_int),
+        ("q_segment", C.c_void_p), ("k_segment", C.c_void_p),
+        ("q_segment_stride", C.c_int64), ("k_segment_stride", C.c_int64),
+        ("plan", C.c_void_p),
+    ]
+
+
+class VarlenPlanArgs(C.Structure):
+    _fields_ = [
+        ("total_q", C.c_int64), ("total_k", C.c_int64),
+        ("num_q_seqs", C.c_int64), ("num_k_seqs", C.c_int64),
+        ("cu_seqlens_q", C.c_void_p), ("cu_seqlens_k", C.c_void_p),
+        ("visibility", C.c_int), ("span", C.c_int64), ("strict_past", C.c_int),
+        ("plan", C.c_void_p),
+    ]
+
+
+class FwdArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int),
+        ("batch", C.c_int64), ("q_len", C.c_int64), ("k_len", C.c_int64),
+        ("q_heads", C.c_int64), ("kv_heads", C.c_int64),
+        ("qk_dim", C.c_int64), ("v_dim", C.c_int64),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+        ("q_strides", C.c_int64 * 3), ("k_strides", C.c_int64 * 3), ("v_strides", C.c_int64 * 3),
+        ("scale", C.c_float), ("high_precision", C.c_int),
+        ("plan", C.c_void_p),
+        ("y", C.c_void_p), ("lse", C.c_void_p), ("y_state", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
+_lock = threading.Lock()
+_lib: Optional[C.CDLL] = None
+
+# name -> (restype, argtypes); every symbol include/xattn_b200.h declares
+SYMBOLS = {
+    "xattn_b200_abi_version": (C.c_int, []),
+    "xattn_b200_last_error": (C.c_char_p, []),
+    "xattn_b200_plan_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
+    "xattn_b200_build_plan": (C.c_int, [C.POINTER(PlanArgs), C.c_void_p]),
+    "xattn_b200_build_varlen_plan": (C.c_int, [C.POINTER(VarlenPlanArgs), C.c_void_p]),
+    "xattn_b200_fwd": (C.c_int, [C.POINTER(FwdArgs), C.c_void_p]),
+    "xattn_b200_check_status": (C.c_int, [C.c_void_p, C.c_void_p]),
+}
+
+
+def load() -> C.CDLL:
+    """Load the shared library once; raise ImportError with build instructions when absent."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing. Build it with `python -m xattn_b200.build` "
+                "(needs nvcc; sm_100a only). There is no CPU fallback."
+            )
+        lib = C.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SYMBOLS.items():
+            fn = getattr(lib, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        if lib.xattn_b200_abi_version() != 1:
+            raise ImportError("libxattn_b200.so has an unexpected ABI version; rebuild it")
+        _lib = lib
+        return lib
+
+
+def last_error() -> str:
+    msg = load().xattn_b200_last_error()
+    return msg.decode() if msg else ""
+
+
+def check(code: int, what: str) -> None:
+    """Turn a negative return code into the exception the reference's TORCH_CHECK would raise."""
+    if code == 0:
+        return
+    raise RuntimeError(f"{what}: {last_error()} (code {code})")

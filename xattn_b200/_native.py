@@ -1,0 +1,224 @@
+"""torch-facing wrappers of the C ABI: allocate outputs and workspaces, pass raw
+pointers, turn status codes into exceptions.
+
+This is the part of the reference's pybind layer that stays in Python
+(csrc/causal_flash_attn/causal_flash_attn.cc:49-122 and friends allocate the
+outputs and forward the tensors; here the library only ever sees pointers).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import _lib
+
+_DTYPES = {torch.float16: _lib.XATTN_DTYPE_F16, torch.bfloat16: _lib.XATTN_DTYPE_BF16}
+_VIS = {"full": _lib.VIS_FULL, "window": _lib.VIS_WINDOW, "chunk": _lib.VIS_CHUNK}
+
+# XATTN_B200_SYNC_CHECK=1: read the device status word after every launch
+# (synchronises).  Otherwise the word is read back asynchronously and examined
+# at the next call on the same device.
+_SYNC_CHECK = os.environ.get("XATTN_B200_SYNC_CHECK", "0") == "1"
+
+
+class _DeviceState:
+    def __init__(self, device: torch.device):
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event: Optional[torch.cuda.Event] = None
+
+
+_states = {}
+
+
+def _state(device: torch.device) -> _DeviceState:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    st = _states.get(index)
+    if st is None:
+        st = _states[index] = _DeviceState(torch.device("cuda", index))
+    return st
+
+
+def _stream_ptr() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _raise_status(value: int) -> None:
+    raise RuntimeError(
+        f"xattn_b200 kernel reported device status {value & 0xff} at wait site {value >> 8}; "
+        "results of that launch are invalid"
+    )
+
+
+def _pre_launch(device: torch.device) -> _DeviceState:
+    st = _state(device)
+    if st.event is not None and st.event.query():
+        st.event = None
+        value = int(st.host[0])
+        if value:
+            st.status.zero_()
+            _raise_status(value)
+    return st
+
+
+def _post_launch(st: _DeviceState) -> None:
+    if _SYNC_CHECK:
+        torch.cuda.current_stream().synchronize()
+        value = int(st.status.item())
+        if value:
+            st.status.zero_()
+            _raise_status(value)
+        return
+    if st.event is None:
+        st.host.copy_(st.status, non_blocking=True)
+        st.event = torch.cuda.Event()
+        st.event.record()
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Synchronise and raise if any kernel launched so far reported a device-side status."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    st = _state(device)
+    torch.cuda.synchronize(device)
+    st.event = None
+    value = int(st.status.item())
+    if value:
+        st.status.zero_()
+        _raise_status(value)
+
+
+def require_cuda(t: Tensor, api_name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{api_name} needs CUDA tensors; this build has no CPU path")
+    major, _ = torch.cuda.get_device_capability(t.device)
+    if major != 10:
+        raise RuntimeError(f"{api_name} is built for sm_100a only (device capability {major}.x found)")
+
+
+def tma_ready(t: Tensor) -> Tensor:
+    """Return ``t`` itself when TMA can read it in place (unit last stride, 16-byte aligned base and
+    strides — the rule of csrc/causal_attention/launch.cu:85-95), otherwise a contiguous copy."""
+    if t.dim() >= 1 and t.stride(-1) == 1 and t.data_ptr() % 16 == 0:
+        ok = True
+        for size, stride in zip(t.shape[:-1], t.stride()[:-1]):
+            if size > 1 and (stride <= 0 or (stride * t.element_size()) % 16):
+                ok = False
+                break
+        if ok:
+            return t
+    out = t.contiguous()
+    if out.data_ptr() % 16:
+        out = out.clone(memory_format=torch.contiguous_format)
+    return out
+
+
+def plan_bytes(batch: int, q_len: int, k_len: int) -> int:
+    return int(_lib.load().xattn_b200_plan_bytes(batch, q_len, k_len))
+
+
+def build_plan(
+    batch: int,
+    q_len: int,
+    k_len: int,
+    device: torch.device,
+    *,
+    visibility: str = "full",
+    span: Optional[int] = None,
+    strict_past: bool = False,
+    reset_positions: bool = False,
+    q_segment_idx: Optional[Tensor] = None,
+    k_segment_idx: Optional[Tensor] = None,
+) -> Tensor:
+    """Device plan (int32 tensor) for dense [B, L, H, D] inputs."""
+    lib = _lib.load()
+    plan = torch.empty(plan_bytes(batch, q_len, k_len) // 4, dtype=torch.int32, device=device)
+    args = _lib.PlanArgs()
+    args.batch, args.q_len, args.k_len = batch, q_len, k_len
+    args.visibility = _VIS[visibility]
+    args.span = 0 if span is None else int(span)
+    args.strict_past = int(bool(strict_past))
+    args.reset_positions = int(bool(reset_positions))
+    keep = []
+    if q_segment_idx is not None:
+        qs = q_segment_idx if q_segment_idx.stride(-1) == 1 else q_segment_idx.contiguous()
+        ks = k_segment_idx if k_segment_idx.stride(-1) == 1 else k_segment_idx.contiguous()
+        keep += [qs, ks]
+        args.q_segment, args.k_segment = qs.data_ptr(), ks.data_ptr()
+        args.q_segment_stride = qs.stride(0) if batch > 1 else q_len
+        args.k_segment_stride = ks.stride(0) if batch > 1 else k_len
+    args.plan = plan.data_ptr()
+    with torch.cuda.device(device):
+        _lib.check(lib.xattn_b200_build_plan(C.byref(args), _stream_ptr()), "xattn_b200_build_plan")
+    return plan
+
+
+def build_varlen_plan(
+    cu_seqlens_q: Tensor,
+    cu_seqlens_k: Tensor,
+    total_q: int,
+    total_k: int,
+    *,
+    visibility: str = "full",
+    span: Optional[int] = None,
+    strict_past: bool = False,
+) -> Tensor:
+    lib = _lib.load()
+    device = cu_seqlens_q.device
+    plan = torch.empty(plan_bytes(1, total_q, total_k) // 4, dtype=torch.int32, device=device)
+    args = _lib.VarlenPlanArgs()
+    args.total_q, args.total_k = total_q, total_k
+    args.num_q_seqs, args.num_k_seqs = cu_seqlens_q.numel() - 1, cu_seqlens_k.numel() - 1
+    cq, ck = cu_seqlens_q.contiguous(), cu_seqlens_k.contiguous()
+    args.cu_seqlens_q, args.cu_seqlens_k = cq.data_ptr(), ck.data_ptr()
+    args.visibility = _VIS[visibility]
+    args.span = 0 if span is None else int(span)
+    args.strict_past = int(bool(strict_past))
+    args.plan = plan.data_ptr()
+    with torch.cuda.device(device):
+        _lib.check(lib.xattn_b200_build_varlen_plan(C.byref(args), _stream_ptr()), "xattn_b200_build_varlen_plan")
+    return plan
+
+
+def attention_fwd(
+    q: Tensor,
+    k: Tensor,
+    v: Tensor,
+    plan: Tensor,
+    scale: float,
+    *,
+    high_precision: bool = False,
+    output_state: Optional[Tensor] = None,
+) -> Tuple[Tensor, Tensor]:
+    """y [B,Lq,Hq,V] (input dtype), lse [B,Hq,Lq] fp32.  ``k``/``v`` already include previous K/V."""
+    lib = _lib.load()
+    require_cuda(q, "xattn_b200 forward")
+    q, k, v = tma_ready(q), tma_ready(k), tma_ready(v)
+    B, Lq, Hq, D = q.shape
+    Lk, Hkv, V = k.shape[1], k.shape[2], v.shape[3]
+    y = torch.empty((B, Lq, Hq, V), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, Hq, Lq), dtype=torch.float32, device=q.device)
+    args = _lib.FwdArgs()
+    args.dtype = _DTYPES[q.dtype]
+    args.batch, args.q_len, args.k_len = B, Lq, Lk
+    args.q_heads, args.kv_heads, args.qk_dim, args.v_dim = Hq, Hkv, D, V
+    args.q, args.k, args.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v)):
+        setattr(args, name, (C.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2)))
+    args.scale = float(scale)
+    args.high_precision = int(bool(high_precision))
+    args.plan = plan.data_ptr()
+    args.y, args.lse = y.data_ptr(), lse.data_ptr()
+    if output_state is not None:
+        if output_state.shape != y.shape or output_state.dtype != torch.float32 or not output_state.is_contiguous():
+            raise ValueError("output_state must be a contiguous FP32 tensor shaped like y")
+        args.y_state = output_state.data_ptr()
+    with torch.cuda.device(q.device):
+        st = _pre_launch(q.device)
+        args.status = st.status.data_ptr()
+        _lib.check(lib.xattn_b200_fwd(C.byref(args), _stream_ptr()), "xattn_b200_fwd")
+        _post_launch(st)
+    return y, lse

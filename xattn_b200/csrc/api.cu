@@ -1,0 +1,46 @@
+// extern "C" surface of libxattn_b200 (declared in include/xattn_b200.h).
+#include "common.cuh"
+
+namespace xb {
+const char* last_error();
+int fwd_entry(const XattnFwdArgs* a, cudaStream_t stream);
+int build_plan_entry(const XattnPlanArgs* a, cudaStream_t stream);
+int build_varlen_plan_entry(const XattnVarlenPlanArgs* a, cudaStream_t stream);
+}  // namespace xb
+
+extern "C" {
+
+int xattn_b200_abi_version(void) { return XATTN_B200_ABI_VERSION; }
+
+const char* xattn_b200_last_error(void) { return xb::last_error(); }
+
+size_t xattn_b200_plan_bytes(int64_t batch, int64_t q_len, int64_t k_len) {
+  if (batch <= 0 || q_len <= 0 || k_len <= 0) return 0;
+  return (size_t)xb::PlanLayout(batch, q_len, k_len).words * sizeof(int32_t);
+}
+
+int xattn_b200_build_plan(const XattnPlanArgs* args, xattn_stream_t stream) {
+  return xb::build_plan_entry(args, static_cast<cudaStream_t>(stream));
+}
+
+int xattn_b200_build_varlen_plan(const XattnVarlenPlanArgs* args, xattn_stream_t stream) {
+  return xb::build_varlen_plan_entry(args, static_cast<cudaStream_t>(stream));
+}
+
+int xattn_b200_fwd(const XattnFwdArgs* args, xattn_stream_t stream) {
+  return xb::fwd_entry(args, static_cast<cudaStream_t>(stream));
+}
+
+int xattn_b200_check_status(const int32_t* status, xattn_stream_t stream) {
+  int32_t host = 0;
+  cudaError_t e = cudaMemcpyAsync(&host, status, sizeof(host), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) { xb::set_error("status read: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
+  if (host != 0) {
+    xb::set_error("kernel reported status %d (wait site %d)", host & 0xff, host >> 8);
+    return XATTN_E_DEVICE;
+  }
+  return XATTN_OK;
+}
+
+}  // extern "C"
