@@ -134,6 +134,45 @@ typedef struct {
 
 int xattn_b200_fwd(const XattnFwdArgs* args, xattn_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Backward.  Replaces causal_flash_attn_bwd / flash_swa_bwd / flash_sca_bwd and
+ * their strict-past, component and varlen forms (same files as the forward
+ * ops) and the kernels behind them: preprocess
+ * (csrc/attention/hopper/bwd_preprocess_kernel.h:23), main loop
+ * (hopper/mainloop_bwd_sm90_tma_gmma_ws.hpp:1725-2149), dQ post-process and
+ * grouped dK/dV cast (hopper/bwd_postprocess_kernel.h, hopper/bwd_template.cuh:241-308).
+ * Launch contract follows AttentionBwdParams (hopper/bwd_params.h:14-120).
+ * Gradients are bitwise repeatable (no atomics), so the reference's
+ * `deterministic` switch has nothing to select.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  int dtype;
+  int64_t batch, q_len, k_len;
+  int64_t q_heads, kv_heads;
+  int64_t qk_dim, v_dim;         /* multiples of 8, <= 128 for now             */
+  const void* q;                 /* as in the forward                          */
+  const void* k;
+  const void* v;
+  const void* y;                 /* forward output [B][q_len][Hq][V]           */
+  const void* dy;                /* gradient of y, same shape                  */
+  int64_t q_strides[3];
+  int64_t k_strides[3];
+  int64_t v_strides[3];
+  int64_t y_strides[3];
+  int64_t dy_strides[3];
+  const float* lse;              /* [B][Hq][q_len] from the forward            */
+  float scale;
+  const int32_t* plan;
+  void* dq;                      /* [B][q_len][Hq][D] contiguous               */
+  void* dk;                      /* [B][k_len][Hkv][D] contiguous              */
+  void* dv;                      /* [B][k_len][Hkv][V] contiguous              */
+  float* workspace;              /* xattn_b200_bwd_workspace_bytes() bytes     */
+  int32_t* status;
+} XattnBwdArgs;
+
+size_t xattn_b200_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);
+int xattn_b200_bwd(const XattnBwdArgs* args, xattn_stream_t stream);
+
 /* Reads `status` back (synchronises the stream).  0 when the word is zero. */
 int xattn_b200_check_status(const int32_t* status, xattn_stream_t stream);
 

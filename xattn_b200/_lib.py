@@ -53,6 +53,22 @@ class FwdArgs(C.Structure):
     ]
 
 
+class BwdArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int),
+        ("batch", C.c_int64), ("q_len", C.c_int64), ("k_len", C.c_int64),
+        ("q_heads", C.c_int64), ("kv_heads", C.c_int64),
+        ("qk_dim", C.c_int64), ("v_dim", C.c_int64),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("y", C.c_void_p), ("dy", C.c_void_p),
+        ("q_strides", C.c_int64 * 3), ("k_strides", C.c_int64 * 3), ("v_strides", C.c_int64 * 3),
+        ("y_strides", C.c_int64 * 3), ("dy_strides", C.c_int64 * 3),
+        ("lse", C.c_void_p), ("scale", C.c_float),
+        ("plan", C.c_void_p),
+        ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+        ("workspace", C.c_void_p), ("status", C.c_void_p),
+    ]
+
+
 _lock = threading.Lock()
 _lib: Optional[C.CDLL] = None
 
@@ -64,6 +80,8 @@ SYMBOLS = {
     "xattn_b200_build_plan": (C.c_int, [C.POINTER(PlanArgs), C.c_void_p]),
     "xattn_b200_build_varlen_plan": (C.c_int, [C.POINTER(VarlenPlanArgs), C.c_void_p]),
     "xattn_b200_fwd": (C.c_int, [C.POINTER(FwdArgs), C.c_void_p]),
+    "xattn_b200_bwd_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
+    "xattn_b200_bwd": (C.c_int, [C.POINTER(BwdArgs), C.c_void_p]),
     "xattn_b200_check_status": (C.c_int, [C.c_void_p, C.c_void_p]),
 }
 

@@ -222,3 +222,44 @@ def attention_fwd(
         _lib.check(lib.xattn_b200_fwd(C.byref(args), _stream_ptr()), "xattn_b200_fwd")
         _post_launch(st)
     return y, lse
+
+
+def attention_bwd(
+    dy: Tensor,
+    q: Tensor,
+    k: Tensor,
+    v: Tensor,
+    y: Tensor,
+    lse: Tensor,
+    plan: Tensor,
+    scale: float,
+) -> Tuple[Tensor, Tensor, Tensor]:
+    """(dq, dk, dv) shaped like q, k, v (k / v including previous K/V), in the input dtype."""
+    lib = _lib.load()
+    require_cuda(q, "xattn_b200 backward")
+    q, k, v, y, dy = tma_ready(q), tma_ready(k), tma_ready(v), tma_ready(y), tma_ready(dy)
+    lse = lse.contiguous()
+    B, Lq, Hq, D = q.shape
+    Lk, Hkv, V = k.shape[1], k.shape[2], v.shape[3]
+    dq = torch.empty((B, Lq, Hq, D), dtype=q.dtype, device=q.device)
+    dk = torch.empty((B, Lk, Hkv, D), dtype=q.dtype, device=q.device)
+    dv = torch.empty((B, Lk, Hkv, V), dtype=q.dtype, device=q.device)
+    ws = torch.empty(int(lib.xattn_b200_bwd_workspace_bytes(B, Hq, Lq)) // 4, dtype=torch.float32, device=q.device)
+    args = _lib.BwdArgs()
+    args.dtype = _DTYPES[q.dtype]
+    args.batch, args.q_len, args.k_len = B, Lq, Lk
+    args.q_heads, args.kv_heads, args.qk_dim, args.v_dim = Hq, Hkv, D, V
+    args.q, args.k, args.v, args.y, args.dy = q.data_ptr(), k.data_ptr(), v.data_ptr(), y.data_ptr(), dy.data_ptr()
+    for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("y_strides", y), ("dy_strides", dy)):
+        setattr(args, name, (C.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2)))
+    args.lse = lse.data_ptr()
+    args.scale = float(scale)
+    args.plan = plan.data_ptr()
+    args.dq, args.dk, args.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    args.workspace = ws.data_ptr()
+    with torch.cuda.device(q.device):
+        st = _pre_launch(q.device)
+        args.status = st.status.data_ptr()
+        _lib.check(lib.xattn_b200_bwd(C.byref(args), _stream_ptr()), "xattn_b200_bwd")
+        _post_launch(st)
+    return dq, dk, dv

@@ -4,6 +4,7 @@
 namespace xb {
 const char* last_error();
 int fwd_entry(const XattnFwdArgs* a, cudaStream_t stream);
+int bwd_entry(const XattnBwdArgs* a, cudaStream_t stream);
 int build_plan_entry(const XattnPlanArgs* a, cudaStream_t stream);
 int build_varlen_plan_entry(const XattnVarlenPlanArgs* a, cudaStream_t stream);
 }  // namespace xb
@@ -29,6 +30,15 @@ int xattn_b200_build_varlen_plan(const XattnVarlenPlanArgs* args, xattn_stream_t
 
 int xattn_b200_fwd(const XattnFwdArgs* args, xattn_stream_t stream) {
   return xb::fwd_entry(args, static_cast<cudaStream_t>(stream));
+}
+
+size_t xattn_b200_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len) {
+  if (batch <= 0 || q_heads <= 0 || q_len <= 0) return 0;
+  return (size_t)batch * q_heads * q_len * 2 * sizeof(float);
+}
+
+int xattn_b200_bwd(const XattnBwdArgs* args, xattn_stream_t stream) {
+  return xb::bwd_entry(args, static_cast<cudaStream_t>(stream));
 }
 
 int xattn_b200_check_status(const int32_t* status, xattn_stream_t stream) {

@@ -1,0 +1,745 @@
+// Backward attention for sm_100a: three kernels, all reductions in a fixed
+// order (bitwise repeatable; nothing is accumulated with atomics).
+//
+//   bwd_pre_kernel   delta = rowsum(dy * y), lse2 = lse * log2(e)      (HBM-bound)
+//   bwd_dq_kernel    query-stationary:  S = Q K^T, dP = dO V^T,
+//                    dS = P * (dP - delta),  dQ += dS K                 (tensor-bound)
+//   bwd_dkv_kernel   key-stationary, transposed:  S^T = K Q^T, dP^T = V dO^T,
+//                    dV += P^T dO,  dK += dS^T Q, looping over the query heads
+//                    of the KV head so dK / dV are written once         (tensor-bound)
+//
+// Arithmetic restated from the reference backward: P = exp2(S*c - lse*log2e)
+// from the saved lse, dS = P * (dP - rowsum(dO*O)), P and dS rounded to the
+// input dtype before the dV / dK / dQ products, dK and dQ scaled by the softmax
+// scale at the end (csrc/attention/hopper/mainloop_bwd_sm90_tma_gmma_ws.hpp:1725-2149,
+// :1877-1900, :2247,2302; hopper/bwd_preprocess_kernel.h:165-297;
+// hopper/bwd_postprocess_kernel.h:273-288).  Where the reference reduces dQ
+// across key tiles with global atomics or semaphores (hopper/mainloop_bwd...:2067-2103,
+// :1261-1324), dQ here has its own query-stationary kernel.
+#include "common.cuh"
+
+namespace xb {
+
+struct BwdParams {
+  int B, Lq, Lk, Hq, Hkv, D, V;
+  int nQT, nKT;
+  float scale;
+  const int* row_lo;
+  const int* row_hi;
+  const TileInfo* q_tiles;
+  const KeyTileInfo* k_tiles;
+  const void* q;              // for direct loads in the dQ kernel
+  int64_t q_sb, q_sl, q_sh;   // element strides of q
+  const float* lse2;          // [B][Hq][Lq]  lse * log2e, +inf for rows without keys
+  const float* delta;         // [B][Hq][Lq]
+  void* dq;                   // [B][Lq][Hq][D]
+  void* dk;                   // [B][Lk][Hkv][D]
+  void* dv;                   // [B][Lk][Hkv][V]
+  int* status;
+};
+
+// ---------------------------------------------------------------------------
+// preprocess: one warp per (batch, row, head)
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, const T* __restrict__ y,
+                                                      const float* __restrict__ lse, int B, int Lq, int Hq, int V,
+                                                      int64_t dy_sb, int64_t dy_sl, int64_t dy_sh, int64_t y_sb,
+                                                      int64_t y_sl, int64_t y_sh, float* __restrict__ delta,
+                                                      float* __restrict__ lse2) {
+  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= (long long)B * Lq * Hq) return;
+  const int h = (int)(w % Hq);
+  const long long bi = w / Hq;
+  const int i = (int)(bi % Lq);
+  const int b = (int)(bi / Lq);
+  const T* dyr = dy + b * dy_sb + i * dy_sl + h * dy_sh;
+  const T* yr = y + b * y_sb + i * y_sl + h * y_sh;
+  float acc = 0.f;
+  for (int c = lane * 8; c < V; c += 256) {
+    const uint4 a = *reinterpret_cast<const uint4*>(dyr + c);
+    const uint4 o = *reinterpret_cast<const uint4*>(yr + c);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+    const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 fa = Pack2<T>::unpack(aw[k]);
+      const float2 fo = Pack2<T>::unpack(ow[k]);
+      acc = fmaf(fa.x, fo.x, acc);
+      acc = fmaf(fa.y, fo.y, acc);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) {
+    const size_t idx = ((size_t)b * Hq + h) * Lq + i;
+    delta[idx] = acc;
+    const float l = lse[idx];
+    lse2[idx] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// dQ kernel
+// ---------------------------------------------------------------------------
+template <int HD>
+struct DqSmem {
+  static constexpr int kTileBytes = kBlockM * HD * 2;
+  alignas(1024) uint8_t d_o[kTileBytes];
+  alignas(1024) uint8_t k[2][kTileBytes];
+  alignas(1024) uint8_t v[2][kTileBytes];
+  uint64_t do_full, q_ready;
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t sdp_full, sdp_free, ds_full, dq_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// warps 0-3 / 4-7: element-wise warpgroups (thread = query row; columns 0-63 / 64-127 of a key tile)
+// warp 8: MMA issuer, warp 9: TMA producer + TMEM owner, warps 10-11: idle
+template <typename T, int HD>
+__global__ void __launch_bounds__(384, 1)
+bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_k,
+              const __grid_constant__ CUtensorMap tm_v, const BwdParams p) {
+  using Smem = DqSmem<HD>;
+  constexpr int kBoxBytes = kBlockM * 64 * 2;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr int kFormat = Pack2<T>::kFormat;
+  // TMEM columns
+  constexpr uint32_t cQ = 0, cDS = 64, cS = 128, cDP = 256, cDQ = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  const int G = p.Hq / p.Hkv;
+  const int per_bk = p.nQT * G;
+  const int bk = blockIdx.x / per_bk;
+  const int rem = blockIdx.x - bk * per_bk;
+  const int qt = p.nQT - 1 - rem / G;
+  const int kvh = bk % p.Hkv;
+  const int h = kvh * G + (rem % G);
+  const int b = bk / p.Hkv;
+
+  int n_lo = 0, n_hi = 0, full_lo = 0x7fffffff, full_hi = 0;
+  {
+    const TileInfo ti = p.q_tiles[(size_t)b * p.nQT + qt];
+    if (ti.max_hi > ti.min_lo) {
+      n_lo = ti.min_lo / kBlockN;
+      n_hi = (ti.max_hi + kBlockN - 1) / kBlockN;
+      full_lo = ti.max_lo;
+      full_hi = ti.min_hi;
+    }
+  }
+  const int iters = n_hi - n_lo;
+
+  if (tid == 0) {
+    s.abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 2 : 0;
+    mbar_init(&s.do_full, 1);
+    mbar_init(&s.q_ready, 256);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.k_full[i], 1); mbar_init(&s.k_empty[i], 1);
+      mbar_init(&s.v_full[i], 1); mbar_init(&s.v_empty[i], 1);
+    }
+    mbar_init(&s.sdp_full, 1);
+    mbar_init(&s.sdp_free, 256);
+    mbar_init(&s.ds_full, 256);
+    mbar_init(&s.dq_done, 1);
+    fence_mbar_init();
+  }
+  if (warp == 9) { tmem_alloc(&s.tmem_base, kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s.tmem_base;
+  WaitCtx ctx{&s.abort_flag, p.status, 2000000000ull};
+  const bool dead = s.abort_flag != 0;
+
+  const int nbox_qk = (p.D + 63) / 64, nbox_v = (p.V + 63) / 64;
+  const int ksteps_qk = (p.D + 15) / 16, ksteps_v = (p.V + 15) / 16;
+  const int d_pad = (p.D + 15) & ~15;
+
+  if (dead) {
+  } else if (warp < 8) {
+    const int hf = warp >> 2;                 // which half of the key-tile columns
+    const int r = tid & 127;
+    const int row = qt * kBlockM + r;
+    const bool live = row < p.Lq;
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    T* dq_row = reinterpret_cast<T*>(p.dq) + (((size_t)b * p.Lq + (live ? row : 0)) * p.Hq + h) * p.D;
+    if (iters == 0) {
+      if (live) {
+        for (int c = hf * (HD / 2); c < (hf + 1) * (HD / 2) && c < p.D; c += 8)
+          *reinterpret_cast<uint4*>(dq_row + c) = make_uint4(0, 0, 0, 0);
+      }
+    } else {
+      // stage this thread's half of the Q row in TMEM (packed pairs, row = lane)
+      {
+        const T* q_row = reinterpret_cast<const T*>(p.q) + b * p.q_sb + (live ? row : 0) * p.q_sl + h * p.q_sh;
+        constexpr int kCols = HD / 4;           // packed columns per half
+        uint32_t qv[kCols];
+#pragma unroll
+        for (int c = 0; c < kCols; c += 4) {
+          const int e = (hf * kCols + c) * 2;   // first element of this 16-byte chunk
+          uint4 u = make_uint4(0, 0, 0, 0);
+          if (live && e < p.D) u = *reinterpret_cast<const uint4*>(q_row + e);
+          qv[c] = u.x; qv[c + 1] = u.y; qv[c + 2] = u.z; qv[c + 3] = u.w;
+        }
+        if (kCols == 32) tmem_st_x32(tmem + lane_off + cQ + hf * kCols, qv);
+        else tmem_st_x16(tmem + lane_off + cQ + hf * kCols, qv);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&s.q_ready);
+      }
+      int lo = 0, hi = 0;
+      float lse2 = INFINITY, delta = 0.f;
+      if (live) {
+        lo = p.row_lo[(size_t)b * p.Lq + row];
+        hi = p.row_hi[(size_t)b * p.Lq + row];
+        lse2 = p.lse2[((size_t)b * p.Hq + h) * p.Lq + row];
+        delta = p.delta[((size_t)b * p.Hq + h) * p.Lq + row];
+      }
+      const float c_log2 = p.scale * 1.4426950408889634f;
+      bool ok = true;
+      for (int i = 0; i < iters && ok; ++i) {
+        const int col0 = (n_lo + i) * kBlockN + hf * 64;
+        ok = mbar_wait(ctx, &s.sdp_full, i & 1, 50);
+        if (!ok) break;
+        tc_fence_after();
+        float sv[64], dpv[64];
+        tmem_ld_x32(tmem + lane_off + cS + hf * 64, reinterpret_cast<uint32_t*>(sv));
+        tmem_ld_x32(tmem + lane_off + cS + hf * 64 + 32, reinterpret_cast<uint32_t*>(sv) + 32);
+        tmem_ld_x32(tmem + lane_off + cDP + hf * 64, reinterpret_cast<uint32_t*>(dpv));
+        tmem_ld_x32(tmem + lane_off + cDP + hf * 64 + 32, reinterpret_cast<uint32_t*>(dpv) + 32);
+        tc_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&s.sdp_free);
+        const bool tile_full = ((n_lo + i) * kBlockN >= full_lo) && ((n_lo + i + 1) * kBlockN <= full_hi);
+        const int rl = lo - col0, rh = hi - col0;
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          float p0 = ex2_approx(fmaf(sv[c], c_log2, -lse2));
+          float p1 = ex2_approx(fmaf(sv[c + 1], c_log2, -lse2));
+          if (!tile_full) {
+            p0 = (c >= rl && c < rh) ? p0 : 0.f;
+            p1 = (c + 1 >= rl && c + 1 < rh) ? p1 : 0.f;
+          }
+          pk[c >> 1] = Pack2<T>::pack(p0 * (dpv[c] - delta), p1 * (dpv[c + 1] - delta));
+        }
+        if (i > 0) {
+          ok = mbar_wait(ctx, &s.dq_done, (i - 1) & 1, 51);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        tmem_st_x32(tmem + lane_off + cDS + hf * 32, pk);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&s.ds_full);
+      }
+      if (ok) ok = mbar_wait(ctx, &s.dq_done, (iters - 1) & 1, 52);
+      if (ok) {
+        tc_fence_after();
+        // this warpgroup writes columns [hf*HD/2, (hf+1)*HD/2) of dQ
+#pragma unroll
+        for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+          const int cbase = hf * (HD / 2) + c0;
+          uint32_t o[32];
+          tmem_ld_x32(tmem + lane_off + cDQ + cbase, o);
+          tc_wait_ld();
+          if (live) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 8) {
+              if (cbase + c < p.D) {
+                uint4 u;
+                u.x = Pack2<T>::pack(__uint_as_float(o[c + 0]) * p.scale, __uint_as_float(o[c + 1]) * p.scale);
+                u.y = Pack2<T>::pack(__uint_as_float(o[c + 2]) * p.scale, __uint_as_float(o[c + 3]) * p.scale);
+                u.z = Pack2<T>::pack(__uint_as_float(o[c + 4]) * p.scale, __uint_as_float(o[c + 5]) * p.scale);
+                u.w = Pack2<T>::pack(__uint_as_float(o[c + 6]) * p.scale, __uint_as_float(o[c + 7]) * p.scale);
+                *reinterpret_cast<uint4*>(dq_row + cbase + c) = u;
+              }
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 8 && lane == 0 && iters > 0) {
+    // ------------------------------ MMA issuer ------------------------------
+    const uint32_t idesc_s = make_idesc(kBlockM, kBlockN, kFormat, 0, 0);
+    const uint32_t idesc_dq = make_idesc(kBlockM, d_pad, kFormat, 0, 1);
+    auto issue_s_dp = [&](int stage) {
+      const uint32_t ka = smem_u32(s.k[stage]), va = smem_u32(s.v[stage]), da = smem_u32(s.d_o);
+      for (int js = 0; js < ksteps_qk; ++js) {
+        const uint32_t off = (js >> 2) * kBoxBytes + (js & 3) * 32;
+        umma_ts(tmem + cS, tmem + cQ + js * 8, make_smem_desc(ka + off, 16, 1024), idesc_s, js > 0);
+      }
+      for (int js = 0; js < ksteps_v; ++js) {
+        const uint32_t off = (js >> 2) * kBoxBytes + (js & 3) * 32;
+        umma_ss(tmem + cDP, make_smem_desc(da + off, 16, 1024), make_smem_desc(va + off, 16, 1024), idesc_s, js > 0);
+      }
+      umma_commit(&s.sdp_full);
+      umma_commit(&s.v_empty[stage]);
+    };
+    bool ok = mbar_wait(ctx, &s.do_full, 0, 60);
+    if (ok) ok = mbar_wait(ctx, &s.q_ready, 0, 61);
+    if (ok) ok = mbar_wait(ctx, &s.k_full[0], 0, 62);
+    if (ok) ok = mbar_wait(ctx, &s.v_full[0], 0, 63);
+    if (ok) { tc_fence_after(); issue_s_dp(0); }
+    for (int i = 0; i < iters && ok; ++i) {
+      const int st = i & 1;
+      if (i + 1 < iters) {
+        const int sn = (i + 1) & 1;
+        ok = mbar_wait(ctx, &s.k_full[sn], ((i + 1) >> 1) & 1, 64);
+        if (ok) ok = mbar_wait(ctx, &s.v_full[sn], ((i + 1) >> 1) & 1, 65);
+        if (ok) ok = mbar_wait(ctx, &s.sdp_free, i & 1, 66);
+        if (!ok) break;
+        tc_fence_after();
+        issue_s_dp(sn);
+      }
+      ok = mbar_wait(ctx, &s.ds_full, i & 1, 67);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t ka = smem_u32(s.k[st]);
+#pragma unroll
+      for (int js = 0; js < kBlockN / 16; ++js) {
+        umma_ts(tmem + cDQ, tmem + cDS + js * 8, make_smem_desc(ka + js * 2048, kBoxBytes, 1024), idesc_dq,
+                (i > 0 || js > 0) ? 1u : 0u);
+      }
+      umma_commit(&s.dq_done);
+      umma_commit(&s.k_empty[st]);
+    }
+  } else if (warp == 9 && lane == 0 && iters > 0) {
+    // ------------------------------ TMA producer ------------------------------
+    tma_prefetch_desc(&tm_do); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+    mbar_arrive_expect_tx(&s.do_full, nbox_v * kBoxBytes);
+    for (int bx = 0; bx < nbox_v; ++bx)
+      tma_load_4d(s.d_o + bx * kBoxBytes, &tm_do, &s.do_full, bx * 64, h, qt * kBlockM, b);
+    bool ok = true;
+    for (int i = 0; i < iters && ok; ++i) {
+      const int st = i & 1, n = n_lo + i;
+      if (i >= 2) ok = mbar_wait(ctx, &s.k_empty[st], ((i >> 1) - 1) & 1, 70);
+      if (!ok) break;
+      mbar_arrive_expect_tx(&s.k_full[st], nbox_qk * kBoxBytes);
+      for (int bx = 0; bx < nbox_qk; ++bx)
+        tma_load_4d(s.k[st] + bx * kBoxBytes, &tm_k, &s.k_full[st], bx * 64, kvh, n * kBlockN, b);
+      if (i >= 2) ok = mbar_wait(ctx, &s.v_empty[st], ((i >> 1) - 1) & 1, 71);
+      if (!ok) break;
+      mbar_arrive_expect_tx(&s.v_full[st], nbox_v * kBoxBytes);
+      for (int bx = 0; bx < nbox_v; ++bx)
+        tma_load_4d(s.v[st] + bx * kBoxBytes, &tm_v, &s.v_full[st], bx * 64, kvh, n * kBlockN, b);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (s.abort_flag == 1) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) { }
+    __syncthreads();
+  }
+  if (warp == 9) { __syncwarp(); tmem_dealloc(tmem, kTmemCols); }
+}
+
+// ---------------------------------------------------------------------------
+// dK / dV kernel
+// ---------------------------------------------------------------------------
+constexpr int kSubM = 64;   // query rows per inner step of the dK/dV kernel
+
+template <int HD>
+struct DkvSmem {
+  static constexpr int kKvBytes = kBlockN * HD * 2;
+  static constexpr int kQBytes = kSubM * HD * 2;
+  static constexpr int kStages = 4;
+  alignas(1024) uint8_t k[kKvBytes];
+  alignas(1024) uint8_t v[kKvBytes];
+  alignas(1024) uint8_t q[kStages][kQBytes];
+  alignas(1024) uint8_t d_o[kStages][kQBytes];
+  // per-query scalars of the sub-tile in flight, double-buffered
+  alignas(16) float lse2[2][kSubM];
+  alignas(16) float delta[2][kSubM];
+  alignas(16) int lo[2][kSubM];
+  alignas(16) int hi[2][kSubM];
+  uint64_t kv_full;
+  uint64_t q_full[kStages], q_empty[kStages];
+  uint64_t sdp_full[2], pds_full[2], scal_full[2], all_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// Enumerates the (query head of the group, 64-row query sub-tile) pairs a key
+// tile has to visit, in the same order for every role.
+struct DkvIter {
+  int g, m, half;        // head within the group, 128-row query tile, which 64-row half
+  int G, m_first, m_end, Lq, k0, k1;
+  const TileInfo* qt;
+  __device__ __forceinline__ bool tile_overlaps(int mm) const {
+    const TileInfo t = qt[mm];
+    return t.max_hi > t.min_lo && t.min_lo < k1 && t.max_hi > k0;
+  }
+  __device__ __forceinline__ bool valid() const { return g < G; }
+  __device__ __forceinline__ bool sub_ok() const { return m * kBlockM + half * kSubM < Lq; }
+  // position on the first valid item at or after the current one
+  __device__ __forceinline__ void settle() {
+    while (g < G) {
+      if (m >= m_end) { m = m_first; half = 0; ++g; continue; }
+      if (half > 1) { half = 0; ++m; continue; }
+      if (half == 0 && !tile_overlaps(m)) { ++m; continue; }
+      if (!sub_ok()) { half = 0; ++m; continue; }
+      return;
+    }
+  }
+  __device__ __forceinline__ void init(int G_, int m_first_, int m_end_, int Lq_, int k0_, const TileInfo* qt_) {
+    G = G_; m_first = m_first_; m_end = m_end_; Lq = Lq_; k0 = k0_; k1 = k0_ + kBlockN; qt = qt_;
+    g = (m_end_ > m_first_) ? 0 : G_;
+    m = m_first_; half = 0;
+    settle();
+  }
+  __device__ __forceinline__ void next() { ++half; settle(); }
+};
+
+// warps 0-3: element-wise warpgroup (thread = key row), warp 4: MMA issuer,
+// warp 5: TMA producer + TMEM owner, warps 6-7: idle
+template <typename T, int HD>
+__global__ void __launch_bounds__(256, 1)
+bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+               const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+               const BwdParams p) {
+  using Smem = DkvSmem<HD>;
+  constexpr int kStages = Smem::kStages;
+  constexpr int kKvBox = kBlockN * 64 * 2;     // 64-column box of a 128-row tile
+  constexpr int kQBox = kSubM * 64 * 2;        // 64-column box of a 64-row tile
+  constexpr uint32_t kTmemCols = 512;
+  constexpr int kFormat = Pack2<T>::kFormat;
+  // TMEM columns: S^T buffers at 0 / 64, dP^T buffers at 128 / 192, dK at 256, dV at 384
+  constexpr uint32_t cS = 0, cDP = 128, cDK = 256, cDV = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  const int G = p.Hq / p.Hkv;
+  const int n = blockIdx.x % p.nKT;            // early key tiles (most query tiles under causal masks) first
+  const int bk = blockIdx.x / p.nKT;
+  const int kvh = bk % p.Hkv;
+  const int b = bk / p.Hkv;
+  const KeyTileInfo kti = p.k_tiles[(size_t)b * p.nKT + n];
+  const TileInfo* qt_info = p.q_tiles + (size_t)b * p.nQT;
+
+  if (tid == 0) {
+    s.abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 2 : 0;
+    mbar_init(&s.kv_full, 1);
+    for (int i = 0; i < kStages; ++i) { mbar_init(&s.q_full[i], 1); mbar_init(&s.q_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&s.sdp_full[i], 1); mbar_init(&s.pds_full[i], 128); mbar_init(&s.scal_full[i], 128); }
+    mbar_init(&s.all_done, 1);
+    fence_mbar_init();
+  }
+  if (warp == 5) { tmem_alloc(&s.tmem_base, kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s.tmem_base;
+  WaitCtx ctx{&s.abort_flag, p.status, 2000000000ull};
+  const bool dead = s.abort_flag != 0;
+
+  const int nbox_qk = (p.D + 63) / 64, nbox_v = (p.V + 63) / 64;
+  const int ksteps_qk = (p.D + 15) / 16, ksteps_v = (p.V + 15) / 16;
+  const int d_pad = (p.D + 15) & ~15, v_pad = (p.V + 15) & ~15;
+
+  DkvIter it0;
+  it0.init(G, kti.m_first, kti.m_end, p.Lq, n * kBlockN, qt_info);
+  const bool any_work = it0.valid();
+
+  if (dead) {
+  } else if (warp < 4) {
+    // ------------------------ element-wise warpgroup ------------------------
+    const int r = tid;                        // key row inside the tile
+    const int key = n * kBlockN + r;
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const float c_log2 = p.scale * 1.4426950408889634f;
+    bool ok = true;
+    // per-query scalars of a sub-tile: thread t < 64 fetches lse2/delta, t >= 64 fetches lo/hi
+    auto fetch = [&](const DkvIter& it, float& f0, float& f1, int& i0, int& i1) {
+      const int qrow = it.m * kBlockM + it.half * kSubM + (tid & 63);
+      const int h = kvh * G + it.g;
+      f0 = INFINITY; f1 = 0.f; i0 = 0; i1 = 0;
+      if (qrow < p.Lq) {
+        if (tid < 64) {
+          f0 = p.lse2[((size_t)b * p.Hq + h) * p.Lq + qrow];
+          f1 = p.delta[((size_t)b * p.Hq + h) * p.Lq + qrow];
+        } else {
+          i0 = p.row_lo[(size_t)b * p.Lq + qrow];
+          i1 = p.row_hi[(size_t)b * p.Lq + qrow];
+        }
+      }
+    };
+    auto stash = [&](int buf, float f0, float f1, int i0, int i1) {
+      if (tid < 64) { s.lse2[buf][tid] = f0; s.delta[buf][tid] = f1; }
+      else { s.lo[buf][tid - 64] = i0; s.hi[buf][tid - 64] = i1; }
+      mbar_arrive(&s.scal_full[buf]);
+    };
+    DkvIter it = it0;
+    float f0, f1; int i0, i1;
+    if (it.valid()) { fetch(it, f0, f1, i0, i1); stash(0, f0, f1, i0, i1); }
+    int cnt = 0;
+    while (it.valid() && ok) {
+      const int buf = cnt & 1;
+      DkvIter nx = it; nx.next();
+      if (nx.valid()) fetch(nx, f0, f1, i0, i1);                 // in flight during this step
+      ok = mbar_wait(ctx, &s.scal_full[buf], (cnt >> 1) & 1, 82);  // scalars of this step are in shared memory
+      if (ok) ok = mbar_wait(ctx, &s.sdp_full[buf], (cnt >> 1) & 1, 80);
+      if (!ok) break;
+      tc_fence_after();
+      float sv[64], dpv[64];
+      tmem_ld_x32(tmem + lane_off + cS + buf * 64, reinterpret_cast<uint32_t*>(sv));
+      tmem_ld_x32(tmem + lane_off + cS + buf * 64 + 32, reinterpret_cast<uint32_t*>(sv) + 32);
+      tmem_ld_x32(tmem + lane_off + cDP + buf * 64, reinterpret_cast<uint32_t*>(dpv));
+      tmem_ld_x32(tmem + lane_off + cDP + buf * 64 + 32, reinterpret_cast<uint32_t*>(dpv) + 32);
+      tc_wait_ld();
+      const TileInfo ti = qt_info[it.m];
+      const bool tile_full = (n * kBlockN >= ti.max_lo) && ((n + 1) * kBlockN <= ti.min_hi);
+      uint32_t pp[32], pd[32];
+#pragma unroll
+      for (int c = 0; c < 64; c += 4) {
+        const float4 l4 = *reinterpret_cast<const float4*>(&s.lse2[buf][c]);
+        const float4 d4 = *reinterpret_cast<const float4*>(&s.delta[buf][c]);
+        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) pv[e] = ex2_approx(fmaf(sv[c + e], c_log2, -ls[e]));
+        if (!tile_full) {
+          const int4 lo4 = *reinterpret_cast<const int4*>(&s.lo[buf][c]);
+          const int4 hi4 = *reinterpret_cast<const int4*>(&s.hi[buf][c]);
+          const int los[4] = {lo4.x, lo4.y, lo4.z, lo4.w};
+          const int his[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) pv[e] = (key >= los[e] && key < his[e]) ? pv[e] : 0.f;
+        }
+        pp[(c >> 1)] = Pack2<T>::pack(pv[0], pv[1]);
+        pp[(c >> 1) + 1] = Pack2<T>::pack(pv[2], pv[3]);
+        pd[(c >> 1)] = Pack2<T>::pack(pv[0] * (dpv[c] - dl[0]), pv[1] * (dpv[c + 1] - dl[1]));
+        pd[(c >> 1) + 1] = Pack2<T>::pack(pv[2] * (dpv[c + 2] - dl[2]), pv[3] * (dpv[c + 3] - dl[3]));
+      }
+      tmem_st_x32(tmem + lane_off + cS + buf * 64, pp);
+      tmem_st_x32(tmem + lane_off + cDP + buf * 64, pd);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&s.pds_full[buf]);
+      if (nx.valid()) stash(buf ^ 1, f0, f1, i0, i1);
+      it = nx;
+      ++cnt;
+    }
+    // epilogue: dK (scaled) and dV rows of this key tile
+    if (ok && any_work) ok = mbar_wait(ctx, &s.all_done, 0, 81);
+    if (ok) {
+      tc_fence_after();
+      const bool live = key < p.Lk;
+      T* dk_row = reinterpret_cast<T*>(p.dk) + (((size_t)b * p.Lk + (live ? key : 0)) * p.Hkv + kvh) * p.D;
+      T* dv_row = reinterpret_cast<T*>(p.dv) + (((size_t)b * p.Lk + (live ? key : 0)) * p.Hkv + kvh) * p.V;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const int width = which == 0 ? p.D : p.V;
+        const int pad = which == 0 ? d_pad : v_pad;
+        const float mul = which == 0 ? p.scale : 1.f;
+        T* out = which == 0 ? dk_row : dv_row;
+        const uint32_t col = which == 0 ? cDK : cDV;
+        for (int c0 = 0; c0 < pad; c0 += 32) {
+          uint32_t o[32];
+          if (any_work) {
+            tmem_ld_x32(tmem + lane_off + col + c0, o);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] = 0u;
+          }
+          if (live) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 8) {
+              if (c0 + c < width) {
+                uint4 u;
+                u.x = Pack2<T>::pack(__uint_as_float(o[c + 0]) * mul, __uint_as_float(o[c + 1]) * mul);
+                u.y = Pack2<T>::pack(__uint_as_float(o[c + 2]) * mul, __uint_as_float(o[c + 3]) * mul);
+                u.z = Pack2<T>::pack(__uint_as_float(o[c + 4]) * mul, __uint_as_float(o[c + 5]) * mul);
+                u.w = Pack2<T>::pack(__uint_as_float(o[c + 6]) * mul, __uint_as_float(o[c + 7]) * mul);
+                *reinterpret_cast<uint4*>(out + c0 + c) = u;
+              }
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 4 && lane == 0 && any_work) {
+    // ------------------------------ MMA issuer ------------------------------
+    const uint32_t idesc_st = make_idesc(kBlockN, kSubM, kFormat, 0, 0);
+    const uint32_t idesc_dv = make_idesc(kBlockN, v_pad, kFormat, 0, 1);
+    const uint32_t idesc_dk = make_idesc(kBlockN, d_pad, kFormat, 0, 1);
+    const uint32_t ka = smem_u32(s.k), va = smem_u32(s.v);
+    auto issue_st = [&](int stage, int buf) {
+      const uint32_t qa = smem_u32(s.q[stage]), da = smem_u32(s.d_o[stage]);
+      for (int js = 0; js < ksteps_qk; ++js) {
+        umma_ss(tmem + cS + buf * 64, make_smem_desc(ka + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024),
+                make_smem_desc(qa + (js >> 2) * kQBox + (js & 3) * 32, 16, 1024), idesc_st, js > 0);
+      }
+      for (int js = 0; js < ksteps_v; ++js) {
+        umma_ss(tmem + cDP + buf * 64, make_smem_desc(va + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024),
+                make_smem_desc(da + (js >> 2) * kQBox + (js & 3) * 32, 16, 1024), idesc_st, js > 0);
+      }
+      umma_commit(&s.sdp_full[buf]);
+    };
+    bool ok = mbar_wait(ctx, &s.kv_full, 0, 90);
+    // how many items in total (cheap: same enumeration)
+    DkvIter it = it0;
+    DkvIter ahead = it0;      // item whose S^T / dP^T is issued next
+    int issued = 0, cnt = 0;
+    // prologue: S^T / dP^T of the first two items
+    for (int k2 = 0; k2 < 2 && ok && ahead.valid(); ++k2) {
+      ok = mbar_wait(ctx, &s.q_full[issued % kStages], (issued / kStages) & 1, 91);
+      if (!ok) break;
+      tc_fence_after();
+      issue_st(issued % kStages, issued & 1);
+      ++issued; ahead.next();
+    }
+    while (it.valid() && ok) {
+      const int buf = cnt & 1, st = cnt % kStages;
+      ok = mbar_wait(ctx, &s.pds_full[buf], (cnt >> 1) & 1, 92);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t qa = smem_u32(s.q[st]), da = smem_u32(s.d_o[st]);
+#pragma unroll
+      for (int js = 0; js < kSubM / 16; ++js) {
+        umma_ts(tmem + cDV, tmem + cS + buf * 64 + js * 8, make_smem_desc(da + js * 2048, kQBox, 1024), idesc_dv,
+                (cnt > 0 || js > 0) ? 1u : 0u);
+      }
+#pragma unroll
+      for (int js = 0; js < kSubM / 16; ++js) {
+        umma_ts(tmem + cDK, tmem + cDP + buf * 64 + js * 8, make_smem_desc(qa + js * 2048, kQBox, 1024), idesc_dk,
+                (cnt > 0 || js > 0) ? 1u : 0u);
+      }
+      umma_commit(&s.q_empty[st]);
+      it.next();
+      ++cnt;
+      if (ahead.valid()) {
+        ok = mbar_wait(ctx, &s.q_full[issued % kStages], (issued / kStages) & 1, 93);
+        if (!ok) break;
+        tc_fence_after();
+        issue_st(issued % kStages, issued & 1);
+        ++issued; ahead.next();
+      }
+    }
+    if (ok) umma_commit(&s.all_done);
+  } else if (warp == 5 && lane == 0 && any_work) {
+    // ------------------------------ TMA producer ------------------------------
+    tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_do); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+    mbar_arrive_expect_tx(&s.kv_full, nbox_qk * kKvBox + nbox_v * kKvBox);
+    for (int bx = 0; bx < nbox_qk; ++bx) tma_load_4d(s.k + bx * kKvBox, &tm_k, &s.kv_full, bx * 64, kvh, n * kBlockN, b);
+    for (int bx = 0; bx < nbox_v; ++bx) tma_load_4d(s.v + bx * kKvBox, &tm_v, &s.kv_full, bx * 64, kvh, n * kBlockN, b);
+    bool ok = true;
+    int cnt = 0;
+    for (DkvIter it = it0; it.valid() && ok; it.next(), ++cnt) {
+      const int st = cnt % kStages;
+      if (cnt >= kStages) ok = mbar_wait(ctx, &s.q_empty[st], ((cnt / kStages) - 1) & 1, 95);
+      if (!ok) break;
+      const int h = kvh * G + it.g;
+      const int row0 = it.m * kBlockM + it.half * kSubM;
+      mbar_arrive_expect_tx(&s.q_full[st], (nbox_qk + nbox_v) * kQBox);
+      for (int bx = 0; bx < nbox_qk; ++bx) tma_load_4d(s.q[st] + bx * kQBox, &tm_q, &s.q_full[st], bx * 64, h, row0, b);
+      for (int bx = 0; bx < nbox_v; ++bx) tma_load_4d(s.d_o[st] + bx * kQBox, &tm_do, &s.q_full[st], bx * 64, h, row0, b);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (s.abort_flag == 1) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) { }
+    __syncthreads();
+  }
+  if (warp == 5) { __syncwarp(); tmem_dealloc(tmem, kTmemCols); }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+template <typename T, int HD>
+static int launch_bwd(const XattnBwdArgs& a, BwdParams& p, cudaStream_t stream) {
+  // 1. preprocess
+  float* delta = a.workspace;
+  float* lse2 = a.workspace + (size_t)p.B * p.Hq * p.Lq;
+  p.delta = delta; p.lse2 = lse2;
+  {
+    const long long warps = (long long)p.B * p.Lq * p.Hq;
+    const long long blocks = (warps * 32 + 255) / 256;
+    bwd_pre_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
+        reinterpret_cast<const T*>(a.dy), reinterpret_cast<const T*>(a.y), a.lse, p.B, p.Lq, p.Hq, p.V,
+        a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], a.y_strides[0], a.y_strides[1], a.y_strides[2], delta, lse2);
+  }
+  CUtensorMap tq64, tdo64, tdo128, tk, tv;
+  if (make_tile_map(&tq64, a.q, a.dtype, a.batch, a.q_len, a.q_heads, a.qk_dim, a.q_strides[0], a.q_strides[1], a.q_strides[2], kSubM)) return XATTN_E_INVALID;
+  if (make_tile_map(&tdo64, a.dy, a.dtype, a.batch, a.q_len, a.q_heads, a.v_dim, a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], kSubM)) return XATTN_E_INVALID;
+  if (make_tile_map(&tdo128, a.dy, a.dtype, a.batch, a.q_len, a.q_heads, a.v_dim, a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], kBlockM)) return XATTN_E_INVALID;
+  if (make_tile_map(&tk, a.k, a.dtype, a.batch, a.k_len, a.kv_heads, a.qk_dim, a.k_strides[0], a.k_strides[1], a.k_strides[2], kBlockN)) return XATTN_E_INVALID;
+  if (make_tile_map(&tv, a.v, a.dtype, a.batch, a.k_len, a.kv_heads, a.v_dim, a.v_strides[0], a.v_strides[1], a.v_strides[2], kBlockN)) return XATTN_E_INVALID;
+  cudaError_t e;
+  // 2. dQ
+  {
+    auto kern = bwd_dq_kernel<T, HD>;
+    const size_t smem = sizeof(DqSmem<HD>) + 1024;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { set_error("cudaFuncSetAttribute(dq): %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
+    const long long grid = (long long)p.nQT * p.Hq * p.B;
+    if (grid > 0x7fffffffLL) { set_error("dQ grid out of range"); return XATTN_E_INVALID; }
+    kern<<<(unsigned)grid, 384, smem, stream>>>(tdo128, tk, tv, p);
+  }
+  // 3. dK / dV
+  {
+    auto kern = bwd_dkv_kernel<T, HD>;
+    const size_t smem = sizeof(DkvSmem<HD>) + 1024;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { set_error("cudaFuncSetAttribute(dkv): %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
+    const long long grid = (long long)p.nKT * p.Hkv * p.B;
+    if (grid > 0x7fffffffLL) { set_error("dK/dV grid out of range"); return XATTN_E_INVALID; }
+    kern<<<(unsigned)grid, 256, smem, stream>>>(tq64, tdo64, tk, tv, p);
+  }
+  e = cudaGetLastError();
+  if (e != cudaSuccess) { set_error("backward launch: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
+  return XATTN_OK;
+}
+
+int bwd_entry(const XattnBwdArgs* a, cudaStream_t stream) {
+  if (!a) { set_error("null arguments"); return XATTN_E_INVALID; }
+  if (a->dtype != XATTN_DTYPE_F16 && a->dtype != XATTN_DTYPE_BF16) { set_error("Q/K/V dtype must be fp16 or bf16"); return XATTN_E_INVALID; }
+  if (a->batch <= 0 || a->q_len <= 0 || a->k_len <= 0 || a->q_heads <= 0 || a->kv_heads <= 0 ||
+      a->q_heads % a->kv_heads != 0) { set_error("bad batch / length / head counts"); return XATTN_E_INVALID; }
+  if (a->qk_dim < 8 || a->qk_dim > 256 || a->qk_dim % 8 || a->v_dim < 8 || a->v_dim > 256 || a->v_dim % 8) {
+    set_error("head dimensions must be multiples of 8 in [8, 256]"); return XATTN_E_INVALID;
+  }
+  if (!(a->scale > 0.f) || !isfinite(a->scale)) { set_error("scale must be finite and positive"); return XATTN_E_INVALID; }
+  if (!a->q || !a->k || !a->v || !a->y || !a->dy || !a->lse || !a->plan || !a->dq || !a->dk || !a->dv ||
+      !a->workspace || !a->status) { set_error("null tensor pointer"); return XATTN_E_INVALID; }
+  for (const void* ptr : {a->q, a->y, a->dy, (const void*)a->dq, (const void*)a->dk, (const void*)a->dv}) {
+    if (reinterpret_cast<uintptr_t>(ptr) & 15) { set_error("tensors must be 16-byte aligned"); return XATTN_E_INVALID; }
+  }
+  for (const int64_t* st : {a->q_strides, a->y_strides, a->dy_strides}) {
+    for (int i = 0; i < 3; ++i) if (st[i] % 8) { set_error("q / y / dy strides must be multiples of 8 elements"); return XATTN_E_INVALID; }
+  }
+  const int hd = (int)(a->qk_dim > a->v_dim ? a->qk_dim : a->v_dim);
+  if (hd > 128) { set_error("backward supports head dimensions up to 128 in this build"); return XATTN_E_UNSUPPORTED; }
+  BwdParams p;
+  p.B = (int)a->batch; p.Lq = (int)a->q_len; p.Lk = (int)a->k_len; p.Hq = (int)a->q_heads; p.Hkv = (int)a->kv_heads;
+  p.D = (int)a->qk_dim; p.V = (int)a->v_dim;
+  const PlanLayout pl(a->batch, a->q_len, a->k_len);
+  p.nQT = (int)pl.nQT; p.nKT = (int)pl.nKT;
+  p.scale = a->scale;
+  p.row_lo = a->plan + pl.off_lo; p.row_hi = a->plan + pl.off_hi;
+  p.q_tiles = reinterpret_cast<const TileInfo*>(a->plan + pl.off_qt);
+  p.k_tiles = reinterpret_cast<const KeyTileInfo*>(a->plan + pl.off_kt);
+  p.q = a->q; p.q_sb = a->q_strides[0]; p.q_sl = a->q_strides[1]; p.q_sh = a->q_strides[2];
+  p.dq = a->dq; p.dk = a->dk; p.dv = a->dv; p.status = a->status;
+  if (a->dtype == XATTN_DTYPE_BF16) {
+    return hd <= 64 ? launch_bwd<__nv_bfloat16, 64>(*a, p, stream) : launch_bwd<__nv_bfloat16, 128>(*a, p, stream);
+  }
+  return hd <= 64 ? launch_bwd<__half, 64>(*a, p, stream) : launch_bwd<__half, 128>(*a, p, stream);
+}
+
+}  // namespace xb
