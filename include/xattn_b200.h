@@ -149,7 +149,7 @@ typedef struct {
   int dtype;
   int64_t batch, q_len, k_len;
   int64_t q_heads, kv_heads;
-  int64_t qk_dim, v_dim;         /* multiples of 8, <= 128 for now             */
+  int64_t qk_dim, v_dim;         /* multiples of 8, <= 256                      */
   const void* q;                 /* as in the forward                          */
   const void* k;
   const void* v;
@@ -172,6 +172,47 @@ typedef struct {
 
 size_t xattn_b200_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);
 int xattn_b200_bwd(const XattnBwdArgs* args, xattn_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * SoftDelta gate (HBM-bound).  Replaces _softdelta_gate_fwd, _softdelta_gate_restore
+ * and _softdelta_gate_bwd (csrc/softdelta/bindings.cc:11-53, csrc/softdelta/gate.cu:559-627)
+ * and the gate part of SoftDeltaBwdPreprocessKernel (csrc/softdelta/preprocess.cu:110-265).
+ * All tensors contiguous; `rows` = batch * tokens.
+ *   forward :  y[rows][H][V]   = read - sigmoid(g) * neg_read           (y may alias read)
+ *   backward:  read            = y + sigmoid(g) * neg_read               (recovered query read)
+ *              dneg_read[rows][Hkv][V] = - sum over the group of sigmoid(g) * dy
+ *              dg[rows][H]     = - sigmoid'(g) * <dy, neg_read>
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  int dtype;
+  int neg_is_f32;                /* neg_read is FP32 (level 1) instead of dtype */
+  int64_t rows, q_heads, kv_heads, v_dim;
+  const void* g;                 /* [rows][H] gate logits, dtype               */
+  const void* neg_read;          /* [rows][Hkv][V]                             */
+  void* read;                    /* forward: input; backward: output           */
+  void* y;                       /* forward: output; backward: input           */
+  const void* dy;                /* backward only                              */
+  void* dneg_read;               /* backward only, dtype                       */
+  void* dg;                      /* backward only, dtype                       */
+} XattnGateArgs;
+
+int xattn_b200_softdelta_gate_fwd(const XattnGateArgs* args, xattn_stream_t stream);
+int xattn_b200_softdelta_gate_bwd(const XattnGateArgs* args, xattn_stream_t stream);
+
+/* Level-1 repair: zero the dQ rows whose visible keys are all one vector
+ * (replaces _attention_precision_key_runs / _attention_precision_enforce_constant_keys,
+ * csrc/attention/precision/bindings.cc:12-24).  `workspace`: batch*kv_heads*k_len int32. */
+typedef struct {
+  int dtype;
+  int64_t batch, q_len, k_len, q_heads, kv_heads, qk_dim;
+  void* dq;                      /* [B][q_len][Hq][D] contiguous, updated in place */
+  const void* k;                 /* total keys, element strides below          */
+  int64_t k_strides[3];
+  const int32_t* plan;
+  int32_t* workspace;
+} XattnConstantKeyArgs;
+
+int xattn_b200_zero_constant_key_rows(const XattnConstantKeyArgs* args, xattn_stream_t stream);
 
 /* Reads `status` back (synchronises the stream).  0 when the word is zero. */
 int xattn_b200_check_status(const int32_t* status, xattn_stream_t stream);

@@ -1,0 +1,82 @@
+"""The CPU oracle against golden outputs of the reference's own oracle (tests/golden), and the
+interval property the device plan relies on."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "golden"))
+from golden_cases import GOLDEN_CASES, golden_inputs  # noqa: E402
+
+from oracle import attention_oracle as O  # noqa: E402
+from tests._cases import cases_for, metadata_for  # noqa: E402
+
+GOLDEN = np.load(os.path.join(HERE, "golden", "attention_golden.npz"))
+
+
+@pytest.mark.parametrize("case", GOLDEN_CASES, ids=lambda c: c["name"])
+def test_oracle_matches_reference_golden(case):
+    t = golden_inputs(case)
+    name = case["name"]
+    inc, strict = O.allowed_masks(case["Lq"], case["Lk"], case["B"], case["vis"], case["span"],
+                                  t["q_ids"], t["k_ids"], case["reset"])
+    shape = (case["B"], case["Lq"], case["Lk"])
+    n = int(np.prod(shape))
+    for mine, key in ((inc, "inclusive"), (strict, "strict")):
+        ref = np.unpackbits(GOLDEN[f"{name}/{key}"])[:n].reshape(shape).astype(bool)
+        assert np.array_equal(mine.numpy(), ref), f"{key} mask differs from the reference's"
+    q, k, v = (t[x].clone().requires_grad_() for x in ("q", "k", "v"))
+    y = O.attention_from_mask(q, k, v, strict if case["strict"] else inc, case["D"] ** -0.5)
+    grads = torch.autograd.grad(y, (q, k, v), t["dy"])
+    for val, key in zip((y, *grads), ("y", "dq", "dk", "dv")):
+        np.testing.assert_allclose(val.detach().numpy(), GOLDEN[f"{name}/{key}"], rtol=1e-12, atol=1e-13)
+    if case["softdelta"]:
+        q, k, v, g = (t[x].clone().requires_grad_() for x in ("q", "k", "v", "g"))
+        ys, _, _ = O.softdelta(q, k, v, g, None, scale=case["D"] ** -0.5, q_segment_idx=t["q_ids"],
+                               k_segment_idx=t["k_ids"], visibility=case["vis"], span=case["span"],
+                               reset_position_per_segment=case["reset"])
+        gs = torch.autograd.grad(ys, (q, k, v, g), t["dy"])
+        for val, key in zip((ys, *gs), ("sd_y", "sd_dq", "sd_dk", "sd_dv", "sd_dg")):
+            np.testing.assert_allclose(val.detach().numpy(), GOLDEN[f"{name}/{key}"], rtol=1e-12, atol=1e-13)
+
+
+@pytest.mark.parametrize("operation", ("full", "window", "chunk"))
+@pytest.mark.parametrize("strict", (False, True))
+def test_visible_keys_form_one_interval(operation, strict):
+    """Every case of the parity matrix: a row's visible keys are contiguous (row_intervals asserts it)
+    and the interval reproduces the mask."""
+    for case in cases_for(operation):
+        if case.q_length * (case.k_length + case.previous) > 80000:
+            continue
+        _, qi, ki = metadata_for(case, torch.device("cpu"))
+        total = case.k_length + case.previous
+        lo, hi = O.row_intervals(case.q_length, total, case.batch, operation, case.span, qi, ki, case.reset, strict)
+        inc, st = O.allowed_masks(case.q_length, total, case.batch, operation, case.span, qi, ki, case.reset)
+        mask = st if strict else inc
+        idx = torch.arange(total)[None, None, :]
+        rebuilt = (idx >= lo[:, :, None]) & (idx < hi[:, :, None])
+        assert torch.equal(rebuilt, mask), case.name
+
+
+def test_empty_rows_read_zero():
+    q = torch.randn(1, 3, 2, 8, dtype=torch.float64)
+    k = torch.randn(1, 5, 1, 8, dtype=torch.float64)
+    v = torch.randn(1, 5, 1, 8, dtype=torch.float64)
+    mask = torch.zeros(1, 3, 5, dtype=torch.bool)
+    mask[0, 2, :2] = True
+    y = O.attention_from_mask(q, k, v, mask, 0.3)
+    assert torch.count_nonzero(y[:, :2]) == 0 and torch.isfinite(y).all()
+    lse = O.lse_from_mask(q, k, mask, 0.3)
+    assert torch.isinf(lse[0, :, :2]).all() and torch.isfinite(lse[0, :, 2]).all()
+
+
+def test_visible_pair_count_causal():
+    lo, hi = O.row_intervals(1024, 1024, 1, "full", None)
+    assert O.visible_pairs(lo, hi) == 1024 * 1025 // 2
+    lo, hi = O.row_intervals(64, 64, 1, "window", 7)
+    assert O.visible_pairs(lo, hi) == sum(min(i, 7) + 1 for i in range(64))
+    lo, hi = O.row_intervals(64, 64, 1, "chunk", 8)
+    assert O.visible_pairs(lo, hi) == sum(i - max(0, (i // 8 - 1) * 8) + 1 for i in range(64))

@@ -69,6 +69,25 @@ class BwdArgs(C.Structure):
     ]
 
 
+class GateArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int), ("neg_is_f32", C.c_int),
+        ("rows", C.c_int64), ("q_heads", C.c_int64), ("kv_heads", C.c_int64), ("v_dim", C.c_int64),
+        ("g", C.c_void_p), ("neg_read", C.c_void_p), ("read", C.c_void_p), ("y", C.c_void_p),
+        ("dy", C.c_void_p), ("dneg_read", C.c_void_p), ("dg", C.c_void_p),
+    ]
+
+
+class ConstantKeyArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int),
+        ("batch", C.c_int64), ("q_len", C.c_int64), ("k_len", C.c_int64),
+        ("q_heads", C.c_int64), ("kv_heads", C.c_int64), ("qk_dim", C.c_int64),
+        ("dq", C.c_void_p), ("k", C.c_void_p), ("k_strides", C.c_int64 * 3),
+        ("plan", C.c_void_p), ("workspace", C.c_void_p),
+    ]
+
+
 _lock = threading.Lock()
 _lib: Optional[C.CDLL] = None
 
@@ -82,6 +101,9 @@ SYMBOLS = {
     "xattn_b200_fwd": (C.c_int, [C.POINTER(FwdArgs), C.c_void_p]),
     "xattn_b200_bwd_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
     "xattn_b200_bwd": (C.c_int, [C.POINTER(BwdArgs), C.c_void_p]),
+    "xattn_b200_softdelta_gate_fwd": (C.c_int, [C.POINTER(GateArgs), C.c_void_p]),
+    "xattn_b200_softdelta_gate_bwd": (C.c_int, [C.POINTER(GateArgs), C.c_void_p]),
+    "xattn_b200_zero_constant_key_rows": (C.c_int, [C.POINTER(ConstantKeyArgs), C.c_void_p]),
     "xattn_b200_check_status": (C.c_int, [C.c_void_p, C.c_void_p]),
 }
 

@@ -263,3 +263,60 @@ def attention_bwd(
         _lib.check(lib.xattn_b200_bwd(C.byref(args), _stream_ptr()), "xattn_b200_bwd")
         _post_launch(st)
     return dq, dk, dv
+
+
+def zero_constant_key_rows(dq: Tensor, k_all: Tensor, plan: Tensor) -> Tensor:
+    """Level-1 repair, in place on ``dq`` (contiguous): rows whose visible keys are one repeated
+    vector get an exactly zero gradient."""
+    lib = _lib.load()
+    k_all = tma_ready(k_all)
+    B, Lq, Hq, D = dq.shape
+    Lk, Hkv = k_all.shape[1], k_all.shape[2]
+    ws = torch.empty(B * Hkv * Lk, dtype=torch.int32, device=dq.device)
+    args = _lib.ConstantKeyArgs()
+    args.dtype = _DTYPES[dq.dtype]
+    args.batch, args.q_len, args.k_len, args.q_heads, args.kv_heads, args.qk_dim = B, Lq, Lk, Hq, Hkv, D
+    args.dq, args.k = dq.data_ptr(), k_all.data_ptr()
+    args.k_strides = (C.c_int64 * 3)(k_all.stride(0), k_all.stride(1), k_all.stride(2))
+    args.plan, args.workspace = plan.data_ptr(), ws.data_ptr()
+    with torch.cuda.device(dq.device):
+        _lib.check(lib.xattn_b200_zero_constant_key_rows(C.byref(args), _stream_ptr()),
+                   "xattn_b200_zero_constant_key_rows")
+    return dq
+
+
+def _gate_args(g: Tensor, neg_read: Tensor, q_heads: int) -> "_lib.GateArgs":
+    args = _lib.GateArgs()
+    args.dtype = _DTYPES[g.dtype]
+    args.neg_is_f32 = int(neg_read.dtype == torch.float32)
+    B, L, Hkv, V = neg_read.shape
+    args.rows, args.q_heads, args.kv_heads, args.v_dim = B * L, q_heads, Hkv, V
+    args.g, args.neg_read = g.data_ptr(), neg_read.data_ptr()
+    return args
+
+
+def softdelta_gate_fwd(read: Tensor, neg_read: Tensor, g: Tensor, out: Optional[Tensor] = None) -> Tensor:
+    """y = read - sigmoid(g) * neg_read; ``out`` may be ``read`` itself."""
+    lib = _lib.load()
+    read, neg_read, g = read.contiguous(), neg_read.contiguous(), g.contiguous()
+    y = torch.empty_like(read) if out is None else out
+    args = _gate_args(g, neg_read, read.shape[2])
+    args.read, args.y = read.data_ptr(), y.data_ptr()
+    with torch.cuda.device(read.device):
+        _lib.check(lib.xattn_b200_softdelta_gate_fwd(C.byref(args), _stream_ptr()), "xattn_b200_softdelta_gate_fwd")
+    return y
+
+
+def softdelta_gate_bwd(dy: Tensor, y: Tensor, neg_read: Tensor, g: Tensor) -> Tuple[Tensor, Tensor, Tensor]:
+    """(read, dneg_read, dg): the recovered query read and the gate's gradients, one pass."""
+    lib = _lib.load()
+    dy, y, neg_read, g = dy.contiguous(), y.contiguous(), neg_read.contiguous(), g.contiguous()
+    read = torch.empty_like(y)
+    dneg = torch.empty(neg_read.shape, dtype=y.dtype, device=y.device)
+    dg = torch.empty_like(g)
+    args = _gate_args(g, neg_read, y.shape[2])
+    args.read, args.y, args.dy = read.data_ptr(), y.data_ptr(), dy.data_ptr()
+    args.dneg_read, args.dg = dneg.data_ptr(), dg.data_ptr()
+    with torch.cuda.device(y.device):
+        _lib.check(lib.xattn_b200_softdelta_gate_bwd(C.byref(args), _stream_ptr()), "xattn_b200_softdelta_gate_bwd")
+    return read, dneg, dg

@@ -5,6 +5,9 @@ namespace xb {
 const char* last_error();
 int fwd_entry(const XattnFwdArgs* a, cudaStream_t stream);
 int bwd_entry(const XattnBwdArgs* a, cudaStream_t stream);
+int gate_fwd_entry(const XattnGateArgs* a, cudaStream_t stream);
+int gate_bwd_entry(const XattnGateArgs* a, cudaStream_t stream);
+int zero_constant_entry(const XattnConstantKeyArgs* a, cudaStream_t stream);
 int build_plan_entry(const XattnPlanArgs* a, cudaStream_t stream);
 int build_varlen_plan_entry(const XattnVarlenPlanArgs* a, cudaStream_t stream);
 }  // namespace xb
@@ -39,6 +42,18 @@ size_t xattn_b200_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_
 
 int xattn_b200_bwd(const XattnBwdArgs* args, xattn_stream_t stream) {
   return xb::bwd_entry(args, static_cast<cudaStream_t>(stream));
+}
+
+int xattn_b200_softdelta_gate_fwd(const XattnGateArgs* args, xattn_stream_t stream) {
+  return xb::gate_fwd_entry(args, static_cast<cudaStream_t>(stream));
+}
+
+int xattn_b200_softdelta_gate_bwd(const XattnGateArgs* args, xattn_stream_t stream) {
+  return xb::gate_bwd_entry(args, static_cast<cudaStream_t>(stream));
+}
+
+int xattn_b200_zero_constant_key_rows(const XattnConstantKeyArgs* args, xattn_stream_t stream) {
+  return xb::zero_constant_entry(args, static_cast<cudaStream_t>(stream));
 }
 
 int xattn_b200_check_status(const int32_t* status, xattn_stream_t stream) {

@@ -83,12 +83,17 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, 
 // ---------------------------------------------------------------------------
 // dQ kernel
 // ---------------------------------------------------------------------------
-template <int HD>
+// HD <= 128: key tiles of BN = 128; TMEM holds Q (packed), dS, S, dP and dQ side by side, so
+//            S / dP of the next key tile are issued while dS of the current one is being built.
+// HD  = 256: BN = 64 and dS overwrites S in place (Q takes 128 columns and dQ 256), so the
+//            tensor core alternates S, dP -> dQ per key tile.
+template <int HD, int BN>
 struct DqSmem {
-  static constexpr int kTileBytes = kBlockM * HD * 2;
-  alignas(1024) uint8_t d_o[kTileBytes];
-  alignas(1024) uint8_t k[2][kTileBytes];
-  alignas(1024) uint8_t v[2][kTileBytes];
+  static constexpr int kDoBytes = kBlockM * HD * 2;
+  static constexpr int kKvBytes = BN * HD * 2;
+  alignas(1024) uint8_t d_o[kDoBytes];
+  alignas(1024) uint8_t k[2][kKvBytes];
+  alignas(1024) uint8_t v[2][kKvBytes];
   uint64_t do_full, q_ready;
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
   uint64_t sdp_full, sdp_free, ds_full, dq_done;
@@ -96,18 +101,25 @@ struct DqSmem {
   int abort_flag;
 };
 
-// warps 0-3 / 4-7: element-wise warpgroups (thread = query row; columns 0-63 / 64-127 of a key tile)
+// warps 0-3 / 4-7: element-wise warpgroups (thread = query row; first / second half of the key-tile columns)
 // warp 8: MMA issuer, warp 9: TMA producer + TMEM owner, warps 10-11: idle
-template <typename T, int HD>
+template <typename T, int HD, int BN>
 __global__ void __launch_bounds__(384, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const BwdParams p) {
-  using Smem = DqSmem<HD>;
-  constexpr int kBoxBytes = kBlockM * 64 * 2;
+  using Smem = DqSmem<HD, BN>;
+  constexpr bool kAlias = HD > 128;
+  constexpr int kDoBox = kBlockM * 64 * 2;     // 64-column box of the 128-row dO tile
+  constexpr int kKvBox = BN * 64 * 2;          // 64-column box of a BN-row K / V tile
+  constexpr int CH = BN / 2;                   // key columns per element-wise thread
   constexpr uint32_t kTmemCols = 512;
   constexpr int kFormat = Pack2<T>::kFormat;
   // TMEM columns
-  constexpr uint32_t cQ = 0, cDS = 64, cS = 128, cDP = 256, cDQ = 384;
+  constexpr uint32_t cQ = 0;
+  constexpr uint32_t cS = 128, cDP = kAlias ? 192 : 256;
+  constexpr uint32_t cDS = kAlias ? cS : 64;   // half hf of dS starts at cDS + hf * kDsStride
+  constexpr uint32_t kDsStride = kAlias ? CH : CH / 2;
+  constexpr uint32_t cDQ = kAlias ? 256 : 384;
 
   extern __shared__ uint8_t smem_raw[];
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -126,8 +138,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
   {
     const TileInfo ti = p.q_tiles[(size_t)b * p.nQT + qt];
     if (ti.max_hi > ti.min_lo) {
-      n_lo = ti.min_lo / kBlockN;
-      n_hi = (ti.max_hi + kBlockN - 1) / kBlockN;
+      n_lo = ti.min_lo / BN;
+      n_hi = (ti.max_hi + BN - 1) / BN;
       full_lo = ti.max_lo;
       full_hi = ti.min_hi;
     }
@@ -178,16 +190,20 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
       {
         const T* q_row = reinterpret_cast<const T*>(p.q) + b * p.q_sb + (live ? row : 0) * p.q_sl + h * p.q_sh;
         constexpr int kCols = HD / 4;           // packed columns per half
-        uint32_t qv[kCols];
+        constexpr int kStep = kCols < 32 ? kCols : 32;
 #pragma unroll
-        for (int c = 0; c < kCols; c += 4) {
-          const int e = (hf * kCols + c) * 2;   // first element of this 16-byte chunk
-          uint4 u = make_uint4(0, 0, 0, 0);
-          if (live && e < p.D) u = *reinterpret_cast<const uint4*>(q_row + e);
-          qv[c] = u.x; qv[c + 1] = u.y; qv[c + 2] = u.z; qv[c + 3] = u.w;
+        for (int c0 = 0; c0 < kCols; c0 += kStep) {
+          uint32_t qv[kStep];
+#pragma unroll
+          for (int c = 0; c < kStep; c += 4) {
+            const int e = (hf * kCols + c0 + c) * 2;   // first element of this 16-byte chunk
+            uint4 u = make_uint4(0, 0, 0, 0);
+            if (live && e < p.D) u = *reinterpret_cast<const uint4*>(q_row + e);
+            qv[c] = u.x; qv[c + 1] = u.y; qv[c + 2] = u.z; qv[c + 3] = u.w;
+          }
+          if (kStep == 32) tmem_st_x32(tmem + lane_off + cQ + hf * kCols + c0, qv);
+          else tmem_st_x16(tmem + lane_off + cQ + hf * kCols + c0, qv);
         }
-        if (kCols == 32) tmem_st_x32(tmem + lane_off + cQ + hf * kCols, qv);
-        else tmem_st_x16(tmem + lane_off + cQ + hf * kCols, qv);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(&s.q_ready);
@@ -203,23 +219,24 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
       const float c_log2 = p.scale * 1.4426950408889634f;
       bool ok = true;
       for (int i = 0; i < iters && ok; ++i) {
-        const int col0 = (n_lo + i) * kBlockN + hf * 64;
+        const int col0 = (n_lo + i) * BN + hf * CH;
         ok = mbar_wait(ctx, &s.sdp_full, i & 1, 50);
         if (!ok) break;
         tc_fence_after();
-        float sv[64], dpv[64];
-        tmem_ld_x32(tmem + lane_off + cS + hf * 64, reinterpret_cast<uint32_t*>(sv));
-        tmem_ld_x32(tmem + lane_off + cS + hf * 64 + 32, reinterpret_cast<uint32_t*>(sv) + 32);
-        tmem_ld_x32(tmem + lane_off + cDP + hf * 64, reinterpret_cast<uint32_t*>(dpv));
-        tmem_ld_x32(tmem + lane_off + cDP + hf * 64 + 32, reinterpret_cast<uint32_t*>(dpv) + 32);
+        float sv[CH], dpv[CH];
+#pragma unroll
+        for (int c = 0; c < CH; c += 32) {
+          tmem_ld_x32(tmem + lane_off + cS + hf * CH + c, reinterpret_cast<uint32_t*>(sv) + c);
+          tmem_ld_x32(tmem + lane_off + cDP + hf * CH + c, reinterpret_cast<uint32_t*>(dpv) + c);
+        }
         tc_wait_ld();
         tc_fence_before();
         mbar_arrive(&s.sdp_free);
-        const bool tile_full = ((n_lo + i) * kBlockN >= full_lo) && ((n_lo + i + 1) * kBlockN <= full_hi);
+        const bool tile_full = ((n_lo + i) * BN >= full_lo) && ((n_lo + i + 1) * BN <= full_hi);
         const int rl = lo - col0, rh = hi - col0;
-        uint32_t pk[32];
+        uint32_t pk[CH / 2];
 #pragma unroll
-        for (int c = 0; c < 64; c += 2) {
+        for (int c = 0; c < CH; c += 2) {
           float p0 = ex2_approx(fmaf(sv[c], c_log2, -lse2));
           float p1 = ex2_approx(fmaf(sv[c + 1], c_log2, -lse2));
           if (!tile_full) {
@@ -228,12 +245,13 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
           }
           pk[c >> 1] = Pack2<T>::pack(p0 * (dpv[c] - delta), p1 * (dpv[c + 1] - delta));
         }
-        if (i > 0) {
+        if (!kAlias && i > 0) {
           ok = mbar_wait(ctx, &s.dq_done, (i - 1) & 1, 51);
           if (!ok) break;
           tc_fence_after();
         }
-        tmem_st_x32(tmem + lane_off + cDS + hf * 32, pk);
+        if (CH == 64) tmem_st_x32(tmem + lane_off + cDS + hf * kDsStride, pk);
+        else tmem_st_x16(tmem + lane_off + cDS + hf * kDsStride, pk);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(&s.ds_full);
@@ -266,20 +284,31 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
     }
   } else if (warp == 8 && lane == 0 && iters > 0) {
     // ------------------------------ MMA issuer ------------------------------
-    const uint32_t idesc_s = make_idesc(kBlockM, kBlockN, kFormat, 0, 0);
+    const uint32_t idesc_s = make_idesc(kBlockM, BN, kFormat, 0, 0);
     const uint32_t idesc_dq = make_idesc(kBlockM, d_pad, kFormat, 0, 1);
     auto issue_s_dp = [&](int stage) {
       const uint32_t ka = smem_u32(s.k[stage]), va = smem_u32(s.v[stage]), da = smem_u32(s.d_o);
       for (int js = 0; js < ksteps_qk; ++js) {
-        const uint32_t off = (js >> 2) * kBoxBytes + (js & 3) * 32;
-        umma_ts(tmem + cS, tmem + cQ + js * 8, make_smem_desc(ka + off, 16, 1024), idesc_s, js > 0);
+        umma_ts(tmem + cS, tmem + cQ + js * 8, make_smem_desc(ka + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024),
+                idesc_s, js > 0);
       }
       for (int js = 0; js < ksteps_v; ++js) {
-        const uint32_t off = (js >> 2) * kBoxBytes + (js & 3) * 32;
-        umma_ss(tmem + cDP, make_smem_desc(da + off, 16, 1024), make_smem_desc(va + off, 16, 1024), idesc_s, js > 0);
+        umma_ss(tmem + cDP, make_smem_desc(da + (js >> 2) * kDoBox + (js & 3) * 32, 16, 1024),
+                make_smem_desc(va + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024), idesc_s, js > 0);
       }
       umma_commit(&s.sdp_full);
       umma_commit(&s.v_empty[stage]);
+    };
+    auto issue_dq = [&](int i) {
+      const uint32_t ka = smem_u32(s.k[i & 1]);
+#pragma unroll
+      for (int js = 0; js < BN / 16; ++js) {
+        const uint32_t a_col = cDS + (js / (CH / 16)) * kDsStride + (js % (CH / 16)) * 8;
+        umma_ts(tmem + cDQ, tmem + a_col, make_smem_desc(ka + js * 2048, kKvBox, 1024), idesc_dq,
+                (i > 0 || js > 0) ? 1u : 0u);
+      }
+      umma_commit(&s.dq_done);
+      umma_commit(&s.k_empty[i & 1]);
     };
     bool ok = mbar_wait(ctx, &s.do_full, 0, 60);
     if (ok) ok = mbar_wait(ctx, &s.q_ready, 0, 61);
@@ -287,47 +316,48 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
     if (ok) ok = mbar_wait(ctx, &s.v_full[0], 0, 63);
     if (ok) { tc_fence_after(); issue_s_dp(0); }
     for (int i = 0; i < iters && ok; ++i) {
-      const int st = i & 1;
+      if (kAlias) {
+        // dS sits on top of S: dQ of this tile first, then S / dP of the next
+        ok = mbar_wait(ctx, &s.ds_full, i & 1, 67);
+        if (!ok) break;
+        tc_fence_after();
+        issue_dq(i);
+      }
       if (i + 1 < iters) {
         const int sn = (i + 1) & 1;
         ok = mbar_wait(ctx, &s.k_full[sn], ((i + 1) >> 1) & 1, 64);
         if (ok) ok = mbar_wait(ctx, &s.v_full[sn], ((i + 1) >> 1) & 1, 65);
-        if (ok) ok = mbar_wait(ctx, &s.sdp_free, i & 1, 66);
+        if (ok && !kAlias) ok = mbar_wait(ctx, &s.sdp_free, i & 1, 66);
         if (!ok) break;
         tc_fence_after();
         issue_s_dp(sn);
       }
-      ok = mbar_wait(ctx, &s.ds_full, i & 1, 67);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t ka = smem_u32(s.k[st]);
-#pragma unroll
-      for (int js = 0; js < kBlockN / 16; ++js) {
-        umma_ts(tmem + cDQ, tmem + cDS + js * 8, make_smem_desc(ka + js * 2048, kBoxBytes, 1024), idesc_dq,
-                (i > 0 || js > 0) ? 1u : 0u);
+      if (!kAlias) {
+        ok = mbar_wait(ctx, &s.ds_full, i & 1, 67);
+        if (!ok) break;
+        tc_fence_after();
+        issue_dq(i);
       }
-      umma_commit(&s.dq_done);
-      umma_commit(&s.k_empty[st]);
     }
   } else if (warp == 9 && lane == 0 && iters > 0) {
     // ------------------------------ TMA producer ------------------------------
     tma_prefetch_desc(&tm_do); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
-    mbar_arrive_expect_tx(&s.do_full, nbox_v * kBoxBytes);
+    mbar_arrive_expect_tx(&s.do_full, nbox_v * kDoBox);
     for (int bx = 0; bx < nbox_v; ++bx)
-      tma_load_4d(s.d_o + bx * kBoxBytes, &tm_do, &s.do_full, bx * 64, h, qt * kBlockM, b);
+      tma_load_4d(s.d_o + bx * kDoBox, &tm_do, &s.do_full, bx * 64, h, qt * kBlockM, b);
     bool ok = true;
     for (int i = 0; i < iters && ok; ++i) {
       const int st = i & 1, n = n_lo + i;
       if (i >= 2) ok = mbar_wait(ctx, &s.k_empty[st], ((i >> 1) - 1) & 1, 70);
       if (!ok) break;
-      mbar_arrive_expect_tx(&s.k_full[st], nbox_qk * kBoxBytes);
+      mbar_arrive_expect_tx(&s.k_full[st], nbox_qk * kKvBox);
       for (int bx = 0; bx < nbox_qk; ++bx)
-        tma_load_4d(s.k[st] + bx * kBoxBytes, &tm_k, &s.k_full[st], bx * 64, kvh, n * kBlockN, b);
+        tma_load_4d(s.k[st] + bx * kKvBox, &tm_k, &s.k_full[st], bx * 64, kvh, n * BN, b);
       if (i >= 2) ok = mbar_wait(ctx, &s.v_empty[st], ((i >> 1) - 1) & 1, 71);
       if (!ok) break;
-      mbar_arrive_expect_tx(&s.v_full[st], nbox_v * kBoxBytes);
+      mbar_arrive_expect_tx(&s.v_full[st], nbox_v * kKvBox);
       for (int bx = 0; bx < nbox_v; ++bx)
-        tma_load_4d(s.v[st] + bx * kBoxBytes, &tm_v, &s.v_full[st], bx * 64, kvh, n * kBlockN, b);
+        tma_load_4d(s.v[st] + bx * kKvBox, &tm_v, &s.v_full[st], bx * 64, kvh, n * BN, b);
     }
   }
 
@@ -344,22 +374,24 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
 // ---------------------------------------------------------------------------
 // dK / dV kernel
 // ---------------------------------------------------------------------------
-constexpr int kSubM = 64;   // query rows per inner step of the dK/dV kernel
+// MODE 0: dK and dV together (HD <= 128).  MODE 1: dV only, MODE 2: dK only (HD = 256, where
+// the two accumulators do not fit TMEM side by side).  SM: query rows per inner step.
+enum { kDkvBoth = 0, kDvOnly = 1, kDkOnly = 2 };
 
-template <int HD>
+template <int HD, int MODE, int SM>
 struct DkvSmem {
   static constexpr int kKvBytes = kBlockN * HD * 2;
-  static constexpr int kQBytes = kSubM * HD * 2;
-  static constexpr int kStages = 4;
+  static constexpr int kQBytes = SM * HD * 2;
+  static constexpr int kStages = MODE == kDkvBoth ? 4 : 2;
   alignas(1024) uint8_t k[kKvBytes];
-  alignas(1024) uint8_t v[kKvBytes];
+  alignas(1024) uint8_t v[MODE == kDvOnly ? 1024 : kKvBytes];
   alignas(1024) uint8_t q[kStages][kQBytes];
   alignas(1024) uint8_t d_o[kStages][kQBytes];
   // per-query scalars of the sub-tile in flight, double-buffered
-  alignas(16) float lse2[2][kSubM];
-  alignas(16) float delta[2][kSubM];
-  alignas(16) int lo[2][kSubM];
-  alignas(16) int hi[2][kSubM];
+  alignas(16) float lse2[2][SM];
+  alignas(16) float delta[2][SM];
+  alignas(16) int lo[2][SM];
+  alignas(16) int hi[2][SM];
   uint64_t kv_full;
   uint64_t q_full[kStages], q_empty[kStages];
   uint64_t sdp_full[2], pds_full[2], scal_full[2], all_done;
@@ -367,10 +399,12 @@ struct DkvSmem {
   int abort_flag;
 };
 
-// Enumerates the (query head of the group, 64-row query sub-tile) pairs a key
+// Enumerates the (query head of the group, SM-row query sub-tile) pairs a key
 // tile has to visit, in the same order for every role.
+template <int SM>
 struct DkvIter {
-  int g, m, half;        // head within the group, 128-row query tile, which 64-row half
+  static constexpr int kParts = kBlockM / SM;
+  int g, m, part;        // head within the group, 128-row query tile, which SM-row part
   int G, m_first, m_end, Lq, k0, k1;
   const TileInfo* qt;
   __device__ __forceinline__ bool tile_overlaps(int mm) const {
@@ -378,41 +412,44 @@ struct DkvIter {
     return t.max_hi > t.min_lo && t.min_lo < k1 && t.max_hi > k0;
   }
   __device__ __forceinline__ bool valid() const { return g < G; }
-  __device__ __forceinline__ bool sub_ok() const { return m * kBlockM + half * kSubM < Lq; }
+  __device__ __forceinline__ int row0() const { return m * kBlockM + part * SM; }
   // position on the first valid item at or after the current one
   __device__ __forceinline__ void settle() {
     while (g < G) {
-      if (m >= m_end) { m = m_first; half = 0; ++g; continue; }
-      if (half > 1) { half = 0; ++m; continue; }
-      if (half == 0 && !tile_overlaps(m)) { ++m; continue; }
-      if (!sub_ok()) { half = 0; ++m; continue; }
+      if (m >= m_end) { m = m_first; part = 0; ++g; continue; }
+      if (part >= kParts) { part = 0; ++m; continue; }
+      if (part == 0 && !tile_overlaps(m)) { ++m; continue; }
+      if (row0() >= Lq) { part = 0; ++m; continue; }
       return;
     }
   }
   __device__ __forceinline__ void init(int G_, int m_first_, int m_end_, int Lq_, int k0_, const TileInfo* qt_) {
     G = G_; m_first = m_first_; m_end = m_end_; Lq = Lq_; k0 = k0_; k1 = k0_ + kBlockN; qt = qt_;
     g = (m_end_ > m_first_) ? 0 : G_;
-    m = m_first_; half = 0;
+    m = m_first_; part = 0;
     settle();
   }
-  __device__ __forceinline__ void next() { ++half; settle(); }
+  __device__ __forceinline__ void next() { ++part; settle(); }
 };
 
 // warps 0-3: element-wise warpgroup (thread = key row), warp 4: MMA issuer,
 // warp 5: TMA producer + TMEM owner, warps 6-7: idle
-template <typename T, int HD>
+template <typename T, int HD, int MODE, int SM>
 __global__ void __launch_bounds__(256, 1)
 bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                const BwdParams p) {
-  using Smem = DkvSmem<HD>;
+  using Smem = DkvSmem<HD, MODE, SM>;
+  using Iter = DkvIter<SM>;
   constexpr int kStages = Smem::kStages;
+  constexpr bool kWantDk = MODE != kDvOnly, kWantDv = MODE != kDkOnly;
   constexpr int kKvBox = kBlockN * 64 * 2;     // 64-column box of a 128-row tile
-  constexpr int kQBox = kSubM * 64 * 2;        // 64-column box of a 64-row tile
+  constexpr int kQBox = SM * 64 * 2;           // 64-column box of an SM-row tile
   constexpr uint32_t kTmemCols = 512;
   constexpr int kFormat = Pack2<T>::kFormat;
-  // TMEM columns: S^T buffers at 0 / 64, dP^T buffers at 128 / 192, dK at 256, dV at 384
-  constexpr uint32_t cS = 0, cDP = 128, cDK = 256, cDV = 384;
+  // TMEM columns: S^T buffers at 0 / SM, dP^T buffers at 128 / 128 + SM, accumulators from 256
+  constexpr uint32_t cS = 0, cDP = 128;
+  constexpr uint32_t cDK = 256, cDV = MODE == kDkvBoth ? 384 : 256;
 
   extern __shared__ uint8_t smem_raw[];
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -430,7 +467,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     s.abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 2 : 0;
     mbar_init(&s.kv_full, 1);
     for (int i = 0; i < kStages; ++i) { mbar_init(&s.q_full[i], 1); mbar_init(&s.q_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s.sdp_full[i], 1); mbar_init(&s.pds_full[i], 128); mbar_init(&s.scal_full[i], 128); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.sdp_full[i], 1); mbar_init(&s.pds_full[i], 128); mbar_init(&s.scal_full[i], 128);
+    }
     mbar_init(&s.all_done, 1);
     fence_mbar_init();
   }
@@ -446,7 +485,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int ksteps_qk = (p.D + 15) / 16, ksteps_v = (p.V + 15) / 16;
   const int d_pad = (p.D + 15) & ~15, v_pad = (p.V + 15) & ~15;
 
-  DkvIter it0;
+  Iter it0;
   it0.init(G, kti.m_first, kti.m_end, p.Lq, n * kBlockN, qt_info);
   const bool any_work = it0.valid();
 
@@ -459,11 +498,12 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const float c_log2 = p.scale * 1.4426950408889634f;
     bool ok = true;
     // per-query scalars of a sub-tile: thread t < 64 fetches lse2/delta, t >= 64 fetches lo/hi
-    auto fetch = [&](const DkvIter& it, float& f0, float& f1, int& i0, int& i1) {
-      const int qrow = it.m * kBlockM + it.half * kSubM + (tid & 63);
+    const int sq = tid & 63;
+    auto fetch = [&](const Iter& it, float& f0, float& f1, int& i0, int& i1) {
+      const int qrow = it.row0() + sq;
       const int h = kvh * G + it.g;
       f0 = INFINITY; f1 = 0.f; i0 = 0; i1 = 0;
-      if (qrow < p.Lq) {
+      if (sq < SM && qrow < p.Lq) {
         if (tid < 64) {
           f0 = p.lse2[((size_t)b * p.Hq + h) * p.Lq + qrow];
           f1 = p.delta[((size_t)b * p.Hq + h) * p.Lq + qrow];
@@ -474,37 +514,38 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
     };
     auto stash = [&](int buf, float f0, float f1, int i0, int i1) {
-      if (tid < 64) { s.lse2[buf][tid] = f0; s.delta[buf][tid] = f1; }
-      else { s.lo[buf][tid - 64] = i0; s.hi[buf][tid - 64] = i1; }
+      if (sq < SM) {
+        if (tid < 64) { s.lse2[buf][sq] = f0; s.delta[buf][sq] = f1; }
+        else { s.lo[buf][sq] = i0; s.hi[buf][sq] = i1; }
+      }
       mbar_arrive(&s.scal_full[buf]);
     };
-    DkvIter it = it0;
+    Iter it = it0;
     float f0, f1; int i0, i1;
     if (it.valid()) { fetch(it, f0, f1, i0, i1); stash(0, f0, f1, i0, i1); }
     int cnt = 0;
     while (it.valid() && ok) {
       const int buf = cnt & 1;
-      DkvIter nx = it; nx.next();
+      Iter nx = it; nx.next();
       if (nx.valid()) fetch(nx, f0, f1, i0, i1);                 // in flight during this step
       ok = mbar_wait(ctx, &s.scal_full[buf], (cnt >> 1) & 1, 82);  // scalars of this step are in shared memory
       if (ok) ok = mbar_wait(ctx, &s.sdp_full[buf], (cnt >> 1) & 1, 80);
       if (!ok) break;
       tc_fence_after();
-      float sv[64], dpv[64];
-      tmem_ld_x32(tmem + lane_off + cS + buf * 64, reinterpret_cast<uint32_t*>(sv));
-      tmem_ld_x32(tmem + lane_off + cS + buf * 64 + 32, reinterpret_cast<uint32_t*>(sv) + 32);
-      tmem_ld_x32(tmem + lane_off + cDP + buf * 64, reinterpret_cast<uint32_t*>(dpv));
-      tmem_ld_x32(tmem + lane_off + cDP + buf * 64 + 32, reinterpret_cast<uint32_t*>(dpv) + 32);
+      float sv[SM], dpv[SM];
+#pragma unroll
+      for (int c = 0; c < SM; c += 32) {
+        tmem_ld_x32(tmem + lane_off + cS + buf * SM + c, reinterpret_cast<uint32_t*>(sv) + c);
+        if (kWantDk) tmem_ld_x32(tmem + lane_off + cDP + buf * SM + c, reinterpret_cast<uint32_t*>(dpv) + c);
+      }
       tc_wait_ld();
       const TileInfo ti = qt_info[it.m];
       const bool tile_full = (n * kBlockN >= ti.max_lo) && ((n + 1) * kBlockN <= ti.min_hi);
-      uint32_t pp[32], pd[32];
+      uint32_t pp[SM / 2], pd[SM / 2];
 #pragma unroll
-      for (int c = 0; c < 64; c += 4) {
+      for (int c = 0; c < SM; c += 4) {
         const float4 l4 = *reinterpret_cast<const float4*>(&s.lse2[buf][c]);
-        const float4 d4 = *reinterpret_cast<const float4*>(&s.delta[buf][c]);
         const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
-        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
         float pv[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) pv[e] = ex2_approx(fmaf(sv[c + e], c_log2, -ls[e]));
@@ -516,13 +557,22 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
           for (int e = 0; e < 4; ++e) pv[e] = (key >= los[e] && key < his[e]) ? pv[e] : 0.f;
         }
-        pp[(c >> 1)] = Pack2<T>::pack(pv[0], pv[1]);
-        pp[(c >> 1) + 1] = Pack2<T>::pack(pv[2], pv[3]);
-        pd[(c >> 1)] = Pack2<T>::pack(pv[0] * (dpv[c] - dl[0]), pv[1] * (dpv[c + 1] - dl[1]));
-        pd[(c >> 1) + 1] = Pack2<T>::pack(pv[2] * (dpv[c + 2] - dl[2]), pv[3] * (dpv[c + 3] - dl[3]));
+        if (kWantDv) {
+          pp[(c >> 1)] = Pack2<T>::pack(pv[0], pv[1]);
+          pp[(c >> 1) + 1] = Pack2<T>::pack(pv[2], pv[3]);
+        }
+        if (kWantDk) {
+          const float4 d4 = *reinterpret_cast<const float4*>(&s.delta[buf][c]);
+          pd[(c >> 1)] = Pack2<T>::pack(pv[0] * (dpv[c] - d4.x), pv[1] * (dpv[c + 1] - d4.y));
+          pd[(c >> 1) + 1] = Pack2<T>::pack(pv[2] * (dpv[c + 2] - d4.z), pv[3] * (dpv[c + 3] - d4.w));
+        }
       }
-      tmem_st_x32(tmem + lane_off + cS + buf * 64, pp);
-      tmem_st_x32(tmem + lane_off + cDP + buf * 64, pd);
+      if (kWantDv) {
+        if (SM == 64) tmem_st_x32(tmem + lane_off + cS + buf * SM, pp); else tmem_st_x16(tmem + lane_off + cS + buf * SM, pp);
+      }
+      if (kWantDk) {
+        if (SM == 64) tmem_st_x32(tmem + lane_off + cDP + buf * SM, pd); else tmem_st_x16(tmem + lane_off + cDP + buf * SM, pd);
+      }
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&s.pds_full[buf]);
@@ -539,6 +589,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       T* dv_row = reinterpret_cast<T*>(p.dv) + (((size_t)b * p.Lk + (live ? key : 0)) * p.Hkv + kvh) * p.V;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
+        if ((which == 0 && !kWantDk) || (which == 1 && !kWantDv)) continue;
         const int width = which == 0 ? p.D : p.V;
         const int pad = which == 0 ? d_pad : v_pad;
         const float mul = which == 0 ? p.scale : 1.f;
@@ -571,26 +622,27 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
   } else if (warp == 4 && lane == 0 && any_work) {
     // ------------------------------ MMA issuer ------------------------------
-    const uint32_t idesc_st = make_idesc(kBlockN, kSubM, kFormat, 0, 0);
+    const uint32_t idesc_st = make_idesc(kBlockN, SM, kFormat, 0, 0);
     const uint32_t idesc_dv = make_idesc(kBlockN, v_pad, kFormat, 0, 1);
     const uint32_t idesc_dk = make_idesc(kBlockN, d_pad, kFormat, 0, 1);
     const uint32_t ka = smem_u32(s.k), va = smem_u32(s.v);
     auto issue_st = [&](int stage, int buf) {
       const uint32_t qa = smem_u32(s.q[stage]), da = smem_u32(s.d_o[stage]);
       for (int js = 0; js < ksteps_qk; ++js) {
-        umma_ss(tmem + cS + buf * 64, make_smem_desc(ka + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024),
+        umma_ss(tmem + cS + buf * SM, make_smem_desc(ka + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024),
                 make_smem_desc(qa + (js >> 2) * kQBox + (js & 3) * 32, 16, 1024), idesc_st, js > 0);
       }
-      for (int js = 0; js < ksteps_v; ++js) {
-        umma_ss(tmem + cDP + buf * 64, make_smem_desc(va + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024),
-                make_smem_desc(da + (js >> 2) * kQBox + (js & 3) * 32, 16, 1024), idesc_st, js > 0);
+      if (kWantDk) {
+        for (int js = 0; js < ksteps_v; ++js) {
+          umma_ss(tmem + cDP + buf * SM, make_smem_desc(va + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024),
+                  make_smem_desc(da + (js >> 2) * kQBox + (js & 3) * 32, 16, 1024), idesc_st, js > 0);
+        }
       }
       umma_commit(&s.sdp_full[buf]);
     };
     bool ok = mbar_wait(ctx, &s.kv_full, 0, 90);
-    // how many items in total (cheap: same enumeration)
-    DkvIter it = it0;
-    DkvIter ahead = it0;      // item whose S^T / dP^T is issued next
+    Iter it = it0;
+    Iter ahead = it0;      // item whose S^T / dP^T is issued next
     int issued = 0, cnt = 0;
     // prologue: S^T / dP^T of the first two items
     for (int k2 = 0; k2 < 2 && ok && ahead.valid(); ++k2) {
@@ -606,15 +658,19 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (!ok) break;
       tc_fence_after();
       const uint32_t qa = smem_u32(s.q[st]), da = smem_u32(s.d_o[st]);
+      if (kWantDv) {
 #pragma unroll
-      for (int js = 0; js < kSubM / 16; ++js) {
-        umma_ts(tmem + cDV, tmem + cS + buf * 64 + js * 8, make_smem_desc(da + js * 2048, kQBox, 1024), idesc_dv,
-                (cnt > 0 || js > 0) ? 1u : 0u);
+        for (int js = 0; js < SM / 16; ++js) {
+          umma_ts(tmem + cDV, tmem + cS + buf * SM + js * 8, make_smem_desc(da + js * 2048, kQBox, 1024), idesc_dv,
+                  (cnt > 0 || js > 0) ? 1u : 0u);
+        }
       }
+      if (kWantDk) {
 #pragma unroll
-      for (int js = 0; js < kSubM / 16; ++js) {
-        umma_ts(tmem + cDK, tmem + cDP + buf * 64 + js * 8, make_smem_desc(qa + js * 2048, kQBox, 1024), idesc_dk,
-                (cnt > 0 || js > 0) ? 1u : 0u);
+        for (int js = 0; js < SM / 16; ++js) {
+          umma_ts(tmem + cDK, tmem + cDP + buf * SM + js * 8, make_smem_desc(qa + js * 2048, kQBox, 1024), idesc_dk,
+                  (cnt > 0 || js > 0) ? 1u : 0u);
+        }
       }
       umma_commit(&s.q_empty[st]);
       it.next();
@@ -631,17 +687,19 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   } else if (warp == 5 && lane == 0 && any_work) {
     // ------------------------------ TMA producer ------------------------------
     tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_do); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
-    mbar_arrive_expect_tx(&s.kv_full, nbox_qk * kKvBox + nbox_v * kKvBox);
+    mbar_arrive_expect_tx(&s.kv_full, nbox_qk * kKvBox + (kWantDk ? nbox_v * kKvBox : 0));
     for (int bx = 0; bx < nbox_qk; ++bx) tma_load_4d(s.k + bx * kKvBox, &tm_k, &s.kv_full, bx * 64, kvh, n * kBlockN, b);
-    for (int bx = 0; bx < nbox_v; ++bx) tma_load_4d(s.v + bx * kKvBox, &tm_v, &s.kv_full, bx * 64, kvh, n * kBlockN, b);
+    if (kWantDk) {
+      for (int bx = 0; bx < nbox_v; ++bx) tma_load_4d(s.v + bx * kKvBox, &tm_v, &s.kv_full, bx * 64, kvh, n * kBlockN, b);
+    }
     bool ok = true;
     int cnt = 0;
-    for (DkvIter it = it0; it.valid() && ok; it.next(), ++cnt) {
+    for (Iter it = it0; it.valid() && ok; it.next(), ++cnt) {
       const int st = cnt % kStages;
       if (cnt >= kStages) ok = mbar_wait(ctx, &s.q_empty[st], ((cnt / kStages) - 1) & 1, 95);
       if (!ok) break;
       const int h = kvh * G + it.g;
-      const int row0 = it.m * kBlockM + it.half * kSubM;
+      const int row0 = it.row0();
       mbar_arrive_expect_tx(&s.q_full[st], (nbox_qk + nbox_v) * kQBox);
       for (int bx = 0; bx < nbox_qk; ++bx) tma_load_4d(s.q[st] + bx * kQBox, &tm_q, &s.q_full[st], bx * 64, h, row0, b);
       for (int bx = 0; bx < nbox_v; ++bx) tma_load_4d(s.d_o[st] + bx * kQBox, &tm_do, &s.q_full[st], bx * 64, h, row0, b);
@@ -661,7 +719,40 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
-template <typename T, int HD>
+template <typename T, int HD, int BN>
+static int launch_dq(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t stream) {
+  CUtensorMap tdo, tk, tv;
+  if (make_tile_map(&tdo, a.dy, a.dtype, a.batch, a.q_len, a.q_heads, a.v_dim, a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], kBlockM)) return XATTN_E_INVALID;
+  if (make_tile_map(&tk, a.k, a.dtype, a.batch, a.k_len, a.kv_heads, a.qk_dim, a.k_strides[0], a.k_strides[1], a.k_strides[2], BN)) return XATTN_E_INVALID;
+  if (make_tile_map(&tv, a.v, a.dtype, a.batch, a.k_len, a.kv_heads, a.v_dim, a.v_strides[0], a.v_strides[1], a.v_strides[2], BN)) return XATTN_E_INVALID;
+  auto kern = bwd_dq_kernel<T, HD, BN>;
+  const size_t smem = sizeof(DqSmem<HD, BN>) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { set_error("cudaFuncSetAttribute(dq): %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
+  const long long grid = (long long)p.nQT * p.Hq * p.B;
+  if (grid > 0x7fffffffLL) { set_error("dQ grid out of range"); return XATTN_E_INVALID; }
+  kern<<<(unsigned)grid, 384, smem, stream>>>(tdo, tk, tv, p);
+  return XATTN_OK;
+}
+
+template <typename T, int HD, int MODE, int SM>
+static int launch_dkv(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t stream) {
+  CUtensorMap tq, tdo, tk, tv;
+  if (make_tile_map(&tq, a.q, a.dtype, a.batch, a.q_len, a.q_heads, a.qk_dim, a.q_strides[0], a.q_strides[1], a.q_strides[2], SM)) return XATTN_E_INVALID;
+  if (make_tile_map(&tdo, a.dy, a.dtype, a.batch, a.q_len, a.q_heads, a.v_dim, a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], SM)) return XATTN_E_INVALID;
+  if (make_tile_map(&tk, a.k, a.dtype, a.batch, a.k_len, a.kv_heads, a.qk_dim, a.k_strides[0], a.k_strides[1], a.k_strides[2], kBlockN)) return XATTN_E_INVALID;
+  if (make_tile_map(&tv, a.v, a.dtype, a.batch, a.k_len, a.kv_heads, a.v_dim, a.v_strides[0], a.v_strides[1], a.v_strides[2], kBlockN)) return XATTN_E_INVALID;
+  auto kern = bwd_dkv_kernel<T, HD, MODE, SM>;
+  const size_t smem = sizeof(DkvSmem<HD, MODE, SM>) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { set_error("cudaFuncSetAttribute(dkv): %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
+  const long long grid = (long long)p.nKT * p.Hkv * p.B;
+  if (grid > 0x7fffffffLL) { set_error("dK/dV grid out of range"); return XATTN_E_INVALID; }
+  kern<<<(unsigned)grid, 256, smem, stream>>>(tq, tdo, tk, tv, p);
+  return XATTN_OK;
+}
+
+template <typename T>
 static int launch_bwd(const XattnBwdArgs& a, BwdParams& p, cudaStream_t stream) {
   // 1. preprocess
   float* delta = a.workspace;
@@ -674,34 +765,21 @@ static int launch_bwd(const XattnBwdArgs& a, BwdParams& p, cudaStream_t stream) 
         reinterpret_cast<const T*>(a.dy), reinterpret_cast<const T*>(a.y), a.lse, p.B, p.Lq, p.Hq, p.V,
         a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], a.y_strides[0], a.y_strides[1], a.y_strides[2], delta, lse2);
   }
-  CUtensorMap tq64, tdo64, tdo128, tk, tv;
-  if (make_tile_map(&tq64, a.q, a.dtype, a.batch, a.q_len, a.q_heads, a.qk_dim, a.q_strides[0], a.q_strides[1], a.q_strides[2], kSubM)) return XATTN_E_INVALID;
-  if (make_tile_map(&tdo64, a.dy, a.dtype, a.batch, a.q_len, a.q_heads, a.v_dim, a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], kSubM)) return XATTN_E_INVALID;
-  if (make_tile_map(&tdo128, a.dy, a.dtype, a.batch, a.q_len, a.q_heads, a.v_dim, a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], kBlockM)) return XATTN_E_INVALID;
-  if (make_tile_map(&tk, a.k, a.dtype, a.batch, a.k_len, a.kv_heads, a.qk_dim, a.k_strides[0], a.k_strides[1], a.k_strides[2], kBlockN)) return XATTN_E_INVALID;
-  if (make_tile_map(&tv, a.v, a.dtype, a.batch, a.k_len, a.kv_heads, a.v_dim, a.v_strides[0], a.v_strides[1], a.v_strides[2], kBlockN)) return XATTN_E_INVALID;
-  cudaError_t e;
-  // 2. dQ
-  {
-    auto kern = bwd_dq_kernel<T, HD>;
-    const size_t smem = sizeof(DqSmem<HD>) + 1024;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) { set_error("cudaFuncSetAttribute(dq): %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
-    const long long grid = (long long)p.nQT * p.Hq * p.B;
-    if (grid > 0x7fffffffLL) { set_error("dQ grid out of range"); return XATTN_E_INVALID; }
-    kern<<<(unsigned)grid, 384, smem, stream>>>(tdo128, tk, tv, p);
+  const int hd = p.D > p.V ? p.D : p.V;
+  int rc;
+  // 2. dQ   3. dK / dV
+  if (hd <= 64) {
+    if ((rc = launch_dq<T, 64, 128>(a, p, stream))) return rc;
+    if ((rc = launch_dkv<T, 64, kDkvBoth, 64>(a, p, stream))) return rc;
+  } else if (hd <= 128) {
+    if ((rc = launch_dq<T, 128, 128>(a, p, stream))) return rc;
+    if ((rc = launch_dkv<T, 128, kDkvBoth, 64>(a, p, stream))) return rc;
+  } else {
+    if ((rc = launch_dq<T, 256, 64>(a, p, stream))) return rc;
+    if ((rc = launch_dkv<T, 256, kDvOnly, 64>(a, p, stream))) return rc;
+    if ((rc = launch_dkv<T, 256, kDkOnly, 32>(a, p, stream))) return rc;
   }
-  // 3. dK / dV
-  {
-    auto kern = bwd_dkv_kernel<T, HD>;
-    const size_t smem = sizeof(DkvSmem<HD>) + 1024;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) { set_error("cudaFuncSetAttribute(dkv): %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
-    const long long grid = (long long)p.nKT * p.Hkv * p.B;
-    if (grid > 0x7fffffffLL) { set_error("dK/dV grid out of range"); return XATTN_E_INVALID; }
-    kern<<<(unsigned)grid, 256, smem, stream>>>(tq64, tdo64, tk, tv, p);
-  }
-  e = cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("backward launch: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
   return XATTN_OK;
 }
@@ -723,8 +801,6 @@ int bwd_entry(const XattnBwdArgs* a, cudaStream_t stream) {
   for (const int64_t* st : {a->q_strides, a->y_strides, a->dy_strides}) {
     for (int i = 0; i < 3; ++i) if (st[i] % 8) { set_error("q / y / dy strides must be multiples of 8 elements"); return XATTN_E_INVALID; }
   }
-  const int hd = (int)(a->qk_dim > a->v_dim ? a->qk_dim : a->v_dim);
-  if (hd > 128) { set_error("backward supports head dimensions up to 128 in this build"); return XATTN_E_UNSUPPORTED; }
   BwdParams p;
   p.B = (int)a->batch; p.Lq = (int)a->q_len; p.Lk = (int)a->k_len; p.Hq = (int)a->q_heads; p.Hkv = (int)a->kv_heads;
   p.D = (int)a->qk_dim; p.V = (int)a->v_dim;
@@ -736,10 +812,8 @@ int bwd_entry(const XattnBwdArgs* a, cudaStream_t stream) {
   p.k_tiles = reinterpret_cast<const KeyTileInfo*>(a->plan + pl.off_kt);
   p.q = a->q; p.q_sb = a->q_strides[0]; p.q_sl = a->q_strides[1]; p.q_sh = a->q_strides[2];
   p.dq = a->dq; p.dk = a->dk; p.dv = a->dv; p.status = a->status;
-  if (a->dtype == XATTN_DTYPE_BF16) {
-    return hd <= 64 ? launch_bwd<__nv_bfloat16, 64>(*a, p, stream) : launch_bwd<__nv_bfloat16, 128>(*a, p, stream);
-  }
-  return hd <= 64 ? launch_bwd<__half, 64>(*a, p, stream) : launch_bwd<__half, 128>(*a, p, stream);
+  if (a->dtype == XATTN_DTYPE_BF16) return launch_bwd<__nv_bfloat16>(*a, p, stream);
+  return launch_bwd<__half>(*a, p, stream);
 }
 
 }  // namespace xb
