@@ -1,0 +1,348 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME]
+
+One step = forward + backward of one batch through the public ops.  The default workload is the
+headline configuration: causal attention, bf16, GQA, B=4, S=8192, Hq=32, Hkv=8, D=128, every
+sequence packed with segments of length ~U[512, 4096] given as int64 segment ids, level 0.
+Inputs are seeded synthetic N(0,1) tensors.  Rank 0 prints ONE JSON line.
+
+* ``value``     throughput with inputs resident in HBM (CUDA events, max over ranks), in TFLOP/s of
+                algorithmic work: 14 * D * (visible query-key pairs over query heads).
+* ``e2e``       the same through the public ops with HOST buffers: every step copies q, k, v, dy
+                from pinned memory and copies y, dq, dk, dv back, inside the timed region.
+* ``roofline``  the dominant kernel's algorithmic FLOP/s from per-launch CUDA events, against the
+                measured dense bf16 peak of MEASURED_PEAKS.json.
+* ``cpu_baseline`` the CPU oracle timed on the host cores (rank 0, N=1 only), on the reference's own
+                CPU-sized configuration.
+
+With N > 1 (torchrun, one rank per GPU) every rank runs its own batch: batch x heads shard with no
+communication, so scaling is weak.  ``--impl reference`` times the CPU oracle on a bounded slice of
+the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "attn fwd+bwd TFLOPS (bf16 causal S=8K D=128), whole job"
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+
+WORKLOADS = {
+    # name: (B, S, Hq, Hkv, D, packed segments?, description)
+    "causal_c2": dict(B=4, S=8192, Hq=32, Hkv=8, D=128, segments=True,
+                      text="configs[1]: causal fwd+bwd bf16 GQA B=4 S=8192 Hq=32 Hkv=8 D=128, packed segments ~U[512,4096], level 0"),
+    "causal_small": dict(B=1, S=8192, Hq=32, Hkv=8, D=128, segments=False,
+                         text="profiling case: dense causal B=1 S=8192 Hq=32 Hkv=8 D=128 (0.24 GB of tensors, above L2)"),
+    "causal_c2_dense": dict(B=4, S=8192, Hq=32, Hkv=8, D=128, segments=False,
+                            text="configs[1] shape with one segment per sequence (dense causal)"),
+}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return json.load(f), "measured"
+    except (OSError, ValueError):
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+def make_host_inputs(w, seed):
+    """q, k, v, dy as bf16 host tensors drawn N(0,1) in fp32 from a seeded generator; int64 segment ids."""
+    g = torch.Generator().manual_seed(seed)
+    B, S, Hq, Hkv, D = w["B"], w["S"], w["Hq"], w["Hkv"], w["D"]
+    draw = lambda *shape: torch.randn(shape, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    q, k, v, dy = draw(B, S, Hq, D), draw(B, S, Hkv, D), draw(B, S, Hkv, D), draw(B, S, Hq, D)
+    ids = None
+    if w["segments"]:
+        ids = torch.zeros(B, S, dtype=torch.int64)
+        for b in range(B):
+            pos, seg = 0, 0
+            while pos < S:
+                length = int(torch.randint(512, 4097, (1,), generator=g))
+                ids[b, pos:pos + length] = seg
+                pos += length
+                seg += 1
+    return q, k, v, dy, ids
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_event = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self._stop_event.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def stop(self):
+        self._stop_event.set()
+        self.join(timeout=2)
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+def cpu_oracle_step(q, k, v, dy, ids):
+    """One forward + backward of the CPU oracle in fp32 on the given slice; returns seconds."""
+    from oracle import attention_oracle as O
+    t0 = time.perf_counter()
+    O.forward_backward(q, k, v, dy, visibility="full", q_segment_idx=ids, k_segment_idx=ids)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline_config0(threads):
+    """The reference's CPU-sized configuration (configs[0]): B=2, S=1024, Hq=Hkv=8, D=64, fp32."""
+    from oracle import attention_oracle as O
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    B, S, H, D = 2, 1024, 8, 64
+    q, k, v, dy = (torch.randn(B, S, H, D, generator=g) for _ in range(4))
+    times = [cpu_oracle_step(q, k, v, dy, None) for _ in range(3)]
+    pairs = B * H * S * (S + 1) // 2
+    flops = 14 * D * pairs
+    t = statistics.median(times)
+    return {"value": flops / t * 1e-12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": "configs[0] in full (B=2 S=1024 Hq=Hkv=8 D=64 fp32 fwd+bwd), median of 3, "
+                      f"{t:.3f} s per step"}
+
+
+def run_reference(args, w):
+    """CPU arm: the oracle (a port of the reference's tests/_reference.py path) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import attention_oracle as O
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    q, k, v, dy, ids = make_host_inputs(w, seed=1)
+    # bounded sample: batch row 0, query head 0 (with its KV head), full sequence
+    qs, ks, vs, dys = (t[:1, :, :1].float() for t in (q, k, v, dy))
+    ids_s = None if ids is None else ids[:1]
+    lo, hi = O.row_intervals(w["S"], w["S"], 1, "full", None, ids_s, ids_s)
+    flops = 14 * w["D"] * O.visible_pairs(lo, hi)
+    for _ in range(min(args.warmup, 1)):
+        cpu_oracle_step(qs, ks, vs, dys, ids_s)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_oracle_step(qs, ks, vs, dys, ids_s)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = flops / dt * 1e-12
+    sample = "one step = batch row 0, query head 0 of the workload (1/128 of a full step), fp32 torch on the host"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["text"], "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_ours(args, w):
+    import torch.distributed as dist
+    import xattn_b200 as xattn
+    from xattn_b200 import _native
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    host = make_host_inputs(w, seed=1 + rank)
+    pinned = [None if t is None else t.pin_memory() for t in host]
+    q, k, v, dy, ids = (None if t is None else t.to(dev) for t in pinned)
+    meta = {} if ids is None else {"segment_idx": ids}
+    D = w["D"]
+
+    # algorithmic work of one step on this rank: 14 * D * visible pairs over query heads
+    plan = _native.build_plan(w["B"], w["S"], w["S"], dev, q_segment_idx=ids, k_segment_idx=ids)
+    n = w["B"] * w["S"]
+    r4 = (n + 3) // 4 * 4
+    pairs = int((plan[r4:r4 + n].long() - plan[:n].long()).clamp_min(0).sum().item()) * w["Hq"]
+    flops_step = 14 * D * pairs
+
+    def step():
+        y, lse = xattn.causal_flash_attn_fwd(q, k, v, **meta)
+        return (y, *xattn.causal_flash_attn_bwd(dy, q, k, v, y, lse, **meta))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    _native.check_status()
+
+    # ---- device-resident timing -------------------------------------------------------------
+    sampler = ClockSampler(local)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    _native.profile_enable(True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    _native.profile_enable(False)
+    records = _native.profile_read()
+    ms_total = e0.elapsed_time(e1)
+    _native.check_status()
+
+    # ---- end to end: host buffers in, host buffers out ------------------------------------------
+    out_host = None
+    h2d = sum(t.numel() * t.element_size() for t in pinned[:4])
+
+    def e2e_step():
+        nonlocal out_host
+        dq_, dk_, dv_, ddy_ = (t.to(dev, non_blocking=True) for t in pinned[:4])
+        y_, lse_ = xattn.causal_flash_attn_fwd(dq_, dk_, dv_, **meta)
+        outs = (y_, *xattn.causal_flash_attn_bwd(ddy_, dq_, dk_, dv_, y_, lse_, **meta))
+        if out_host is None:
+            out_host = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+        for dst, src in zip(out_host, outs):
+            dst.copy_(src, non_blocking=True)
+
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 10))
+    for _ in range(0 if args.no_e2e else 2):
+        e2e_step()
+    barrier()
+    f0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    e2e_ms_total = f0.elapsed_time(f1)
+    clocks = sampler.stop()
+    d2h = sum(t.numel() * t.element_size() for t in out_host) if out_host else 0
+
+    times = torch.tensor([ms_total / args.steps, e2e_ms_total / max(e2e_steps, 1)], dtype=torch.float64, device=dev)
+    work = torch.tensor([float(flops_step)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(work, op=dist.ReduceOp.SUM)
+    ms_step, e2e_ms_step = float(times[0]), float(times[1])
+    total_flops = float(work[0])
+
+    if rank == 0:
+        peaks, peak_src = measured_peaks()
+        per_kind = {}
+        for kind, ms in records:
+            per_kind.setdefault(kind, []).append(ms)
+        launches = len(records)  # plan scopes hold three small kernels each
+        launches += 2 * len(per_kind.get("plan", []))
+        # algorithmic FLOPs per launch: forward 4*D*P; in the backward the dQ kernel's S / dP
+        # products repeat the dK/dV kernel's, so only its dQ product is new work
+        algo = {"fwd": 4 * D * pairs, "bwd_dq": 2 * D * pairs, "bwd_dkv": 8 * D * pairs}
+        executed = {"fwd": 4 * D * pairs, "bwd_dq": 6 * D * pairs, "bwd_dkv": 8 * D * pairs}
+        kernels = {}
+        for kind, vals in per_kind.items():
+            avg = sum(vals) / len(vals)
+            entry = {"launches": len(vals), "avg_ms": avg, "share": sum(vals) / max(ms_total, 1e-9)}
+            if kind in algo:
+                entry["algorithmic_tflops"] = algo[kind] / avg * 1e-9
+                entry["executed_tflops"] = executed[kind] / avg * 1e-9
+            kernels[kind] = entry
+        dominant = max((kd for kd in kernels if kd in algo), key=lambda kd: kernels[kd]["avg_ms"] * kernels[kd]["launches"])
+        peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
+        achieved = kernels[dominant]["algorithmic_tflops"]
+        line = {
+            "metric": METRIC, "value": total_flops / ms_step * 1e-9, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["text"], "l2": "inputs (0.67 GB per step) exceed the 126 MB L2",
+                       "visible_pairs_per_step": pairs, "flops_per_step": flops_step,
+                       "parallelism": f"batch x heads sharded over {world} GPU(s), no communication"},
+            "per_gpu_tflops": total_flops / ms_step * 1e-9 / world,
+            "frac_of_measured_bf16_peak": {
+                "burst": total_flops / ms_step * 1e-9 / world / float(peaks.get("bf16_tflops", peak)),
+                "sustained": total_flops / ms_step * 1e-9 / world / peak, "source": peak_src},
+            "e2e": None if not e2e_steps else {
+                "value": total_flops / e2e_ms_step * 1e-9, "unit": "TFLOP/s", "ms_per_step": e2e_ms_step,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": f"{peak_src} bf16_tflops_sustained (kernel timed inside a long step)",
+                         "executed_tflops": kernels[dominant]["executed_tflops"]},
+            "kernels": kernels,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_config0(os.cpu_count() or 1)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--workload", default="causal_c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w)
+    else:
+        run_ours(args, w)
+
+
+if __name__ == "__main__":
+    main()

@@ -214,6 +214,15 @@ typedef struct {
 
 int xattn_b200_zero_constant_key_rows(const XattnConstantKeyArgs* args, xattn_stream_t stream);
 
+/* Per-kernel timing for benchmarks (no counterpart in the reference, whose benchmark tool times
+ * whole ops from Python, tests/_benchmark.py:22-35).  While enabled, every entry point brackets
+ * its kernels with CUDA events on the launch stream.  xattn_b200_profile_read() synchronises
+ * those events, writes (kind, milliseconds) pairs and clears the log; it returns the number of
+ * records written.  Kinds: 1 plan, 2 forward, 3 backward preprocess, 4 backward dQ,
+ * 5 backward dK/dV, 6 SoftDelta gate, 7 constant-key repair. */
+int xattn_b200_profile_enable(int enable);
+int xattn_b200_profile_read(int* kinds, float* ms, int capacity);
+
 /* Reads `status` back (synchronises the stream).  0 when the word is zero. */
 int xattn_b200_check_status(const int32_t* status, xattn_stream_t stream);
 

@@ -104,6 +104,8 @@ SYMBOLS = {
     "xattn_b200_softdelta_gate_fwd": (C.c_int, [C.POINTER(GateArgs), C.c_void_p]),
     "xattn_b200_softdelta_gate_bwd": (C.c_int, [C.POINTER(GateArgs), C.c_void_p]),
     "xattn_b200_zero_constant_key_rows": (C.c_int, [C.POINTER(ConstantKeyArgs), C.c_void_p]),
+    "xattn_b200_profile_enable": (C.c_int, [C.c_int]),
+    "xattn_b200_profile_read": (C.c_int, [C.POINTER(C.c_int), C.POINTER(C.c_float), C.c_int]),
     "xattn_b200_check_status": (C.c_int, [C.c_void_p, C.c_void_p]),
 }
 

@@ -320,3 +320,19 @@ def softdelta_gate_bwd(dy: Tensor, y: Tensor, neg_read: Tensor, g: Tensor) -> Tu
     with torch.cuda.device(y.device):
         _lib.check(lib.xattn_b200_softdelta_gate_bwd(C.byref(args), _stream_ptr()), "xattn_b200_softdelta_gate_bwd")
     return read, dneg, dg
+
+
+PROFILE_KINDS = {1: "plan", 2: "fwd", 3: "bwd_pre", 4: "bwd_dq", 5: "bwd_dkv", 6: "gate", 7: "repair"}
+
+
+def profile_enable(enable: bool) -> None:
+    """Bracket every kernel launched by the library with CUDA events (for benchmarks)."""
+    _lib.load().xattn_b200_profile_enable(int(bool(enable)))
+
+
+def profile_read(capacity: int = 65536):
+    """[(kind name, milliseconds)] of the launches since the last read; synchronises their events."""
+    kinds = (C.c_int * capacity)()
+    ms = (C.c_float * capacity)()
+    n = _lib.load().xattn_b200_profile_read(kinds, ms, capacity)
+    return [(PROFILE_KINDS.get(kinds[i], str(kinds[i])), float(ms[i])) for i in range(max(n, 0))]

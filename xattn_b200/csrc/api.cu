@@ -56,6 +56,13 @@ int xattn_b200_zero_constant_key_rows(const XattnConstantKeyArgs* args, xattn_st
   return xb::zero_constant_entry(args, static_cast<cudaStream_t>(stream));
 }
 
+int xattn_b200_profile_enable(int enable) { return xb::profile_enable(enable); }
+
+int xattn_b200_profile_read(int* kinds, float* ms, int capacity) {
+  if (!kinds || !ms || capacity < 0) return XATTN_E_INVALID;
+  return xb::profile_read(kinds, ms, capacity);
+}
+
 int xattn_b200_check_status(const int32_t* status, xattn_stream_t stream) {
   int32_t host = 0;
   cudaError_t e = cudaMemcpyAsync(&host, status, sizeof(host), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));

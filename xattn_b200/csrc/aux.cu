@@ -212,6 +212,7 @@ static void launch_gate_bwd(const XattnGateArgs* a, cudaStream_t s) {
 int gate_fwd_entry(const XattnGateArgs* a, cudaStream_t s) {
   if (int rc = check_gate(a)) return rc;
   if (!a->read) { set_error("null read pointer"); return XATTN_E_INVALID; }
+  ProfileScope prof(kProfGate, s);
   if (a->dtype == XATTN_DTYPE_BF16) launch_gate_fwd<__nv_bfloat16>(a, s); else launch_gate_fwd<__half>(a, s);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("gate forward launch: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
@@ -221,6 +222,7 @@ int gate_fwd_entry(const XattnGateArgs* a, cudaStream_t s) {
 int gate_bwd_entry(const XattnGateArgs* a, cudaStream_t s) {
   if (int rc = check_gate(a)) return rc;
   if (!a->dy || !a->read || !a->dneg_read || !a->dg) { set_error("null gradient pointer"); return XATTN_E_INVALID; }
+  ProfileScope prof(kProfGate, s);
   if (a->dtype == XATTN_DTYPE_BF16) launch_gate_bwd<__nv_bfloat16>(a, s); else launch_gate_bwd<__half>(a, s);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("gate backward launch: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
@@ -233,6 +235,7 @@ int zero_constant_entry(const XattnConstantKeyArgs* a, cudaStream_t s) {
   const int B = (int)a->batch, Lq = (int)a->q_len, Lk = (int)a->k_len, Hq = (int)a->q_heads, Hkv = (int)a->kv_heads, D = (int)a->qk_dim;
   if (B <= 0 || Lq <= 0 || Lk <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || D % 8 || D > 256) { set_error("bad sizes"); return XATTN_E_INVALID; }
   const PlanLayout pl(B, Lq, Lk);
+  ProfileScope prof(kProfRepair, s);
   int* flags = a->workspace;
   {
     const long long warps = (long long)B * Hkv * Lk;

@@ -731,7 +731,10 @@ static int launch_dq(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t str
   if (e != cudaSuccess) { set_error("cudaFuncSetAttribute(dq): %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
   const long long grid = (long long)p.nQT * p.Hq * p.B;
   if (grid > 0x7fffffffLL) { set_error("dQ grid out of range"); return XATTN_E_INVALID; }
-  kern<<<(unsigned)grid, 384, smem, stream>>>(tdo, tk, tv, p);
+  {
+    ProfileScope prof(kProfBwdDq, stream);
+    kern<<<(unsigned)grid, 384, smem, stream>>>(tdo, tk, tv, p);
+  }
   return XATTN_OK;
 }
 
@@ -748,7 +751,10 @@ static int launch_dkv(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t st
   if (e != cudaSuccess) { set_error("cudaFuncSetAttribute(dkv): %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
   const long long grid = (long long)p.nKT * p.Hkv * p.B;
   if (grid > 0x7fffffffLL) { set_error("dK/dV grid out of range"); return XATTN_E_INVALID; }
-  kern<<<(unsigned)grid, 256, smem, stream>>>(tq, tdo, tk, tv, p);
+  {
+    ProfileScope prof(kProfBwdDkv, stream);
+    kern<<<(unsigned)grid, 256, smem, stream>>>(tq, tdo, tk, tv, p);
+  }
   return XATTN_OK;
 }
 
@@ -761,6 +767,7 @@ static int launch_bwd(const XattnBwdArgs& a, BwdParams& p, cudaStream_t stream) 
   {
     const long long warps = (long long)p.B * p.Lq * p.Hq;
     const long long blocks = (warps * 32 + 255) / 256;
+    ProfileScope prof(kProfBwdPre, stream);
     bwd_pre_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
         reinterpret_cast<const T*>(a.dy), reinterpret_cast<const T*>(a.y), a.lse, p.B, p.Lq, p.Hq, p.V,
         a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], a.y_strides[0], a.y_strides[1], a.y_strides[2], delta, lse2);

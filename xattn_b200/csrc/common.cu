@@ -2,6 +2,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
+#include <vector>
 #include "common.cuh"
 
 namespace xb {
@@ -54,6 +55,61 @@ int make_tile_map(CUtensorMap* out, const void* base, int dtype, int64_t B, int6
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with code %d", (int)r); return -1; }
   return 0;
+}
+
+// ---- optional per-kernel timing -------------------------------------------------
+namespace {
+struct ProfRecord { int kind; cudaEvent_t start, stop; };
+std::mutex g_prof_mutex;
+std::vector<ProfRecord> g_prof_records;
+std::vector<cudaEvent_t> g_prof_pool;
+bool g_prof_on = false;
+cudaEvent_t prof_event() {
+  if (!g_prof_pool.empty()) { cudaEvent_t e = g_prof_pool.back(); g_prof_pool.pop_back(); return e; }
+  cudaEvent_t e = nullptr;
+  cudaEventCreate(&e);
+  return e;
+}
+}  // namespace
+
+ProfileScope::ProfileScope(int kind, cudaStream_t st) : slot(-1), stream(st) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  if (!g_prof_on) return;
+  ProfRecord r{kind, prof_event(), prof_event()};
+  if (!r.start || !r.stop) return;
+  cudaEventRecord(r.start, stream);
+  g_prof_records.push_back(r);
+  slot = (int)g_prof_records.size() - 1;
+}
+
+ProfileScope::~ProfileScope() {
+  if (slot < 0) return;
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  if (slot < (int)g_prof_records.size()) cudaEventRecord(g_prof_records[slot].stop, stream);
+}
+
+int profile_enable(int enable) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  g_prof_on = enable != 0;
+  return 0;
+}
+
+int profile_read(int* kinds, float* ms, int capacity) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  int n = 0;
+  for (const ProfRecord& r : g_prof_records) {
+    float t = 0.f;
+    if (cudaEventSynchronize(r.stop) == cudaSuccess && cudaEventElapsedTime(&t, r.start, r.stop) == cudaSuccess &&
+        n < capacity) {
+      kinds[n] = r.kind;
+      ms[n] = t;
+      ++n;
+    }
+    g_prof_pool.push_back(r.start);
+    g_prof_pool.push_back(r.stop);
+  }
+  g_prof_records.clear();
+  return n;
 }
 
 }  // namespace xb

@@ -64,4 +64,18 @@ int make_tile_map(CUtensorMap* out, const void* base, int dtype, int64_t B, int6
 // Last error text of this thread (set by the host entry points).
 void set_error(const char* fmt, ...);
 
+// Optional per-kernel timing: when enabled, a ProfileScope brackets the launches made
+// inside it with CUDA events on the launch stream.
+enum ProfileKind : int {
+  kProfPlan = 1, kProfFwd = 2, kProfBwdPre = 3, kProfBwdDq = 4, kProfBwdDkv = 5, kProfGate = 6, kProfRepair = 7,
+};
+struct ProfileScope {
+  ProfileScope(int kind, cudaStream_t stream);
+  ~ProfileScope();
+  int slot;
+  cudaStream_t stream;
+};
+int profile_enable(int enable);
+int profile_read(int* kinds, float* ms, int capacity);
+
 }  // namespace xb

@@ -486,7 +486,10 @@ static int launch_fwd(const XattnFwdArgs& a, const FwdParams& p, cudaStream_t st
   const int n_groups = (p.nQT + NT - 1) / NT;
   const long long grid = (long long)n_groups * p.Hq * p.B;
   if (grid <= 0 || grid > 0x7fffffffLL) { set_error("forward grid out of range"); return XATTN_E_INVALID; }
-  kern<<<(unsigned)grid, 512, smem, stream>>>(tq, tk, tv, p);
+  {
+    ProfileScope prof(kProfFwd, stream);
+    kern<<<(unsigned)grid, 512, smem, stream>>>(tq, tk, tv, p);
+  }
   e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("forward launch: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
   return XATTN_OK;

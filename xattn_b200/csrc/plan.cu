@@ -245,6 +245,7 @@ int build_plan_entry(const XattnPlanArgs* a, cudaStream_t stream) {
   if ((a->q_segment == nullptr) != (a->k_segment == nullptr)) { set_error("q_segment and k_segment must be given together"); return XATTN_E_INVALID; }
   const int B = (int)a->batch, Lq = (int)a->q_len, Lk = (int)a->k_len;
   const PlanLayout pl(B, Lq, Lk);
+  ProfileScope prof(kProfPlan, stream);
   RowArgs r;
   r.B = B; r.Lq = Lq; r.Lk = Lk; r.visibility = a->visibility; r.span = a->span; r.strict = a->strict_past;
   r.reset = a->reset_positions && a->q_segment; r.q_seg = a->q_segment; r.k_seg = a->k_segment;
@@ -269,6 +270,7 @@ int build_varlen_plan_entry(const XattnVarlenPlanArgs* a, cudaStream_t stream) {
       a->num_q_seqs < 1 || a->num_k_seqs < a->num_q_seqs) { set_error("bad varlen sizes"); return XATTN_E_INVALID; }
   if (a->visibility == XATTN_VIS_CHUNK && a->span <= 0) { set_error("chunk_size must be positive"); return XATTN_E_INVALID; }
   const PlanLayout pl(1, a->total_q, a->total_k);
+  ProfileScope prof(kProfPlan, stream);
   VarlenRowArgs r;
   r.total_q = (int)a->total_q; r.total_k = (int)a->total_k; r.nq = (int)a->num_q_seqs; r.nk = (int)a->num_k_seqs;
   r.cu_q = a->cu_seqlens_q; r.cu_k = a->cu_seqlens_k; r.visibility = a->visibility; r.span = a->span; r.strict = a->strict_past;
