@@ -80,6 +80,7 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, 
   }
 }
 
+
 // ---------------------------------------------------------------------------
 // dQ kernel
 // ---------------------------------------------------------------------------
@@ -91,11 +92,14 @@ template <int HD, int BN>
 struct DqSmem {
   static constexpr int kDoBytes = kBlockM * HD * 2;
   static constexpr int kKvBytes = BN * HD * 2;
+  // K is held from S of its key tile until dQ of the same tile, V only for dP: one more K stage
+  // keeps the next S from waiting for a K buffer that dQ has just released
+  static constexpr int kKStages = HD <= 128 ? 3 : 2;
   alignas(1024) uint8_t d_o[kDoBytes];
-  alignas(1024) uint8_t k[2][kKvBytes];
+  alignas(1024) uint8_t k[kKStages][kKvBytes];
   alignas(1024) uint8_t v[2][kKvBytes];
   uint64_t do_full, q_ready;
-  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t k_full[kKStages], k_empty[kKStages], v_full[2], v_empty[2];
   uint64_t sdp_full, sdp_free, ds_full, dq_done;
   uint32_t tmem_base;
   int abort_flag;
@@ -109,6 +113,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
               const __grid_constant__ CUtensorMap tm_v, const BwdParams p) {
   using Smem = DqSmem<HD, BN>;
   constexpr bool kAlias = HD > 128;
+  constexpr int kKStages = Smem::kKStages;
   constexpr int kDoBox = kBlockM * 64 * 2;     // 64-column box of the 128-row dO tile
   constexpr int kKvBox = BN * 64 * 2;          // 64-column box of a BN-row K / V tile
   constexpr int CH = BN / 2;                   // key columns per element-wise thread
@@ -149,14 +154,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
   if (tid == 0) {
     s.abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 2 : 0;
     mbar_init(&s.do_full, 1);
-    mbar_init(&s.q_ready, 256);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s.k_full[i], 1); mbar_init(&s.k_empty[i], 1);
-      mbar_init(&s.v_full[i], 1); mbar_init(&s.v_empty[i], 1);
-    }
+    mbar_init(&s.q_ready, 8);
+    for (int i = 0; i < kKStages; ++i) { mbar_init(&s.k_full[i], 1); mbar_init(&s.k_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&s.v_full[i], 1); mbar_init(&s.v_empty[i], 1); }
     mbar_init(&s.sdp_full, 1);
-    mbar_init(&s.sdp_free, 256);
-    mbar_init(&s.ds_full, 256);
+    mbar_init(&s.sdp_free, 8);
+    mbar_init(&s.ds_full, 8);
     mbar_init(&s.dq_done, 1);
     fence_mbar_init();
   }
@@ -172,6 +175,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
   const int ksteps_qk = (p.D + 15) / 16, ksteps_v = (p.V + 15) / 16;
   const int d_pad = (p.D + 15) & ~15;
 
+  // 384 threads start with 168 registers each; the element-wise warpgroups take the MMA / TMA
+  // warpgroup's share
+  if (warp < 8) setmaxnreg_inc<216>(); else setmaxnreg_dec<40>();
   if (dead) {
   } else if (warp < 8) {
     const int hf = warp >> 2;                 // which half of the key-tile columns
@@ -206,7 +212,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
         }
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(&s.q_ready);
+        mbar_arrive_warp(&s.q_ready);
       }
       int lo = 0, hi = 0;
       float lse2 = INFINITY, delta = 0.f;
@@ -231,19 +237,21 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
         }
         tc_wait_ld();
         tc_fence_before();
-        mbar_arrive(&s.sdp_free);
+        mbar_arrive_warp(&s.sdp_free);
         const bool tile_full = ((n_lo + i) * BN >= full_lo) && ((n_lo + i + 1) * BN <= full_hi);
         const int rl = lo - col0, rh = hi - col0;
         uint32_t pk[CH / 2];
+        const float2 cc = make_float2(c_log2, c_log2), nl = make_float2(-lse2, -lse2);
+        const float2 nd = make_float2(-delta, -delta);
 #pragma unroll
         for (int c = 0; c < CH; c += 2) {
-          float p0 = ex2_approx(fmaf(sv[c], c_log2, -lse2));
-          float p1 = ex2_approx(fmaf(sv[c + 1], c_log2, -lse2));
+          float2 pr = ex2_pair_sfu(fma2(make_float2(sv[c], sv[c + 1]), cc, nl));
           if (!tile_full) {
-            p0 = (c >= rl && c < rh) ? p0 : 0.f;
-            p1 = (c + 1 >= rl && c + 1 < rh) ? p1 : 0.f;
+            pr.x = (c >= rl && c < rh) ? pr.x : 0.f;
+            pr.y = (c + 1 >= rl && c + 1 < rh) ? pr.y : 0.f;
           }
-          pk[c >> 1] = Pack2<T>::pack(p0 * (dpv[c] - delta), p1 * (dpv[c + 1] - delta));
+          const float2 ds = mul2(pr, add2(make_float2(dpv[c], dpv[c + 1]), nd));
+          pk[c >> 1] = Pack2<T>::pack(ds.x, ds.y);
         }
         if (!kAlias && i > 0) {
           ok = mbar_wait(ctx, &s.dq_done, (i - 1) & 1, 51);
@@ -254,7 +262,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
         else tmem_st_x16(tmem + lane_off + cDS + hf * kDsStride, pk);
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(&s.ds_full);
+        mbar_arrive_warp(&s.ds_full);
       }
       if (ok) ok = mbar_wait(ctx, &s.dq_done, (iters - 1) & 1, 52);
       if (ok) {
@@ -286,8 +294,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
     // ------------------------------ MMA issuer ------------------------------
     const uint32_t idesc_s = make_idesc(kBlockM, BN, kFormat, 0, 0);
     const uint32_t idesc_dq = make_idesc(kBlockM, d_pad, kFormat, 0, 1);
-    auto issue_s_dp = [&](int stage) {
-      const uint32_t ka = smem_u32(s.k[stage]), va = smem_u32(s.v[stage]), da = smem_u32(s.d_o);
+    auto issue_s_dp = [&](int i) {
+      const int stage = i & 1;
+      const uint32_t ka = smem_u32(s.k[i % kKStages]), va = smem_u32(s.v[stage]), da = smem_u32(s.d_o);
       for (int js = 0; js < ksteps_qk; ++js) {
         umma_ts(tmem + cS, tmem + cQ + js * 8, make_smem_desc(ka + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024),
                 idesc_s, js > 0);
@@ -300,7 +309,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
       umma_commit(&s.v_empty[stage]);
     };
     auto issue_dq = [&](int i) {
-      const uint32_t ka = smem_u32(s.k[i & 1]);
+      const uint32_t ka = smem_u32(s.k[i % kKStages]);
 #pragma unroll
       for (int js = 0; js < BN / 16; ++js) {
         const uint32_t a_col = cDS + (js / (CH / 16)) * kDsStride + (js % (CH / 16)) * 8;
@@ -308,7 +317,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
                 (i > 0 || js > 0) ? 1u : 0u);
       }
       umma_commit(&s.dq_done);
-      umma_commit(&s.k_empty[i & 1]);
+      umma_commit(&s.k_empty[i % kKStages]);
     };
     bool ok = mbar_wait(ctx, &s.do_full, 0, 60);
     if (ok) ok = mbar_wait(ctx, &s.q_ready, 0, 61);
@@ -325,12 +334,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
       }
       if (i + 1 < iters) {
         const int sn = (i + 1) & 1;
-        ok = mbar_wait(ctx, &s.k_full[sn], ((i + 1) >> 1) & 1, 64);
+        ok = mbar_wait(ctx, &s.k_full[(i + 1) % kKStages], ((i + 1) / kKStages) & 1, 64);
         if (ok) ok = mbar_wait(ctx, &s.v_full[sn], ((i + 1) >> 1) & 1, 65);
         if (ok && !kAlias) ok = mbar_wait(ctx, &s.sdp_free, i & 1, 66);
         if (!ok) break;
         tc_fence_after();
-        issue_s_dp(sn);
+        issue_s_dp(i + 1);
       }
       if (!kAlias) {
         ok = mbar_wait(ctx, &s.ds_full, i & 1, 67);
@@ -347,12 +356,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
       tma_load_4d(s.d_o + bx * kDoBox, &tm_do, &s.do_full, bx * 64, h, qt * kBlockM, b);
     bool ok = true;
     for (int i = 0; i < iters && ok; ++i) {
-      const int st = i & 1, n = n_lo + i;
-      if (i >= 2) ok = mbar_wait(ctx, &s.k_empty[st], ((i >> 1) - 1) & 1, 70);
+      const int st = i & 1, ks = i % kKStages, n = n_lo + i;
+      if (i >= kKStages) ok = mbar_wait(ctx, &s.k_empty[ks], ((i / kKStages) - 1) & 1, 70);
       if (!ok) break;
-      mbar_arrive_expect_tx(&s.k_full[st], nbox_qk * kKvBox);
+      mbar_arrive_expect_tx(&s.k_full[ks], nbox_qk * kKvBox);
       for (int bx = 0; bx < nbox_qk; ++bx)
-        tma_load_4d(s.k[st] + bx * kKvBox, &tm_k, &s.k_full[st], bx * 64, kvh, n * BN, b);
+        tma_load_4d(s.k[ks] + bx * kKvBox, &tm_k, &s.k_full[ks], bx * 64, kvh, n * BN, b);
       if (i >= 2) ok = mbar_wait(ctx, &s.v_empty[st], ((i >> 1) - 1) & 1, 71);
       if (!ok) break;
       mbar_arrive_expect_tx(&s.v_full[st], nbox_v * kKvBox);
@@ -371,6 +380,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
   if (warp == 9) { __syncwarp(); tmem_dealloc(tmem, kTmemCols); }
 }
 
+
 // ---------------------------------------------------------------------------
 // dK / dV kernel
 // ---------------------------------------------------------------------------
@@ -387,16 +397,20 @@ struct DkvSmem {
   alignas(1024) uint8_t v[MODE == kDvOnly ? 1024 : kKvBytes];
   alignas(1024) uint8_t q[kStages][kQBytes];
   alignas(1024) uint8_t d_o[kStages][kQBytes];
-  // per-query scalars of the sub-tile in flight, double-buffered
-  alignas(16) float lse2[2][SM];
-  alignas(16) float delta[2][SM];
-  alignas(16) int lo[2][SM];
-  alignas(16) int hi[2][SM];
+  // per-query scalars (-lse*log2e, -delta, lo, hi) of the sub-tiles in flight: one pair of
+  // buffers per element-wise warpgroup
+  alignas(16) float nlse2[2][2][SM];
+  alignas(16) float ndelta[2][2][SM];
+  alignas(16) int lo[2][2][SM];
+  alignas(16) int hi[2][2][SM];
   uint64_t kv_full;
   uint64_t q_full[kStages], q_empty[kStages];
-  uint64_t sdp_full[2], pds_full[2], scal_full[2], all_done;
+  uint64_t sdp_full[2], pds_full[2], scal_full[2][2], all_done;
   uint32_t tmem_base;
   int abort_flag;
+  // query-tile summaries [m_first, m_first + kTileCache) of this batch row, staged once
+  static constexpr int kTileCache = 256;
+  TileInfo tiles[kTileCache];
 };
 
 // Enumerates the (query head of the group, SM-row query sub-tile) pairs a key
@@ -406,9 +420,15 @@ struct DkvIter {
   static constexpr int kParts = kBlockM / SM;
   int g, m, part;        // head within the group, 128-row query tile, which SM-row part
   int G, m_first, m_end, Lq, k0, k1;
-  const TileInfo* qt;
+  const TileInfo* qt;        // global table of this batch row
+  const TileInfo* cache;     // shared-memory copy of entries [m_first, m_first + cache_n)
+  int cache_n;
+  __device__ __forceinline__ TileInfo tile(int mm) const {
+    const int rel = mm - m_first;
+    return (rel >= 0 && rel < cache_n) ? cache[rel] : qt[mm];
+  }
   __device__ __forceinline__ bool tile_overlaps(int mm) const {
-    const TileInfo t = qt[mm];
+    const TileInfo t = tile(mm);
     return t.max_hi > t.min_lo && t.min_lo < k1 && t.max_hi > k0;
   }
   __device__ __forceinline__ bool valid() const { return g < G; }
@@ -423,8 +443,10 @@ struct DkvIter {
       return;
     }
   }
-  __device__ __forceinline__ void init(int G_, int m_first_, int m_end_, int Lq_, int k0_, const TileInfo* qt_) {
+  __device__ __forceinline__ void init(int G_, int m_first_, int m_end_, int Lq_, int k0_, const TileInfo* qt_,
+                                       const TileInfo* cache_, int cache_n_) {
     G = G_; m_first = m_first_; m_end = m_end_; Lq = Lq_; k0 = k0_; k1 = k0_ + kBlockN; qt = qt_;
+    cache = cache_; cache_n = cache_n_;
     g = (m_end_ > m_first_) ? 0 : G_;
     m = m_first_; part = 0;
     settle();
@@ -432,10 +454,10 @@ struct DkvIter {
   __device__ __forceinline__ void next() { ++part; settle(); }
 };
 
-// warps 0-3: element-wise warpgroup (thread = key row), warp 4: MMA issuer,
-// warp 5: TMA producer + TMEM owner, warps 6-7: idle
+// warps 0-3 / 4-7: element-wise warpgroups (thread = key row); warpgroup w owns TMEM buffer w and
+// takes every other sub-tile.  warp 8: MMA issuer, warp 9: TMA producer + TMEM owner, warps 10-11 idle
 template <typename T, int HD, int MODE, int SM>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(384, 1)
 bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                const BwdParams p) {
@@ -468,12 +490,15 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     mbar_init(&s.kv_full, 1);
     for (int i = 0; i < kStages; ++i) { mbar_init(&s.q_full[i], 1); mbar_init(&s.q_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&s.sdp_full[i], 1); mbar_init(&s.pds_full[i], 128); mbar_init(&s.scal_full[i], 128);
+      mbar_init(&s.sdp_full[i], 1); mbar_init(&s.pds_full[i], 4);
+      mbar_init(&s.scal_full[i][0], 4); mbar_init(&s.scal_full[i][1], 4);
     }
     mbar_init(&s.all_done, 1);
     fence_mbar_init();
   }
-  if (warp == 5) { tmem_alloc(&s.tmem_base, kTmemCols); tmem_relinquish(); }
+  if (warp == 9) { tmem_alloc(&s.tmem_base, kTmemCols); tmem_relinquish(); }
+  const int cache_n = min(max(kti.m_end - kti.m_first, 0), Smem::kTileCache);
+  for (int i = tid; i < cache_n; i += blockDim.x) s.tiles[i] = qt_info[kti.m_first + i];
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -486,141 +511,144 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int d_pad = (p.D + 15) & ~15, v_pad = (p.V + 15) & ~15;
 
   Iter it0;
-  it0.init(G, kti.m_first, kti.m_end, p.Lq, n * kBlockN, qt_info);
+  it0.init(G, kti.m_first, kti.m_end, p.Lq, n * kBlockN, qt_info, s.tiles, cache_n);
   const bool any_work = it0.valid();
 
+  if (warp < 8) setmaxnreg_inc<216>(); else setmaxnreg_dec<40>();
   if (dead) {
-  } else if (warp < 4) {
-    // ------------------------ element-wise warpgroup ------------------------
-    const int r = tid;                        // key row inside the tile
+  } else if (warp < 8) {
+    // ------------------------ element-wise warpgroups ------------------------
+    const int wg = warp >> 2;                 // also the TMEM buffer this warpgroup owns
+    const int wt = tid & 127;
+    const int r = wt;                         // key row inside the tile
     const int key = n * kBlockN + r;
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const float c_log2 = p.scale * 1.4426950408889634f;
+    const float2 cc = make_float2(c_log2, c_log2);
     bool ok = true;
-    // per-query scalars of a sub-tile: thread t < 64 fetches lse2/delta, t >= 64 fetches lo/hi
-    const int sq = tid & 63;
+    // per-query scalars of a sub-tile: thread t < 64 fetches lse2 / delta, t >= 64 fetches lo / hi
+    const int sq = wt & 63;
     auto fetch = [&](const Iter& it, float& f0, float& f1, int& i0, int& i1) {
       const int qrow = it.row0() + sq;
       const int h = kvh * G + it.g;
-      f0 = INFINITY; f1 = 0.f; i0 = 0; i1 = 0;
+      f0 = -INFINITY; f1 = 0.f; i0 = 0; i1 = 0;
       if (sq < SM && qrow < p.Lq) {
-        if (tid < 64) {
-          f0 = p.lse2[((size_t)b * p.Hq + h) * p.Lq + qrow];
-          f1 = p.delta[((size_t)b * p.Hq + h) * p.Lq + qrow];
+        if (wt < 64) {
+          f0 = -p.lse2[((size_t)b * p.Hq + h) * p.Lq + qrow];
+          f1 = -p.delta[((size_t)b * p.Hq + h) * p.Lq + qrow];
         } else {
           i0 = p.row_lo[(size_t)b * p.Lq + qrow];
           i1 = p.row_hi[(size_t)b * p.Lq + qrow];
         }
       }
     };
-    auto stash = [&](int buf, float f0, float f1, int i0, int i1) {
+    auto stash = [&](int sub, float f0, float f1, int i0, int i1) {
       if (sq < SM) {
-        if (tid < 64) { s.lse2[buf][sq] = f0; s.delta[buf][sq] = f1; }
-        else { s.lo[buf][sq] = i0; s.hi[buf][sq] = i1; }
+        if (wt < 64) { s.nlse2[wg][sub][sq] = f0; s.ndelta[wg][sub][sq] = f1; }
+        else { s.lo[wg][sub][sq] = i0; s.hi[wg][sub][sq] = i1; }
       }
-      mbar_arrive(&s.scal_full[buf]);
+      mbar_arrive_warp(&s.scal_full[wg][sub]);
     };
     Iter it = it0;
+    if (wg == 1 && it.valid()) it.next();     // warpgroup 1 starts at the second sub-tile
     float f0, f1; int i0, i1;
     if (it.valid()) { fetch(it, f0, f1, i0, i1); stash(0, f0, f1, i0, i1); }
-    int cnt = 0;
+    int kk = 0;                               // steps taken by this warpgroup
     while (it.valid() && ok) {
-      const int buf = cnt & 1;
+      const int sub = kk & 1;
       Iter nx = it; nx.next();
+      if (nx.valid()) nx.next();                                 // this warpgroup's next sub-tile
       if (nx.valid()) fetch(nx, f0, f1, i0, i1);                 // in flight during this step
-      ok = mbar_wait(ctx, &s.scal_full[buf], (cnt >> 1) & 1, 82);  // scalars of this step are in shared memory
-      if (ok) ok = mbar_wait(ctx, &s.sdp_full[buf], (cnt >> 1) & 1, 80);
+      ok = mbar_wait(ctx, &s.scal_full[wg][sub], (kk >> 1) & 1, 82);  // scalars of this step are in shared memory
+      if (ok) ok = mbar_wait(ctx, &s.sdp_full[wg], kk & 1, 80);
       if (!ok) break;
       tc_fence_after();
       float sv[SM], dpv[SM];
 #pragma unroll
       for (int c = 0; c < SM; c += 32) {
-        tmem_ld_x32(tmem + lane_off + cS + buf * SM + c, reinterpret_cast<uint32_t*>(sv) + c);
-        if (kWantDk) tmem_ld_x32(tmem + lane_off + cDP + buf * SM + c, reinterpret_cast<uint32_t*>(dpv) + c);
+        tmem_ld_x32(tmem + lane_off + cS + wg * SM + c, reinterpret_cast<uint32_t*>(sv) + c);
+        if (kWantDk) tmem_ld_x32(tmem + lane_off + cDP + wg * SM + c, reinterpret_cast<uint32_t*>(dpv) + c);
       }
       tc_wait_ld();
-      const TileInfo ti = qt_info[it.m];
+      const TileInfo ti = it.tile(it.m);
       const bool tile_full = (n * kBlockN >= ti.max_lo) && ((n + 1) * kBlockN <= ti.min_hi);
-      uint32_t pp[SM / 2], pd[SM / 2];
 #pragma unroll
-      for (int c = 0; c < SM; c += 4) {
-        const float4 l4 = *reinterpret_cast<const float4*>(&s.lse2[buf][c]);
-        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
-        float pv[4];
+      for (int c0 = 0; c0 < SM; c0 += 32) {
+        uint32_t pp[16], pd[16];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) pv[e] = ex2_approx(fmaf(sv[c + e], c_log2, -ls[e]));
-        if (!tile_full) {
-          const int4 lo4 = *reinterpret_cast<const int4*>(&s.lo[buf][c]);
-          const int4 hi4 = *reinterpret_cast<const int4*>(&s.hi[buf][c]);
-          const int los[4] = {lo4.x, lo4.y, lo4.z, lo4.w};
-          const int his[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) pv[e] = (key >= los[e] && key < his[e]) ? pv[e] : 0.f;
+        for (int c = c0; c < c0 + 32; c += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(&s.nlse2[wg][sub][c]);
+          float2 pa = ex2_pair_sfu(fma2(make_float2(sv[c], sv[c + 1]), cc, make_float2(l4.x, l4.y)));
+          float2 pb = ex2_pair_sfu(fma2(make_float2(sv[c + 2], sv[c + 3]), cc, make_float2(l4.z, l4.w)));
+          if (!tile_full) {
+            const int4 lo4 = *reinterpret_cast<const int4*>(&s.lo[wg][sub][c]);
+            const int4 hi4 = *reinterpret_cast<const int4*>(&s.hi[wg][sub][c]);
+            pa.x = (key >= lo4.x && key < hi4.x) ? pa.x : 0.f;
+            pa.y = (key >= lo4.y && key < hi4.y) ? pa.y : 0.f;
+            pb.x = (key >= lo4.z && key < hi4.z) ? pb.x : 0.f;
+            pb.y = (key >= lo4.w && key < hi4.w) ? pb.y : 0.f;
+          }
+          const int o = (c - c0) >> 1;
+          if (kWantDv) {
+            pp[o] = Pack2<T>::pack(pa.x, pa.y);
+            pp[o + 1] = Pack2<T>::pack(pb.x, pb.y);
+          }
+          if (kWantDk) {
+            const float4 d4 = *reinterpret_cast<const float4*>(&s.ndelta[wg][sub][c]);
+            const float2 da = mul2(pa, add2(make_float2(dpv[c], dpv[c + 1]), make_float2(d4.x, d4.y)));
+            const float2 db = mul2(pb, add2(make_float2(dpv[c + 2], dpv[c + 3]), make_float2(d4.z, d4.w)));
+            pd[o] = Pack2<T>::pack(da.x, da.y);
+            pd[o + 1] = Pack2<T>::pack(db.x, db.y);
+          }
         }
-        if (kWantDv) {
-          pp[(c >> 1)] = Pack2<T>::pack(pv[0], pv[1]);
-          pp[(c >> 1) + 1] = Pack2<T>::pack(pv[2], pv[3]);
-        }
-        if (kWantDk) {
-          const float4 d4 = *reinterpret_cast<const float4*>(&s.delta[buf][c]);
-          pd[(c >> 1)] = Pack2<T>::pack(pv[0] * (dpv[c] - d4.x), pv[1] * (dpv[c + 1] - d4.y));
-          pd[(c >> 1) + 1] = Pack2<T>::pack(pv[2] * (dpv[c + 2] - d4.z), pv[3] * (dpv[c + 3] - d4.w));
-        }
-      }
-      if (kWantDv) {
-        if (SM == 64) tmem_st_x32(tmem + lane_off + cS + buf * SM, pp); else tmem_st_x16(tmem + lane_off + cS + buf * SM, pp);
-      }
-      if (kWantDk) {
-        if (SM == 64) tmem_st_x32(tmem + lane_off + cDP + buf * SM, pd); else tmem_st_x16(tmem + lane_off + cDP + buf * SM, pd);
+        if (kWantDv) tmem_st_x16(tmem + lane_off + cS + wg * SM + (c0 >> 1), pp);
+        if (kWantDk) tmem_st_x16(tmem + lane_off + cDP + wg * SM + (c0 >> 1), pd);
       }
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(&s.pds_full[buf]);
-      if (nx.valid()) stash(buf ^ 1, f0, f1, i0, i1);
+      mbar_arrive_warp(&s.pds_full[wg]);
+      if (nx.valid()) stash(sub ^ 1, f0, f1, i0, i1);
       it = nx;
-      ++cnt;
+      ++kk;
     }
-    // epilogue: dK (scaled) and dV rows of this key tile
+    // epilogue: warpgroup 0 writes dK (scaled), warpgroup 1 writes dV
     if (ok && any_work) ok = mbar_wait(ctx, &s.all_done, 0, 81);
-    if (ok) {
+    const bool mine = (wg == 0) ? kWantDk : kWantDv;
+    if (ok && mine) {
       tc_fence_after();
       const bool live = key < p.Lk;
-      T* dk_row = reinterpret_cast<T*>(p.dk) + (((size_t)b * p.Lk + (live ? key : 0)) * p.Hkv + kvh) * p.D;
-      T* dv_row = reinterpret_cast<T*>(p.dv) + (((size_t)b * p.Lk + (live ? key : 0)) * p.Hkv + kvh) * p.V;
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        if ((which == 0 && !kWantDk) || (which == 1 && !kWantDv)) continue;
-        const int width = which == 0 ? p.D : p.V;
-        const int pad = which == 0 ? d_pad : v_pad;
-        const float mul = which == 0 ? p.scale : 1.f;
-        T* out = which == 0 ? dk_row : dv_row;
-        const uint32_t col = which == 0 ? cDK : cDV;
-        for (int c0 = 0; c0 < pad; c0 += 32) {
-          uint32_t o[32];
-          if (any_work) {
-            tmem_ld_x32(tmem + lane_off + col + c0, o);
-            tc_wait_ld();
-          } else {
+      const int width = wg == 0 ? p.D : p.V;
+      const int pad = wg == 0 ? d_pad : v_pad;
+      const float mul = wg == 0 ? p.scale : 1.f;
+      const uint32_t col = wg == 0 ? cDK : cDV;
+      T* out = wg == 0
+          ? reinterpret_cast<T*>(p.dk) + (((size_t)b * p.Lk + (live ? key : 0)) * p.Hkv + kvh) * p.D
+          : reinterpret_cast<T*>(p.dv) + (((size_t)b * p.Lk + (live ? key : 0)) * p.Hkv + kvh) * p.V;
+      for (int c0 = 0; c0 < pad; c0 += 32) {
+        uint32_t o[32];
+        if (any_work) {
+          tmem_ld_x32(tmem + lane_off + col + c0, o);
+          tc_wait_ld();
+        } else {
 #pragma unroll
-            for (int c = 0; c < 32; ++c) o[c] = 0u;
-          }
-          if (live) {
+          for (int c = 0; c < 32; ++c) o[c] = 0u;
+        }
+        if (live) {
 #pragma unroll
-            for (int c = 0; c < 32; c += 8) {
-              if (c0 + c < width) {
-                uint4 u;
-                u.x = Pack2<T>::pack(__uint_as_float(o[c + 0]) * mul, __uint_as_float(o[c + 1]) * mul);
-                u.y = Pack2<T>::pack(__uint_as_float(o[c + 2]) * mul, __uint_as_float(o[c + 3]) * mul);
-                u.z = Pack2<T>::pack(__uint_as_float(o[c + 4]) * mul, __uint_as_float(o[c + 5]) * mul);
-                u.w = Pack2<T>::pack(__uint_as_float(o[c + 6]) * mul, __uint_as_float(o[c + 7]) * mul);
-                *reinterpret_cast<uint4*>(out + c0 + c) = u;
-              }
+          for (int c = 0; c < 32; c += 8) {
+            if (c0 + c < width) {
+              uint4 u;
+              u.x = Pack2<T>::pack(__uint_as_float(o[c + 0]) * mul, __uint_as_float(o[c + 1]) * mul);
+              u.y = Pack2<T>::pack(__uint_as_float(o[c + 2]) * mul, __uint_as_float(o[c + 3]) * mul);
+              u.z = Pack2<T>::pack(__uint_as_float(o[c + 4]) * mul, __uint_as_float(o[c + 5]) * mul);
+              u.w = Pack2<T>::pack(__uint_as_float(o[c + 6]) * mul, __uint_as_float(o[c + 7]) * mul);
+              *reinterpret_cast<uint4*>(out + c0 + c) = u;
             }
           }
         }
       }
     }
-  } else if (warp == 4 && lane == 0 && any_work) {
+  } else if (warp == 8 && lane == 0 && any_work) {
     // ------------------------------ MMA issuer ------------------------------
     const uint32_t idesc_st = make_idesc(kBlockN, SM, kFormat, 0, 0);
     const uint32_t idesc_dv = make_idesc(kBlockN, v_pad, kFormat, 0, 1);
@@ -641,7 +669,6 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       umma_commit(&s.sdp_full[buf]);
     };
     bool ok = mbar_wait(ctx, &s.kv_full, 0, 90);
-    Iter it = it0;
     Iter ahead = it0;      // item whose S^T / dP^T is issued next
     int issued = 0, cnt = 0;
     // prologue: S^T / dP^T of the first two items
@@ -652,7 +679,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       issue_st(issued % kStages, issued & 1);
       ++issued; ahead.next();
     }
-    while (it.valid() && ok) {
+    while (cnt < issued && ok) {
       const int buf = cnt & 1, st = cnt % kStages;
       ok = mbar_wait(ctx, &s.pds_full[buf], (cnt >> 1) & 1, 92);
       if (!ok) break;
@@ -673,7 +700,6 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
       umma_commit(&s.q_empty[st]);
-      it.next();
       ++cnt;
       if (ahead.valid()) {
         ok = mbar_wait(ctx, &s.q_full[issued % kStages], (issued / kStages) & 1, 93);
@@ -684,7 +710,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
     }
     if (ok) umma_commit(&s.all_done);
-  } else if (warp == 5 && lane == 0 && any_work) {
+  } else if (warp == 9 && lane == 0 && any_work) {
     // ------------------------------ TMA producer ------------------------------
     tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_do); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
     mbar_arrive_expect_tx(&s.kv_full, nbox_qk * kKvBox + (kWantDk ? nbox_v * kKvBox : 0));
@@ -713,7 +739,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     while (globaltimer_ns() - t0 < 200000ull) { }
     __syncthreads();
   }
-  if (warp == 5) { __syncwarp(); tmem_dealloc(tmem, kTmemCols); }
+  if (warp == 9) { __syncwarp(); tmem_dealloc(tmem, kTmemCols); }
 }
 
 // ---------------------------------------------------------------------------
@@ -753,7 +779,7 @@ static int launch_dkv(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t st
   if (grid > 0x7fffffffLL) { set_error("dK/dV grid out of range"); return XATTN_E_INVALID; }
   {
     ProfileScope prof(kProfBwdDkv, stream);
-    kern<<<(unsigned)grid, 256, smem, stream>>>(tq, tdo, tk, tv, p);
+    kern<<<(unsigned)grid, 384, smem, stream>>>(tq, tdo, tk, tv, p);
   }
   return XATTN_OK;
 }

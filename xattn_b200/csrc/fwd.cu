@@ -52,14 +52,7 @@ struct FwdSmem {
   int abort_flag;
 };
 
-template <int N>
-__device__ __forceinline__ void setmaxnreg_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N>
-__device__ __forceinline__ void setmaxnreg_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
+
 
 // T: __nv_bfloat16 or __half.  HD: padded head dimension of the shared-memory
 // tiles (64, 128 or 256).  NT: query tiles per CTA.  HP: high-precision softmax.
@@ -122,10 +115,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     for (int t = 0; t < NT; ++t) {
       mbar_init(&s.q_full[t], 1);
       mbar_init(&s.s_full[t], 1);
-      mbar_init(&s.p_full[t], 128);
-      mbar_init(&s.o_ready[t], 128);
+      mbar_init(&s.p_full[t], 4);
+      mbar_init(&s.o_ready[t], 4);
       mbar_init(&s.pv_done[t], 1);
-      mbar_init(&s.corr_full[t], 128);
+      mbar_init(&s.corr_full[t], 4);
     }
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&s.k_full[i], 1);
@@ -185,9 +178,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
         for (int c = 0; c < 128; ++c) sc[c] = (c >= rl && c < rh) ? sc[c] : -INFINITY;
       }
-      float mx = sc[0];
+      float mxa = max3(sc[0], sc[1], sc[2]), mxb = max3(sc[3], sc[4], sc[5]);
+      float mxc = max3(sc[6], sc[7], sc[8]), mxd = max3(sc[9], sc[10], sc[11]);
 #pragma unroll
-      for (int c = 1; c < 128; ++c) mx = fmaxf(mx, sc[c]);
+      for (int c = 12; c < 124; c += 8) {
+        mxa = max3(mxa, sc[c], sc[c + 1]);
+        mxb = max3(mxb, sc[c + 2], sc[c + 3]);
+        mxc = max3(mxc, sc[c + 4], sc[c + 5]);
+        mxd = max3(mxd, sc[c + 6], sc[c + 7]);
+      }
+      mxa = max3(mxa, sc[124], sc[125]);
+      mxb = max3(mxb, sc[126], sc[127]);
+      const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
       float m_new = fmaxf(m, mx);
       if (!HP) {
         // keep the old reference while the maximum grew by less than 2^8: the
@@ -198,40 +200,57 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       if (m != -INFINITY && m_new != m) factor = HP ? exp2f((m - m_new) * c_log2) : ex2_approx((m - m_new) * c_log2);
       if (j > 0) {
         s.scale_buf[t][j & 1][r] = factor;
-        mbar_arrive(&s.corr_full[t]);
+        mbar_arrive_warp(&s.corr_full[t]);
       }
       m = m_new;
       const float m_ref = (m == -INFINITY) ? 0.f : m;
       const float neg_mc = -m_ref * c_log2;
-      float sum = 0.f;
       const uint32_t t_p = t_s;   // P overwrites the first 64 columns of S
+      float sum = 0.f;
+      if (HP) {
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c0 = 0; c0 < 128; c0 += 32) {
-        uint32_t pk[16];
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+          uint32_t pk[16];
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float p0, p1;
-          if (HP) {
-            p0 = exp2f(__fmul_rn(__fsub_rn(sc[c0 + c], m_ref), c_log2));
-            p1 = exp2f(__fmul_rn(__fsub_rn(sc[c0 + c + 1], m_ref), c_log2));
-          } else {
-            p0 = ex2_approx(fmaf(sc[c0 + c], c_log2, neg_mc));
-            p1 = ex2_approx(fmaf(sc[c0 + c + 1], c_log2, neg_mc));
+          for (int c = 0; c < 32; c += 2) {
+            const float p0 = exp2f(__fmul_rn(__fsub_rn(sc[c0 + c], m_ref), c_log2));
+            const float p1 = exp2f(__fmul_rn(__fsub_rn(sc[c0 + c + 1], m_ref), c_log2));
+            sum4[(c >> 1) & 3] += p0 + p1;
+            pk[c >> 1] = Pack2<T>::pack(p0, p1);
           }
-          sum += p0 + p1;
-          pk[c >> 1] = Pack2<T>::pack(p0, p1);
+          tmem_st_x16(t_p + (c0 >> 1), pk);
         }
-        tmem_st_x16(t_p + (c0 >> 1), pk);
+        sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      } else {
+        const float2 cc = make_float2(c_log2, c_log2), nm = make_float2(neg_mc, neg_mc);
+        float2 s2a = make_float2(0.f, 0.f), s2b = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int c = 0; c < 32; c += 4) {
+            const float2 pa = ex2_pair_sfu(fma2(make_float2(sc[c0 + c], sc[c0 + c + 1]), cc, nm));
+            const float2 pb = ex2_pair_sfu(fma2(make_float2(sc[c0 + c + 2], sc[c0 + c + 3]), cc, nm));
+            s2a = add2(s2a, pa);
+            s2b = add2(s2b, pb);
+            pk[c >> 1] = Pack2<T>::pack(pa.x, pa.y);
+            pk[(c >> 1) + 1] = Pack2<T>::pack(pb.x, pb.y);
+          }
+          tmem_st_x16(t_p + (c0 >> 1), pk);
+        }
+        const float2 s2 = add2(s2a, s2b);
+        sum = s2.x + s2.y;
       }
       l = l * factor + sum;
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(&s.p_full[t]);
+      mbar_arrive_warp(&s.p_full[t]);
     }
     // hand the row statistics to the epilogue
     s.final_l[t][r] = l;
     s.final_m[t][r] = m;
-    mbar_arrive(&s.corr_full[t]);
+    mbar_arrive_warp(&s.corr_full[t]);
   } else if (warp < 4 * NT + 4) {
     // ======================= correction + epilogue warpgroup =======================
     // launch allocation is 128 registers per thread: shrink below it, grow above it
@@ -264,7 +283,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           tc_wait_st();
         }
         tc_fence_before();
-        mbar_arrive(&s.o_ready[t]);
+        mbar_arrive_warp(&s.o_ready[t]);
       }
     }
     // epilogue: y = O / l, lse = ln2 * (m * c + log2 l)
@@ -336,9 +355,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       // ------------------------------ MMA issuer ------------------------------
       const uint32_t idesc_qk = make_idesc(kBlockM, kBlockN, kFormat, 0, 0);
       const uint32_t idesc_pv = make_idesc(kBlockM, v_pad, kFormat, 0, 1);
-      int cnt[NT];            // iterations started per tile
-#pragma unroll
-      for (int t = 0; t < NT; ++t) cnt[t] = 0;
       bool ok = true;
       auto issue_qk = [&](int t, int stage) {
         const uint32_t qa = smem_u32(s.q[t]);
@@ -502,6 +518,7 @@ static int dispatch_fwd_dim(const XattnFwdArgs& a, const FwdParams& p, cudaStrea
   if (hd <= 128) return launch_fwd<T, 128, 2, HP>(a, p, stream);
   return launch_fwd<T, 256, 1, HP>(a, p, stream);
 }
+
 
 int fwd_entry(const XattnFwdArgs* a, cudaStream_t stream) {
   if (!a) { set_error("null arguments"); return XATTN_E_INVALID; }
