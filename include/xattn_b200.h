@@ -173,6 +173,17 @@ typedef struct {
 size_t xattn_b200_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);
 int xattn_b200_bwd(const XattnBwdArgs* args, xattn_stream_t stream);
 
+/* The same backward for callers that may not allocate device memory (no counterpart in the
+ * reference, whose ops allocate their workspaces themselves): a plugin host that owns the device
+ * arena, or a serving loop that cannot afford the device-wide stall of a cudaMalloc.  `workspace`
+ * in the arguments is ignored; the scratch lives in a fixed 8 MiB array inside the library that
+ * every GPU loading it keeps until exit.  Limit: batch * q_heads * q_len <= 1048576, larger
+ * problems return XATTN_E_INVALID.  Nothing is allocated or freed on any path.  All calls on a
+ * device share the array: nothing needs clearing between calls, but calls whose kernels overlap
+ * on the GPU race, so serialise them.  The first call on a device looks up the array's address;
+ * make it outside any stream capture. */
+int xattn_b200_bwd_static_scratch(const XattnBwdArgs* args, xattn_stream_t stream);
+
 /* ------------------------------------------------------------------------
  * SoftDelta gate (HBM-bound).  Replaces _softdelta_gate_fwd, _softdelta_gate_restore
  * and _softdelta_gate_bwd (csrc/softdelta/bindings.cc:11-53, csrc/softdelta/gate.cu:559-627)

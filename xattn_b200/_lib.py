@@ -102,6 +102,7 @@ SYMBOLS = {
     "xattn_b200_fwd": (C.c_int, [C.POINTER(FwdArgs), C.c_void_p]),
     "xattn_b200_bwd_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
     "xattn_b200_bwd": (C.c_int, [C.POINTER(BwdArgs), C.c_void_p]),
+    "xattn_b200_bwd_static_scratch": (C.c_int, [C.POINTER(BwdArgs), C.c_void_p]),
     "xattn_b200_softdelta_gate_fwd": (C.c_int, [C.POINTER(GateArgs), C.c_void_p]),
     "xattn_b200_softdelta_gate_bwd": (C.c_int, [C.POINTER(GateArgs), C.c_void_p]),
     "xattn_b200_zero_constant_key_rows": (C.c_int, [C.POINTER(ConstantKeyArgs), C.c_void_p]),

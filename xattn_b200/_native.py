@@ -336,3 +336,51 @@ def profile_read(capacity: int = 65536):
     ms = (C.c_float * capacity)()
     n = _lib.load().xattn_b200_profile_read(kinds, ms, capacity)
     return [(PROFILE_KINDS.get(kinds[i], str(kinds[i])), float(ms[i])) for i in range(max(n, 0))]
+
+
+STATIC_SCRATCH_MAX_ROWS = 1 << 20
+
+
+def attention_bwd_static_scratch(dy: Tensor, q: Tensor, k: Tensor, v: Tensor, y: Tensor, lse: Tensor,
+                                 plan: Tensor, scale: float, dq: Tensor, dk: Tensor, dv: Tensor) -> None:
+    """Backward into caller-provided ``dq`` / ``dk`` / ``dv`` without any device allocation.
+
+    For callers that are not allowed to allocate on the device (a host application that owns all
+    device memory and passes an op only its inputs and outputs; a serving loop that must not hit
+    the device-wide stall of an allocation).  The kernel scratch is a fixed array inside the
+    library instead of a tensor, so ``batch * q_heads * q_len`` is limited to
+    ``STATIC_SCRATCH_MAX_ROWS``; calls on one device share that array and must not overlap on the
+    GPU.  Every tensor must already be laid out the way the kernels read it (unit last stride,
+    16-byte aligned base and strides): nothing is copied or made contiguous here.  The first call
+    on a device resolves the array's address and belongs outside any stream capture.
+    """
+    lib = _lib.load()
+    require_cuda(q, "xattn_b200 backward (static scratch)")
+    for name, t in (("q", q), ("k", k), ("v", v), ("y", y), ("dy", dy)):
+        if tma_ready(t) is not t:
+            raise ValueError(f"{name} needs a unit last stride and 16-byte aligned base and strides; "
+                             "this entry point does not copy")
+    for name, t in (("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv)):
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    B, Lq, Hq, D = q.shape
+    Lk, Hkv, V = k.shape[1], k.shape[2], v.shape[3]
+    if dq.shape != q.shape or dk.shape != k.shape or dv.shape != v.shape:
+        raise ValueError("dq / dk / dv must be shaped like q / k / v")
+    args = _lib.BwdArgs()
+    args.dtype = _DTYPES[q.dtype]
+    args.batch, args.q_len, args.k_len = B, Lq, Lk
+    args.q_heads, args.kv_heads, args.qk_dim, args.v_dim = Hq, Hkv, D, V
+    args.q, args.k, args.v, args.y, args.dy = q.data_ptr(), k.data_ptr(), v.data_ptr(), y.data_ptr(), dy.data_ptr()
+    for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("y_strides", y), ("dy_strides", dy)):
+        setattr(args, name, (C.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2)))
+    args.lse = lse.data_ptr()
+    args.scale = float(scale)
+    args.plan = plan.data_ptr()
+    args.dq, args.dk, args.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    args.workspace = None
+    st = _state(q.device)
+    args.status = st.status.data_ptr()
+    with torch.cuda.device(q.device):
+        _lib.check(lib.xattn_b200_bwd_static_scratch(C.byref(args), _stream_ptr()),
+                   "xattn_b200_bwd_static_scratch")

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libxattn_b200.so")
-SOURCES = ("api.cu", "common.cu", "plan.cu", "fwd.cu", "bwd.cu", "aux.cu")
+SOURCES = ("api.cu", "common.cu", "plan.cu", "fwd.cu", "bwd.cu", "aux.cu", "bwd_static.cu")
 HEADERS = ("ptx.cuh", "common.cuh", os.path.join("..", "..", "include", "xattn_b200.h"))
 
 

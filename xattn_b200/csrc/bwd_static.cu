@@ -1,0 +1,83 @@
+// Backward pass for callers that must not allocate device memory.
+//
+// The regular backward entry takes a caller-provided workspace (two FP32 words per batch row, query
+// head and query position: rowsum(dy*y) and lse*log2e).  Some callers cannot provide one: a plugin
+// host that owns the whole device arena and hands an op nothing but its input and output buffers,
+// or a serving loop where a cudaMalloc would stall every stream of the device at an unpredictable
+// moment.  For them the same kernels run here with the workspace in a fixed array that lives in the
+// library image: no cudaMalloc, cudaFree or allocating library call is made on any path of this file.
+//
+// Costs and rules:
+//  * the array is part of the module, so every GPU that loads the library holds its
+//    kStaticRows * 8 bytes (8 MiB) until the process exits, used or not;
+//  * batch * q_heads * q_len may not exceed kStaticRows; larger problems are refused with
+//    XATTN_E_INVALID before anything is launched;
+//  * every call on a device shares the one array.  The preprocess kernel rewrites all entries it
+//    later reads, so nothing has to be cleared between calls and a previous call's contents are
+//    never observed; but two calls whose kernels overlap on the GPU (different streams, or threads
+//    without ordering) would overwrite each other's rows — callers serialise them;
+//  * the first call on a device resolves the array's device address (cudaGetSymbolAddress, with
+//    that device current).  Make that first call outside any stream capture.
+#include <mutex>
+#include "common.cuh"
+
+namespace xb {
+int bwd_entry(const XattnBwdArgs* a, cudaStream_t stream);
+
+namespace {
+
+constexpr long long kStaticRows = 1ll << 20;   // batch * q_heads * q_len, at most
+constexpr int kMaxDevices = 64;
+
+// delta in the first half, lse*log2e in the second — the layout bwd_entry gives its workspace
+static __device__ __align__(256) float g_static_workspace[2 * kStaticRows];
+
+std::mutex g_static_mutex;
+float* g_static_ptr[kMaxDevices] = {};
+
+// Device address of the array on the current device; resolved once per device.
+int static_workspace(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { set_error("cudaGetDevice: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
+  if (dev < 0 || dev >= kMaxDevices) { set_error("device index %d out of range", dev); return XATTN_E_UNSUPPORTED; }
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_ptr[dev]) {
+    // In host code the array's name is only a handle for the runtime, not an address a kernel can use.
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_workspace);
+    if (e != cudaSuccess || !p) {
+      set_error("cudaGetSymbolAddress(static workspace): %s", cudaGetErrorString(e));
+      return XATTN_E_CUDA;
+    }
+    g_static_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_static_ptr[dev];
+  return XATTN_OK;
+}
+
+}  // namespace
+
+int bwd_static_entry(const XattnBwdArgs* a, cudaStream_t stream) {
+  if (!a) { set_error("null arguments"); return XATTN_E_INVALID; }
+  if (a->batch <= 0 || a->q_heads <= 0 || a->q_len <= 0) { set_error("bad batch / head / length"); return XATTN_E_INVALID; }
+  const long long rows = (long long)a->batch * a->q_heads * a->q_len;
+  if (rows > kStaticRows || rows / a->batch / a->q_heads != a->q_len) {
+    set_error("batch * q_heads * q_len = %lld exceeds the static workspace of %lld rows; "
+              "use xattn_b200_bwd with a caller-provided workspace", rows, kStaticRows);
+    return XATTN_E_INVALID;
+  }
+  float* ws = nullptr;
+  if (int rc = static_workspace(&ws)) return rc;
+  XattnBwdArgs with_ws = *a;
+  with_ws.workspace = ws;            // whatever the caller put there is ignored
+  return bwd_entry(&with_ws, stream);
+}
+
+long long bwd_static_max_rows() { return kStaticRows; }
+
+}  // namespace xb
+
+extern "C" int xattn_b200_bwd_static_scratch(const XattnBwdArgs* args, xattn_stream_t stream) {
+  return xb::bwd_static_entry(args, static_cast<cudaStream_t>(stream));
+}
