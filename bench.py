@@ -49,6 +49,10 @@ WORKLOADS = {
                          text="profiling case: dense causal B=1 S=8192 Hq=32 Hkv=8 D=128 (0.24 GB of tensors, above L2)"),
     "causal_c2_dense": dict(B=4, S=8192, Hq=32, Hkv=8, D=128, segments=False,
                             text="configs[1] shape with one segment per sequence (dense causal)"),
+    # sequence-sharded across the ranks (strong scaling): each rank holds S / N tokens and receives a
+    # window-sized K/V halo from its predecessor
+    "swa_c3": dict(B=1, S=32768, Hq=32, Hkv=8, D=128, segments=False, window=4096,
+                   text="configs[2]: sliding-window fwd+bwd bf16 B=1 S=32768 Hq=32 Hkv=8 D=128 window=4096, sequence-sharded with KV halo exchange"),
 }
 
 
@@ -197,6 +201,8 @@ def run_ours(args, w):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    if "window" in w:
+        return run_swa_sharded(args, w, world, rank, dev)
     host = make_host_inputs(w, seed=1 + rank)
     pinned = [None if t is None else t.pin_memory() for t in host]
     q, k, v, dy, ids = (None if t is None else t.to(dev) for t in pinned)
@@ -325,6 +331,114 @@ def run_ours(args, w):
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_swa_sharded(args, w, world, rank, dev):
+    """configs[2]: one sequence of S tokens split contiguously over the ranks; total work is fixed."""
+    import torch.distributed as dist
+    import xattn_b200 as xattn
+    from xattn_b200 import _native, parallel as P
+
+    if world == 1:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=os.environ.get("MASTER_PORT", "29533"))
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    S, D, window = w["S"], w["D"], w["window"]
+    if S % world or S // world < window:
+        raise SystemExit("sequence length must split into slices of at least one window")
+    n = S // world
+    g = torch.Generator().manual_seed(2)
+    draw = lambda *shape: torch.randn(shape, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    q, k, v, dy = draw(1, S, w["Hq"], D), draw(1, S, w["Hkv"], D), draw(1, S, w["Hkv"], D), draw(1, S, w["Hq"], D)
+    sl = slice(rank * n, (rank + 1) * n)
+    pinned = [t[:, sl].contiguous().pin_memory() for t in (q, k, v, dy)]
+    ql, kl, vl, dyl = (t.to(dev) for t in pinned)
+    pairs = w["Hq"] * sum(min(i, window) + 1 for i in range(S))      # whole job
+    flops_step = 14 * D * pairs
+
+    def step(a, b, c, d):
+        a, b, c = (t.detach().requires_grad_() for t in (a, b, c))
+        y = P.sequence_parallel_flash_swa(a, b, c, window)
+        return (y, *torch.autograd.grad(y, (a, b, c), d))
+
+    def barrier():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step(ql, kl, vl, dyl)
+    _native.check_status()
+    sampler = ClockSampler(dev.index)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    _native.profile_enable(True)
+    e0.record()
+    for _ in range(args.steps):
+        step(ql, kl, vl, dyl)
+    e1.record()
+    barrier()
+    _native.profile_enable(False)
+    records = _native.profile_read()
+    ms = e0.elapsed_time(e1) / args.steps
+    out_host = None
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 10))
+
+    def e2e_step():
+        nonlocal out_host
+        outs = step(*(t.to(dev, non_blocking=True) for t in pinned))
+        if out_host is None:
+            out_host = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+        for dst, src in zip(out_host, outs):
+            dst.copy_(src, non_blocking=True)
+
+    for _ in range(0 if args.no_e2e else 2):
+        e2e_step()
+    barrier()
+    f0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1) / max(e2e_steps, 1)
+    clocks = sampler.stop()
+    times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(times[0]), float(times[1])
+    if rank == 0:
+        peaks, peak_src = measured_peaks()
+        peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
+        per_kind = {}
+        for kind, t in records:
+            per_kind.setdefault(kind, []).append(t)
+        kernels = {kd: {"launches": len(vs), "avg_ms": sum(vs) / len(vs), "share": sum(vs) / (ms * args.steps)}
+                   for kd, vs in per_kind.items()}
+        rank_pairs = pairs / world
+        dkv = kernels.get("bwd_dkv", {"avg_ms": float("inf")})
+        achieved = 8 * D * rank_pairs / dkv["avg_ms"] * 1e-9
+        h2d = sum(t.numel() * t.element_size() for t in pinned) * world
+        d2h = sum(t.numel() * t.element_size() for t in out_host) * world if out_host else 0
+        print(json.dumps({
+            "metric": "sliding-window attn fwd+bwd TFLOPS (bf16 S=32K w=4096 D=128), whole job",
+            "value": flops_step / ms * 1e-9, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["text"], "l2": "0.27 GB of tensors per step in total",
+                       "visible_pairs_per_step": pairs, "flops_per_step": flops_step,
+                       "parallelism": f"sequence split over {world} GPU(s); K/V halo of {window} tokens from the previous rank (NCCL send/recv), halo gradients sent back"},
+            "per_gpu_tflops": flops_step / ms * 1e-9 / world,
+            "e2e": None if not e2e_steps else {"value": flops_step / e2e_ms * 1e-9, "unit": "TFLOP/s",
+                                               "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                                               "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "gpu_launches": len(records) + 2 * len(per_kind.get("plan", [])),
+            "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": "bwd_dkv", "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": f"{peak_src} bf16_tflops_sustained"},
+            "kernels": kernels,
+        }))
+    dist.destroy_process_group()
 
 
 def main():

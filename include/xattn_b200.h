@@ -38,7 +38,10 @@ enum { XATTN_DTYPE_F16 = 0, XATTN_DTYPE_BF16 = 1 };
 
 /* Visibility of keys to the left of a query (tests/_reference.py:50-59,
  * csrc/attention/hopper/semantics/visibility.h:17-180). */
-enum { XATTN_VIS_FULL = 0, XATTN_VIS_WINDOW = 1, XATTN_VIS_CHUNK = 2 };
+enum { XATTN_VIS_FULL = 0, XATTN_VIS_WINDOW = 1, XATTN_VIS_CHUNK = 2,
+       /* every key of the query's segment, later ones too: the off-diagonal blocks of ring attention
+          (no counterpart in the reference, which has no non-causal mode) */
+       XATTN_VIS_ALL = 3 };
 
 typedef void* xattn_stream_t; /* cudaStream_t */
 

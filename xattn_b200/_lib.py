@@ -15,7 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("XATTN_B200_LIBRARY") or os.path.join(_HERE, "libxattn_b200.so")
 
 XATTN_DTYPE_F16, XATTN_DTYPE_BF16 = 0, 1
-VIS_FULL, VIS_WINDOW, VIS_CHUNK = 0, 1, 2
+VIS_FULL, VIS_WINDOW, VIS_CHUNK, VIS_ALL = 0, 1, 2, 3
 
 
 class PlanArgs(C.Structure):

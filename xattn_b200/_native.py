@@ -17,7 +17,7 @@ from torch import Tensor
 from . import _lib
 
 _DTYPES = {torch.float16: _lib.XATTN_DTYPE_F16, torch.bfloat16: _lib.XATTN_DTYPE_BF16}
-_VIS = {"full": _lib.VIS_FULL, "window": _lib.VIS_WINDOW, "chunk": _lib.VIS_CHUNK}
+_VIS = {"full": _lib.VIS_FULL, "window": _lib.VIS_WINDOW, "chunk": _lib.VIS_CHUNK, "all": _lib.VIS_ALL}
 
 # XATTN_B200_SYNC_CHECK=1: read the device status word after every launch
 # (synchronises).  Otherwise the word is read back asynchronously and examined

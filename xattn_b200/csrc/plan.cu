@@ -127,6 +127,7 @@ __global__ void __launch_bounds__(256) plan_rows_kernel(const RowArgs a) {
   }
   long long lo = origin + left_edge(a.visibility, a.span, qp);
   long long hi = origin + qp + 1 - (a.strict ? 1 : 0);
+  if (a.visibility == XATTN_VIS_ALL) hi = k_end;
   if (lo < k_start) lo = k_start;
   if (hi > k_end) hi = k_end;
   if (hi <= lo) { lo = 0; hi = 0; }
@@ -239,7 +240,7 @@ int build_plan_entry(const XattnPlanArgs* a, cudaStream_t stream) {
   if (a->batch <= 0 || a->q_len <= 0 || a->k_len <= 0 || a->batch * a->q_len > 0x7fffffffLL || a->k_len > 0x7fffffffLL) {
     set_error("plan sizes out of range"); return XATTN_E_INVALID;
   }
-  if (a->visibility < XATTN_VIS_FULL || a->visibility > XATTN_VIS_CHUNK) { set_error("unknown visibility"); return XATTN_E_INVALID; }
+  if (a->visibility < XATTN_VIS_FULL || a->visibility > XATTN_VIS_ALL) { set_error("unknown visibility"); return XATTN_E_INVALID; }
   if (a->visibility == XATTN_VIS_WINDOW && a->span < 0) { set_error("window_size must be nonnegative"); return XATTN_E_INVALID; }
   if (a->visibility == XATTN_VIS_CHUNK && a->span <= 0) { set_error("chunk_size must be positive"); return XATTN_E_INVALID; }
   if ((a->q_segment == nullptr) != (a->k_segment == nullptr)) { set_error("q_segment and k_segment must be given together"); return XATTN_E_INVALID; }
