@@ -50,10 +50,8 @@ def _worker(rank, world, port, mode, results):
         grads = torch.autograd.grad(y, (ql, kl, vl), dy[:, sl])
         ref = torch.autograd.grad(yf, (qf, kf, vf), dy)
         xattn.check_status()
-        errs = [(y.float() - yf[:, sl].float()).abs().max().item()]
-        errs += [(a.float() - b[:, sl].float()).abs().max().item() for a, b in zip(grads, ref)]
-        scale = [yf.float().abs().max().item()] + [b.float().abs().max().item() for b in ref]
-        results[rank] = max(e / max(s_, 1e-6) for e, s_ in zip(errs, scale))
+        pairs = [(y, yf[:, sl])] + [(a, b[:, sl]) for a, b in zip(grads, ref)]
+        results[rank] = max(((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-6)).item() for a, b in pairs)
     finally:
         dist.destroy_process_group()
 
@@ -74,6 +72,6 @@ def test_sharded_matches_single_gpu(mode, cuda_device):
             p.join(timeout=300)
         for p in procs:
             assert p.exitcode == 0, f"rank exited with {p.exitcode}"
-        # halo variants tile the sequence exactly like the single-GPU run except at slice starts: bf16 rounding
-        # of partial results is the only difference; the ring merges FP32 partials and rounds once
-        assert max(results.values()) < 2e-2, dict(results)
+        # relative norm error of y, dq, dk, dv on each rank's slice: the sharded runs differ from the single-GPU
+        # run only by bf16 rounding of partial results (measured 2e-3 to 3e-3)
+        assert max(results.values()) < 1e-2, dict(results)
