@@ -1,0 +1,142 @@
+"""Edge sizes and regressions the reference pins in its own suite: very large batches
+(tests/test_large_batch.py:16-112), long sequences checked on sampled rows with sparse dO
+(tests/_numerics.py:293-320), the rounding-bias regression with identical keys (:216-235), and
+live previous-K/V gradients under BOS masks (tests/test_high_precision.py:166-190)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+import xattn_b200 as xattn
+from oracle import attention_oracle as O
+from tests._cases import Case, make_inputs, metadata_for, op_options
+
+pytestmark = pytest.mark.gpu
+OPS = {"full": "causal_flash_attn", "window": "flash_swa", "chunk": "flash_sca"}
+
+
+def test_large_batch_equals_chunked_batches(cuda_device):
+    """More batch rows than a grid dimension holds: the result equals the same rows run in pieces."""
+    dev = cuda_device
+    torch.manual_seed(0)
+    B, L, Hq, Hkv, D = 66000, 8, 2, 1, 32
+    q = torch.randn(B, L, Hq, D, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(B, L, Hkv, D, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(B, L, Hkv, D, device=dev, dtype=torch.bfloat16)
+    y, lse = xattn.causal_flash_attn_fwd(q, k, v)
+    dy = torch.randn_like(y)
+    grads = xattn.causal_flash_attn_bwd(dy, q, k, v, y, lse)
+    for lo in (0, 40000):
+        hi = min(lo + 40000, B)
+        ys, ls = xattn.causal_flash_attn_fwd(q[lo:hi], k[lo:hi], v[lo:hi])
+        assert torch.equal(ys, y[lo:hi]) and torch.equal(ls, lse[lo:hi])
+        gs = xattn.causal_flash_attn_bwd(dy[lo:hi], q[lo:hi], k[lo:hi], v[lo:hi], ys, ls)
+        for a, b in zip(gs, grads):
+            assert torch.equal(a, b[lo:hi])
+    ref = O.attention(q[:64].double().cpu(), k[:64].double().cpu(), v[:64].double().cpu())
+    torch.testing.assert_close(y[:64].cpu().double(), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("operation", OPS)
+@pytest.mark.parametrize("length", (4096, 65536))
+def test_long_sequences_on_sampled_rows(operation, length, cuda_device):
+    """Sampled query rows against all keys; the gradient of those rows alone (sparse dO) is checked on
+    the full-sized dq, dk, dv."""
+    dev = cuda_device
+    dtype = torch.bfloat16
+    span = 255
+    gen = torch.Generator().manual_seed(length)
+    H, Hkv, D = 4, 2, 64
+    q = F.normalize(torch.randn(1, length, H, D, generator=gen), dim=-1).to(dev, dtype).requires_grad_()
+    k = F.normalize(torch.randn(1, length, Hkv, D, generator=gen), dim=-1).to(dev, dtype).requires_grad_()
+    v = (F.silu(torch.randn(1, length, Hkv, D, generator=gen)) + 0.1).to(dev, dtype).requires_grad_()
+    rows = torch.tensor(sorted({0, 1, 127, 128, 191, 192, 255, 256, 257, 511, 512, length // 2, length - 2, length - 1}))
+    kw = {"window": dict(window_size=span), "chunk": dict(chunk_size=span)}.get(operation, {})
+    y = getattr(xattn, OPS[operation])(q, k, v, **kw)
+    assert torch.isfinite(y).all()
+    sel = y[:, rows.to(dev)]
+    refs = [t.detach().double().cpu().requires_grad_() for t in (q, k, v)]
+    qp = rows[:, None]
+    kp = torch.arange(length)[None, :]
+    left = torch.ones_like(kp, dtype=torch.bool).expand(len(rows), -1)
+    if operation == "window":
+        left = kp >= qp - span
+    elif operation == "chunk":
+        left = kp >= qp // span * span - span
+    mask = (left & (kp <= qp))[None]
+    expected = O.attention_from_mask(refs[0][:, rows], refs[1], refs[2], mask, D ** -0.5)
+    torch.testing.assert_close(sel.detach().cpu(), expected.detach().to(dtype), atol=O.ATOL[dtype], rtol=O.RTOL[dtype])
+    dy = (torch.randn(sel.shape, generator=gen) / sel.numel() ** 0.5).to(dev, dtype)
+    grads = torch.autograd.grad(sel, (q, k, v), dy)
+    want = torch.autograd.grad(expected, refs, dy.double().cpu())
+    for g_, w_ in zip(grads, want):
+        torch.testing.assert_close(g_.cpu(), w_.to(dtype), atol=O.GRAD_ATOL[dtype], rtol=O.RTOL[dtype])
+
+
+@pytest.mark.parametrize("operation", ("window", "chunk"))
+def test_rounding_bias_identical_keys(operation, cuda_device):
+    """Identical key rows make dQ exactly zero whatever V and Q are; level 1 must not accumulate a bias."""
+    dev = cuda_device
+    q = torch.zeros(1, 128, 1, 64, dtype=torch.bfloat16, device=dev, requires_grad=True)
+    k = torch.ones_like(q, requires_grad=True)
+    values = torch.full_like(q, -1.0078125)
+    values[:, :32] = -1.0
+    fn = getattr(xattn, OPS[operation])
+    options = {"chunk_size": 64} if operation == "chunk" else {"window_size": 127}
+    dy = torch.zeros_like(q)
+    dy[:, -1] = -1
+    total = torch.zeros_like(q, dtype=torch.float64)
+    for step in range(4):
+        v = values.roll(step, 1).detach().requires_grad_()
+        y = fn(q, k, v, **options, high_precision_level=1)
+        dq = torch.autograd.grad(y, q, dy)[0]
+        assert y.dtype == torch.bfloat16 and dq.abs().max() <= 1e-4
+        total += dq.double()
+    assert total.abs().max() <= 1e-3
+
+
+@pytest.mark.parametrize("operation,reset", (("window", False), ("chunk", False), ("chunk", True)))
+@pytest.mark.parametrize("level", (0, 1))
+@pytest.mark.parametrize("kv_heads", (1, 2, 4))
+def test_live_bos_previous_gradients(operation, reset, level, kv_heads, cuda_device):
+    """Previous K/V that the current queries really read receive gradients of the right size."""
+    dtype = torch.bfloat16
+    case = Case("live-bos-previous", 129, 129, 128, 96, metadata="bos", previous=64, span=64, reset=reset, batch=1)
+    inputs = make_inputs(operation, case, dtype, kv_heads, cuda_device)
+    meta, qi, ki = metadata_for(case, cuda_device)
+    options = {**op_options(operation, case, inputs), **meta}
+    y = getattr(xattn, OPS[operation])(*inputs[:3], **options, high_precision_level=level)
+    dy = torch.randn_like(y)
+    grads = torch.autograd.grad(y, inputs, dy)
+    refs = [t.detach().double().cpu().requires_grad_() for t in inputs]
+    kk, vv = torch.cat((refs[3], refs[1]), 1), torch.cat((refs[4], refs[2]), 1)
+    inc, _ = O.allowed_masks(129, 193, 1, operation, 64, qi.cpu(), ki.cpu(), reset)
+    expected = O.attention_from_mask(refs[0], kk, vv, inc, 128 ** -0.5)
+    want = torch.autograd.grad(expected, refs, dy.double().cpu())
+    for g_, w_ in zip(grads[-2:], want[-2:]):
+        assert w_.norm() > 0, "fixture must exercise live previous K/V"
+        assert g_.dtype == dtype and g_.shape == w_.shape and torch.isfinite(g_).all()
+        assert (g_.double().cpu() - w_).norm() <= 0.02 * w_.norm() + 1e-6
+
+
+@pytest.mark.parametrize("operation", OPS)
+@pytest.mark.parametrize("dims", ((40, 72), (136, 120), (152, 152), (56, 248)))
+@pytest.mark.parametrize("level", (0, 1))
+def test_padded_gqa_gradients(operation, dims, level, cuda_device):
+    """Head dimensions that are not tile multiples, short Q, unit-variance dO: relative norm error of
+    every gradient below 1.5 % (tests/test_high_precision.py:143-164)."""
+    dtype = torch.bfloat16
+    case = Case("padded-gqa", 17, 33, *dims, span=16, batch=1)
+    inputs = make_inputs(operation, case, dtype, 2, cuda_device)
+    options = op_options(operation, case, inputs)
+    name = OPS[operation]
+    y, lse = getattr(xattn, name + "_fwd")(*inputs, **options, high_precision_level=level)
+    gen = torch.Generator().manual_seed(3)
+    dy = torch.randn(y.shape, generator=gen).to(cuda_device, dtype)
+    grads = getattr(xattn, name + "_bwd")(dy, *inputs, y, lse, **options, high_precision_level=level)[:3]
+    refs = [t.detach().double().cpu().requires_grad_() for t in inputs]
+    inc, _ = O.allowed_masks(17, 33, 1, operation, 16)
+    expected = O.attention_from_mask(*refs, inc, dims[0] ** -0.5)
+    want = torch.autograd.grad(expected, refs, dy.double().cpu())
+    for g_, w_ in zip(grads, want):
+        assert g_.dtype == dtype and torch.isfinite(g_).all()
+        assert (g_.double().cpu() - w_).norm() <= 0.015 * w_.norm() + 1e-6
