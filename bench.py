@@ -41,6 +41,10 @@ if ROOT not in sys.path:
 METRIC = "attn fwd+bwd TFLOPS (bf16 causal S=8K D=128), whole job"
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 
+# DRAM bytes (read + write) of one launch per batch row of S=8192, Hq=32, Hkv=8, D=128, from the ncu
+# capture summarised in profiles/ncu_full_causal_small.md
+NCU_DRAM_BYTES_PER_BATCH_ROW = {"fwd": 134.2e6, "bwd_dq": 213.3e6, "bwd_dkv": 194.1e6}
+
 WORKLOADS = {
     # name: (B, S, Hq, Hkv, D, packed segments?, description)
     "causal_c2": dict(B=4, S=8192, Hq=32, Hkv=8, D=128, segments=True,
@@ -321,7 +325,10 @@ def run_ours(args, w):
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak,
-                         "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                         "unit": "TFLOP/s", "frac": achieved / peak,
+                         "traffic": NCU_DRAM_BYTES_PER_BATCH_ROW.get(dominant, 0) * w["B"] or None,
+                         "traffic_source": "ncu dram__bytes_read+write of one launch at B=1 S=8192 dense "
+                                           "(profiles/ncu_full_causal_small.md), times the batch size",
                          "peak_source": f"{peak_src} bf16_tflops_sustained (kernel timed inside a long step)",
                          "executed_tflops": kernels[dominant]["executed_tflops"]},
             "kernels": kernels,
