@@ -1,22 +1,22 @@
 // Forward attention for sm_100a.
 //
-// One CTA owns NT tiles of 128 query rows of one (batch, query head) and walks
-// the key tiles their visible-key intervals touch.  Roles (16 warps):
-//   warps 0-3 / 4-7   softmax warpgroup of tile 0 / tile 1 (thread = row)
-//   warps 8-11        correction + epilogue warpgroup (rescales O in TMEM,
-//                     writes y and lse)
+// One CTA owns one tile of 128 query rows of one (batch, query head) and walks the key tiles its
+// visible-key intervals touch.  Roles (16 warps):
+//   warps 0-3 / 4-7   softmax warpgroups: thread = (query row, half of the key tile's 128 columns);
+//                     the two halves exchange their row maxima through shared memory
+//   warps 8-11        correction + epilogue warpgroup (rescales O in TMEM, writes y and lse)
 //   warp 12           tcgen05.mma issuer (one thread)
 //   warp 13           TMA producer (one thread); also owns the TMEM allocation
-// Per key tile and query tile:  S = Q K^T (operands in shared memory, S in
-// TMEM) -> softmax in registers -> P (16-bit) written over S in TMEM ->
-// O += P V (P from TMEM, V from shared memory, O in TMEM).  The two query
-// tiles alternate on the tensor core so that one's MMAs cover the other's
-// softmax.
+// S has two TMEM buffers, so S = Q K^T of the next key tiles is already running while the softmax of
+// the current one works: softmax in registers -> P (16-bit) into TMEM -> O += P V (P from TMEM, V
+// from shared memory, O in TMEM).  For head dimensions up to 128 P has TMEM columns of its own, so
+// that the next S product never has to wait for a P V product to release its buffer; at 256 the
+// accumulator leaves no room and P is written over its own half of S.
 //
 // Semantics restated from the reference: online softmax in the exp2 domain
-// (csrc/attention/cuda/softmax.h:124-207), rows without a visible key give
-// y = 0 and lse = -inf (csrc/attention/hopper/epilogue_fwd.hpp:474-566),
-// key tiles no row can see are skipped (hopper/mainloop_fwd_sm90_tma_gmma_ws.hpp:1169-1172).
+// (csrc/attention/cuda/softmax.h:124-207), rows without a visible key give y = 0 and lse = -inf
+// (csrc/attention/hopper/epilogue_fwd.hpp:474-566), key tiles no row can see are skipped
+// (hopper/mainloop_fwd_sm90_tma_gmma_ws.hpp:1169-1172).
 #include "common.cuh"
 
 namespace xb {
@@ -34,37 +34,41 @@ struct FwdParams {
   int* status;
 };
 
-template <int HD, int NT>
+template <int HD>
 struct FwdSmem {
   static constexpr int kTileBytes = kBlockM * HD * 2;
-  static constexpr int kStages = (HD <= 128) ? 2 : 1;
-  alignas(1024) uint8_t q[NT][kTileBytes];
-  alignas(1024) uint8_t k[kStages][kTileBytes];
-  alignas(1024) uint8_t v[kStages][kTileBytes];
-  float scale_buf[NT][2][kBlockM];   // rescale factors, double-buffered by iteration parity
-  float final_l[NT][kBlockM];
-  float final_m[NT][kBlockM];
-  uint64_t q_full[NT];
-  uint64_t k_full[kStages], k_empty[kStages];
-  uint64_t v_full[kStages], v_empty[kStages];
-  uint64_t s_full[NT], p_full[NT], o_ready[NT], pv_done[NT], corr_full[NT];
+  static constexpr int kKStages = HD <= 128 ? 3 : 1;
+  static constexpr int kVStages = HD <= 128 ? 2 : 1;
+  static constexpr int kLookahead = HD <= 128 ? 2 : 1;   // S tiles issued ahead of the softmax
+  alignas(1024) uint8_t q[kTileBytes];
+  alignas(1024) uint8_t k[kKStages][kTileBytes];
+  alignas(1024) uint8_t v[kVStages][kTileBytes];
+  float scale_buf[2][kBlockM];       // rescale factors, double-buffered by iteration parity
+  float xmax[2][2][kBlockM];         // row maxima of the two column halves, by iteration parity
+  float final_l[2][kBlockM];
+  float final_m[kBlockM];
+  uint64_t q_full;
+  uint64_t k_full[kKStages], k_empty[kKStages];
+  uint64_t v_full[kVStages], v_empty[kVStages];
+  uint64_t s_full[2], p_full[2], max_x[2];
+  uint64_t o_ready, pv_done, corr_full, final_full;
   uint32_t tmem_base;
   int abort_flag;
 };
 
-
-
-// T: __nv_bfloat16 or __half.  HD: padded head dimension of the shared-memory
-// tiles (64, 128 or 256).  NT: query tiles per CTA.  HP: high-precision softmax.
-template <typename T, int HD, int NT, bool HP>
+// T: __nv_bfloat16 or __half.  HD: padded head dimension of the shared-memory tiles (64, 128 or 256).
+// HP: high-precision softmax.
+template <typename T, int HD, bool HP>
 __global__ void __launch_bounds__(512, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
-  using Smem = FwdSmem<HD, NT>;
-  constexpr int kStages = Smem::kStages;
+  using Smem = FwdSmem<HD>;
+  constexpr bool kAliasP = HD > 128;                    // P over S instead of in columns of its own
+  constexpr int kKStages = Smem::kKStages, kVStages = Smem::kVStages, kLA = Smem::kLookahead;
   constexpr int kBoxBytes = kBlockM * 64 * 2;          // one 64-column box of a tile
   constexpr uint32_t kTmemCols = 512;
-  // TMEM columns: S/P of tile t at t*128; O of tile t at NT*128 + t*HD.
+  // TMEM columns: S buffers at 0 / 128, O at 256, P buffers (64 packed columns each) at 384 / 448
+  constexpr uint32_t cS = 0, cO = 256, cP = 384;
   constexpr int kFormat = Pack2<T>::kFormat;
 
   extern __shared__ uint8_t smem_raw[];
@@ -76,56 +80,38 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
   // ---- which work item -----------------------------------------------------
   const int G = p.Hq / p.Hkv;
-  const int n_groups = (p.nQT + NT - 1) / NT;     // groups of NT query tiles
-  const int per_bk = n_groups * G;
+  const int per_bk = p.nQT * G;
   const int bk = blockIdx.x / per_bk;
   const int rem = blockIdx.x - bk * per_bk;
-  const int grp = n_groups - 1 - rem / G;          // later (heavier under causal masks) groups first
-  const int h = (bk % p.Hkv) * G + (rem % G);
+  const int qt = p.nQT - 1 - rem / G;                 // later (heavier under causal masks) tiles first
   const int kvh = bk % p.Hkv;
+  const int h = kvh * G + (rem % G);
   const int b = bk / p.Hkv;
 
-  // key-tile range of each query tile
-  int n_lo[NT], n_hi[NT], full_lo[NT], full_hi[NT];
-  int u_lo = 0x7fffffff, u_hi = 0;
-#pragma unroll
-  for (int t = 0; t < NT; ++t) {
-    const int qt = grp * NT + t;
-    n_lo[t] = n_hi[t] = 0;
-    full_lo[t] = 0x7fffffff;
-    full_hi[t] = 0;
-    if (qt < p.nQT) {
-      const TileInfo ti = p.q_tiles[(size_t)b * p.nQT + qt];
-      if (ti.max_hi > ti.min_lo) {
-        n_lo[t] = ti.min_lo / kBlockN;
-        n_hi[t] = (ti.max_hi + kBlockN - 1) / kBlockN;
-        full_lo[t] = ti.max_lo;
-        full_hi[t] = ti.min_hi;
-        u_lo = min(u_lo, n_lo[t]);
-        u_hi = max(u_hi, n_hi[t]);
-      }
+  int n_lo = 0, n_hi = 0, full_lo = 0x7fffffff, full_hi = 0;
+  {
+    const TileInfo ti = p.q_tiles[(size_t)b * p.nQT + qt];
+    if (ti.max_hi > ti.min_lo) {
+      n_lo = ti.min_lo / kBlockN;
+      n_hi = (ti.max_hi + kBlockN - 1) / kBlockN;
+      full_lo = ti.max_lo;
+      full_hi = ti.min_hi;
     }
   }
-  if (u_hi == 0) u_lo = 0;
+  const int iters = n_hi - n_lo;
 
   // ---- set-up ----------------------------------------------------------------
   if (tid == 0) {
     // an earlier CTA gave up: do not pile on
     s.abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 2 : 0;
-    for (int t = 0; t < NT; ++t) {
-      mbar_init(&s.q_full[t], 1);
-      mbar_init(&s.s_full[t], 1);
-      mbar_init(&s.p_full[t], 4);
-      mbar_init(&s.o_ready[t], 4);
-      mbar_init(&s.pv_done[t], 1);
-      mbar_init(&s.corr_full[t], 4);
-    }
-    for (int i = 0; i < kStages; ++i) {
-      mbar_init(&s.k_full[i], 1);
-      mbar_init(&s.k_empty[i], 1);
-      mbar_init(&s.v_full[i], 1);
-      mbar_init(&s.v_empty[i], 1);
-    }
+    mbar_init(&s.q_full, 1);
+    for (int i = 0; i < kKStages; ++i) { mbar_init(&s.k_full[i], 1); mbar_init(&s.k_empty[i], 1); }
+    for (int i = 0; i < kVStages; ++i) { mbar_init(&s.v_full[i], 1); mbar_init(&s.v_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&s.s_full[i], 1); mbar_init(&s.p_full[i], 8); mbar_init(&s.max_x[i], 8); }
+    mbar_init(&s.o_ready, 4);
+    mbar_init(&s.pv_done, 1);
+    mbar_init(&s.corr_full, 4);
+    mbar_init(&s.final_full, 8);
     fence_mbar_init();
   }
   if (warp == 13) {
@@ -142,169 +128,152 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const int nbox_v = (p.V + 63) / 64;
   const int ksteps_qk = (p.D + 15) / 16;
   const int v_pad = (p.V + 15) & ~15;
-
   const bool dead = s.abort_flag != 0;
+
+  // 512 threads start with 128 registers each
+  if (warp < 8) setmaxnreg_inc<152>(); else if (warp < 12) setmaxnreg_dec<104>(); else setmaxnreg_dec<48>();
+
   if (dead) {
     // nothing to do
-  } else if (warp < 4 * NT) {
+  } else if (warp < 8) {
     // =========================== softmax warpgroups ===========================
-    setmaxnreg_inc<NT == 2 ? 192 : 216>();
-    const int t = warp >> 2;
+    const int hf = warp >> 2;                   // which half of the key-tile columns
     const int r = tid & 127;
-    const int qt = grp * NT + t;
     const int row = qt * kBlockM + r;
     int lo = 0, hi = 0;
-    if (qt < p.nQT && row < p.Lq) {
+    if (row < p.Lq) {
       lo = p.row_lo[(size_t)b * p.Lq + row];
       hi = p.row_hi[(size_t)b * p.Lq + row];
     }
-    const uint32_t t_s = tmem + ((uint32_t)((warp & 3) * 32) << 16) + t * 128;
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const float c_log2 = p.scale * 1.4426950408889634f;
     float m = -INFINITY, l = 0.f;
-    const int iters = n_hi[t] - n_lo[t];
     bool ok = true;
     for (int j = 0; j < iters && ok; ++j) {
-      const int col0 = (n_lo[t] + j) * kBlockN;
-      ok = mbar_wait(ctx, &s.s_full[t], j & 1, 10 + t);
+      const int buf = j & 1;
+      const int col0 = (n_lo + j) * kBlockN + hf * 64;
+      const uint32_t t_s = tmem + lane_off + cS + buf * 128 + hf * 64;
+      ok = mbar_wait(ctx, &s.s_full[buf], (j >> 1) & 1, 10);
       if (!ok) break;
       tc_fence_after();
-      float sc[128];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_x32(t_s + c * 32, reinterpret_cast<uint32_t*>(sc) + c * 32);
+      float sc[64];
+      tmem_ld_x32(t_s, reinterpret_cast<uint32_t*>(sc));
+      tmem_ld_x32(t_s + 32, reinterpret_cast<uint32_t*>(sc) + 32);
       tc_wait_ld();
-      const bool tile_full = (col0 >= full_lo[t]) && (col0 + kBlockN <= full_hi[t]);
+      const bool tile_full = ((n_lo + j) * kBlockN >= full_lo) && ((n_lo + j + 1) * kBlockN <= full_hi);
       if (!tile_full) {
         const int rl = lo - col0, rh = hi - col0;
 #pragma unroll
-        for (int c = 0; c < 128; ++c) sc[c] = (c >= rl && c < rh) ? sc[c] : -INFINITY;
+        for (int c = 0; c < 64; ++c) sc[c] = (c >= rl && c < rh) ? sc[c] : -INFINITY;
       }
       float mxa = max3(sc[0], sc[1], sc[2]), mxb = max3(sc[3], sc[4], sc[5]);
       float mxc = max3(sc[6], sc[7], sc[8]), mxd = max3(sc[9], sc[10], sc[11]);
 #pragma unroll
-      for (int c = 12; c < 124; c += 8) {
+      for (int c = 12; c < 60; c += 8) {
         mxa = max3(mxa, sc[c], sc[c + 1]);
         mxb = max3(mxb, sc[c + 2], sc[c + 3]);
         mxc = max3(mxc, sc[c + 4], sc[c + 5]);
         mxd = max3(mxd, sc[c + 6], sc[c + 7]);
       }
-      mxa = max3(mxa, sc[124], sc[125]);
-      mxb = max3(mxb, sc[126], sc[127]);
-      const float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
+      mxa = max3(mxa, sc[60], sc[61]);
+      mxb = max3(mxb, sc[62], sc[63]);
+      float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
+      // the row maximum over both halves
+      s.xmax[buf][hf][r] = mx;
+      mbar_arrive_warp(&s.max_x[buf]);
+      ok = mbar_wait(ctx, &s.max_x[buf], (j >> 1) & 1, 11);
+      if (!ok) break;
+      mx = fmaxf(mx, s.xmax[buf][hf ^ 1][r]);
       float m_new = fmaxf(m, mx);
       if (!HP) {
-        // keep the old reference while the maximum grew by less than 2^8: the
-        // accumulator is then left untouched and P stays below 256
+        // keep the old reference while the maximum grew by less than 2^8: the accumulator is then
+        // left untouched and P stays below 256
         if (m != -INFINITY && (m_new - m) * c_log2 <= 8.f) m_new = m;
       }
       float factor = 1.f;
       if (m != -INFINITY && m_new != m) factor = HP ? exp2f((m - m_new) * c_log2) : ex2_approx((m - m_new) * c_log2);
-      if (j > 0) {
-        s.scale_buf[t][j & 1][r] = factor;
-        mbar_arrive_warp(&s.corr_full[t]);
+      if (hf == 0 && j > 0) {
+        s.scale_buf[buf][r] = factor;
+        mbar_arrive_warp(&s.corr_full);
       }
       m = m_new;
       const float m_ref = (m == -INFINITY) ? 0.f : m;
       const float neg_mc = -m_ref * c_log2;
-      const uint32_t t_p = t_s;   // P overwrites the first 64 columns of S
+      uint32_t pk[32];
       float sum = 0.f;
       if (HP) {
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c0 = 0; c0 < 128; c0 += 32) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            const float p0 = exp2f(__fmul_rn(__fsub_rn(sc[c0 + c], m_ref), c_log2));
-            const float p1 = exp2f(__fmul_rn(__fsub_rn(sc[c0 + c + 1], m_ref), c_log2));
-            sum4[(c >> 1) & 3] += p0 + p1;
-            pk[c >> 1] = Pack2<T>::pack(p0, p1);
-          }
-          tmem_st_x16(t_p + (c0 >> 1), pk);
+        for (int c = 0; c < 64; c += 2) {
+          const float p0 = exp2f(__fmul_rn(__fsub_rn(sc[c], m_ref), c_log2));
+          const float p1 = exp2f(__fmul_rn(__fsub_rn(sc[c + 1], m_ref), c_log2));
+          sum4[(c >> 1) & 3] += p0 + p1;
+          pk[c >> 1] = Pack2<T>::pack(p0, p1);
         }
         sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       } else {
         const float2 cc = make_float2(c_log2, c_log2), nm = make_float2(neg_mc, neg_mc);
         float2 s2a = make_float2(0.f, 0.f), s2b = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int c0 = 0; c0 < 128; c0 += 32) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int c = 0; c < 32; c += 4) {
-            const float2 pa = ex2_pair_sfu(fma2(make_float2(sc[c0 + c], sc[c0 + c + 1]), cc, nm));
-            const float2 pb = ex2_pair_sfu(fma2(make_float2(sc[c0 + c + 2], sc[c0 + c + 3]), cc, nm));
-            s2a = add2(s2a, pa);
-            s2b = add2(s2b, pb);
-            pk[c >> 1] = Pack2<T>::pack(pa.x, pa.y);
-            pk[(c >> 1) + 1] = Pack2<T>::pack(pb.x, pb.y);
-          }
-          tmem_st_x16(t_p + (c0 >> 1), pk);
+        for (int c = 0; c < 64; c += 4) {
+          const float2 pa = ex2_pair_sfu(fma2(make_float2(sc[c], sc[c + 1]), cc, nm));
+          const float2 pb = ex2_pair_sfu(fma2(make_float2(sc[c + 2], sc[c + 3]), cc, nm));
+          s2a = add2(s2a, pa);
+          s2b = add2(s2b, pb);
+          pk[c >> 1] = Pack2<T>::pack(pa.x, pa.y);
+          pk[(c >> 1) + 1] = Pack2<T>::pack(pb.x, pb.y);
         }
         const float2 s2 = add2(s2a, s2b);
         sum = s2.x + s2.y;
       }
+      // 32 packed columns per half: next to each other in the P buffer, or (HD = 256) over the first
+      // 32 of the half's own S columns
+      tmem_st_x32(kAliasP ? t_s : tmem + lane_off + cP + buf * 64 + hf * 32, pk);
       l = l * factor + sum;
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive_warp(&s.p_full[t]);
+      mbar_arrive_warp(&s.p_full[buf]);
     }
     // hand the row statistics to the epilogue
-    s.final_l[t][r] = l;
-    s.final_m[t][r] = m;
-    mbar_arrive_warp(&s.corr_full[t]);
-  } else if (warp < 4 * NT + 4) {
+    s.final_l[hf][r] = l;
+    if (hf == 0) s.final_m[r] = m;
+    mbar_arrive_warp(&s.final_full);
+  } else if (warp < 12) {
     // ======================= correction + epilogue warpgroup =======================
-    // launch allocation is 128 registers per thread: shrink below it, grow above it
-    if (NT == 2) setmaxnreg_dec<80>(); else setmaxnreg_inc<152>();
     const int r = tid & 127;
+    const int row = qt * kBlockM + r;
+    const bool live = row < p.Lq;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
-    for (int n = u_lo; n < u_hi && ok; ++n) {
+    for (int j = 1; j < iters && ok; ++j) {
+      ok = mbar_wait(ctx, &s.corr_full, (j - 1) & 1, 20);
+      if (!ok) break;
+      const float f = s.scale_buf[j & 1][r];
+      ok = mbar_wait(ctx, &s.pv_done, (j - 1) & 1, 22);
+      if (!ok) break;
+      tc_fence_after();
+      if (__any_sync(0xffffffffu, f != 1.f)) {
+        const uint32_t t_o = tmem + lane_off + cO;
+        for (int c0 = 0; c0 < v_pad; c0 += 32) {
+          uint32_t o[32];
+          tmem_ld_x32(t_o + c0, o);
+          tc_wait_ld();
 #pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        if (n < n_lo[t] || n >= n_hi[t]) continue;
-        const int j = n - n_lo[t];
-        if (j == 0) continue;
-        ok = mbar_wait(ctx, &s.corr_full[t], (j - 1) & 1, 20 + t);
-        if (!ok) break;
-        const float f = s.scale_buf[t][j & 1][r];
-        ok = mbar_wait(ctx, &s.pv_done[t], (j - 1) & 1, 22 + t);
-        if (!ok) break;
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, f != 1.f)) {
-          const uint32_t t_o = tmem + lane_off + NT * 128 + t * HD;
-          for (int c0 = 0; c0 < v_pad; c0 += 32) {
-            uint32_t o[32];
-            tmem_ld_x32(t_o + c0, o);
-            tc_wait_ld();
-#pragma unroll
-            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f);
-            tmem_st_x32(t_o + c0, o);
-          }
-          tc_wait_st();
+          for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * f);
+          tmem_st_x32(t_o + c0, o);
         }
-        tc_fence_before();
-        mbar_arrive_warp(&s.o_ready[t]);
+        tc_wait_st();
       }
+      tc_fence_before();
+      mbar_arrive_warp(&s.o_ready);
     }
     // epilogue: y = O / l, lse = ln2 * (m * c + log2 l)
-#pragma unroll
-    for (int t = 0; t < NT; ++t) {
-      if (!ok) break;
-      const int qt = grp * NT + t;
-      const int iters = n_hi[t] - n_lo[t];
-      // final statistics are arrival number `max(iters,1) - 1` on corr_full[t]
-      const int arrivals_before = iters > 0 ? iters - 1 : 0;
-      ok = mbar_wait(ctx, &s.corr_full[t], arrivals_before & 1, 24 + t);
-      if (!ok) break;
-      if (iters > 0) {
-        ok = mbar_wait(ctx, &s.pv_done[t], (iters - 1) & 1, 26 + t);
-        if (!ok) break;
-      }
+    if (ok) ok = mbar_wait(ctx, &s.final_full, 0, 24);
+    if (ok && iters > 0) ok = mbar_wait(ctx, &s.pv_done, (iters - 1) & 1, 26);
+    if (ok) {
       tc_fence_after();
-      const int row = qt * kBlockM + r;
-      const float l = s.final_l[t][r];
-      const float m = s.final_m[t][r];
-      const bool live = (qt < p.nQT) && (row < p.Lq);
+      const float l = s.final_l[0][r] + s.final_l[1][r];
+      const float m = s.final_m[r];
       const bool has = l > 0.f && iters > 0;
       float inv = 0.f;
       if (has) inv = HP ? __frcp_rn(l) : __fdividef(1.f, l);
@@ -313,7 +282,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         p.lse[((size_t)b * p.Hq + h) * p.Lq + row] =
             has ? (m * c_log2 + log2f(l)) * 0.6931471805599453f : -INFINITY;
       }
-      const uint32_t t_o = tmem + lane_off + NT * 128 + t * HD;
+      const uint32_t t_o = tmem + lane_off + cO;
       T* y_row = reinterpret_cast<T*>(p.y) + (((size_t)b * p.Lq + (live ? row : 0)) * p.Hq + h) * p.V;
       float* ys_row = p.y_state ? p.y_state + (((size_t)b * p.Lq + (live ? row : 0)) * p.Hq + h) * p.V : nullptr;
       for (int c0 = 0; c0 < v_pad; c0 += 32) {
@@ -329,140 +298,98 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
           for (int c = 0; c < 32; c += 8) {
             if (c0 + c < p.V) {
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[c + e]) * inv;
               uint4 pk;
-              pk.x = Pack2<T>::pack(__uint_as_float(o[c + 0]) * inv, __uint_as_float(o[c + 1]) * inv);
-              pk.y = Pack2<T>::pack(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
-              pk.z = Pack2<T>::pack(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
-              pk.w = Pack2<T>::pack(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+              pk.x = Pack2<T>::pack(f[0], f[1]);
+              pk.y = Pack2<T>::pack(f[2], f[3]);
+              pk.z = Pack2<T>::pack(f[4], f[5]);
+              pk.w = Pack2<T>::pack(f[6], f[7]);
               *reinterpret_cast<uint4*>(y_row + c0 + c) = pk;
               if (ys_row) {
-                float4 a = make_float4(__uint_as_float(o[c + 0]) * inv, __uint_as_float(o[c + 1]) * inv,
-                                       __uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
-                float4 bq = make_float4(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv,
-                                        __uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
-                *reinterpret_cast<float4*>(ys_row + c0 + c) = a;
-                *reinterpret_cast<float4*>(ys_row + c0 + c + 4) = bq;
+                *reinterpret_cast<float4*>(ys_row + c0 + c) = make_float4(f[0], f[1], f[2], f[3]);
+                *reinterpret_cast<float4*>(ys_row + c0 + c + 4) = make_float4(f[4], f[5], f[6], f[7]);
               }
             }
           }
         }
       }
     }
-  } else {
-    // ============================ MMA issuer / TMA producer ============================
-    setmaxnreg_dec<48>();
-    if (warp == 4 * NT + 4 && lane == 0) {
-      // ------------------------------ MMA issuer ------------------------------
-      const uint32_t idesc_qk = make_idesc(kBlockM, kBlockN, kFormat, 0, 0);
-      const uint32_t idesc_pv = make_idesc(kBlockM, v_pad, kFormat, 0, 1);
-      bool ok = true;
-      auto issue_qk = [&](int t, int stage) {
-        const uint32_t qa = smem_u32(s.q[t]);
-        const uint32_t ka = smem_u32(s.k[stage]);
-        const uint32_t d = tmem + t * 128;
-        for (int js = 0; js < ksteps_qk; ++js) {
-          const uint32_t off = (js >> 2) * kBoxBytes + (js & 3) * 32;
-          umma_ss(d, make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024), idesc_qk, js > 0);
-        }
-        umma_commit(&s.s_full[t]);
-      };
-      auto issue_pv = [&](int t, int stage, bool accumulate) {
-        const uint32_t va = smem_u32(s.v[stage]);
-        const uint32_t d = tmem + NT * 128 + t * HD;
-        const uint32_t pa = tmem + t * 128;
+  } else if (warp == 12 && lane == 0 && iters > 0) {
+    // ------------------------------ MMA issuer ------------------------------
+    const uint32_t idesc_qk = make_idesc(kBlockM, kBlockN, kFormat, 0, 0);
+    const uint32_t idesc_pv = make_idesc(kBlockM, v_pad, kFormat, 0, 1);
+    auto issue_qk = [&](int i) {          // S of key tile i -> buffer i & 1
+      const uint32_t ka = smem_u32(s.k[i % kKStages]);
+      const uint32_t d = tmem + cS + (i & 1) * 128;
+      for (int js = 0; js < ksteps_qk; ++js) {
+        const uint32_t off = (js >> 2) * kBoxBytes + (js & 3) * 32;
+        umma_ss(d, make_smem_desc(smem_u32(s.q) + off, 16, 1024), make_smem_desc(ka + off, 16, 1024), idesc_qk, js > 0);
+      }
+      umma_commit(&s.s_full[i & 1]);
+      umma_commit(&s.k_empty[i % kKStages]);
+    };
+    bool ok = mbar_wait(ctx, &s.q_full, 0, 30);
+    for (int i = 0; i < kLA && i < iters && ok; ++i) {
+      ok = mbar_wait(ctx, &s.k_full[i % kKStages], (i / kKStages) & 1, 31);
+      if (ok) { tc_fence_after(); issue_qk(i); }
+    }
+    for (int n = 0; n < iters && ok; ++n) {
+      const int vs = n % kVStages;
+      ok = mbar_wait(ctx, &s.v_full[vs], (n / kVStages) & 1, 32);
+      if (ok) ok = mbar_wait(ctx, &s.p_full[n & 1], (n >> 1) & 1, 33);
+      if (ok && n > 0) ok = mbar_wait(ctx, &s.o_ready, (n - 1) & 1, 34);
+      if (!ok) break;
+      tc_fence_after();
+      {
+        // O += P V
+        const uint32_t va = smem_u32(s.v[vs]);
 #pragma unroll
         for (int js = 0; js < kBlockN / 16; ++js) {
-          umma_ts(d, pa + js * 8, make_smem_desc(va + js * 2048, kBoxBytes, 1024), idesc_pv,
-                  (accumulate || js > 0) ? 1u : 0u);
+          const uint32_t a_col = kAliasP ? tmem + cS + (n & 1) * 128 + (js >> 2) * 64 + (js & 3) * 8
+                                         : tmem + cP + (n & 1) * 64 + js * 8;
+          umma_ts(tmem + cO, a_col, make_smem_desc(va + js * 2048, kBoxBytes, 1024), idesc_pv,
+                  (n > 0 || js > 0) ? 1u : 0u);
         }
-        umma_commit(&s.pv_done[t]);
-      };
-      if (u_hi > u_lo) {
-        // prologue: S for the first key tile
-        ok = mbar_wait(ctx, &s.k_full[0], 0, 30);
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-          if (ok && u_lo >= n_lo[t] && u_lo < n_hi[t]) {
-            ok = mbar_wait(ctx, &s.q_full[t], 0, 31);
-            if (ok) { tc_fence_after(); issue_qk(t, 0); }
-          }
-        }
-        if (ok) umma_commit(&s.k_empty[0]);
-        for (int n = u_lo; n < u_hi && ok; ++n) {
-          const int i = n - u_lo;
-          const int st = i % kStages;
-          const int st_next = (i + 1) % kStages;
-          bool v_waited = false, k_waited = false;
-#pragma unroll
-          for (int t = 0; t < NT; ++t) {
-            if (!ok) break;
-            if (n >= n_lo[t] && n < n_hi[t]) {
-              const int j = n - n_lo[t];
-              if (!v_waited) { ok = mbar_wait(ctx, &s.v_full[st], (i / kStages) & 1, 32); v_waited = true; }
-              if (ok) ok = mbar_wait(ctx, &s.p_full[t], j & 1, 33);
-              if (ok && j > 0) ok = mbar_wait(ctx, &s.o_ready[t], (j - 1) & 1, 34);
-              if (!ok) break;
-              tc_fence_after();
-              issue_pv(t, st, j > 0);
-            }
-            if (n + 1 < u_hi && n + 1 >= n_lo[t] && n + 1 < n_hi[t]) {
-              if (!k_waited) { ok = mbar_wait(ctx, &s.k_full[st_next], ((i + 1) / kStages) & 1, 35); k_waited = true; }
-              if (ok && n + 1 == n_lo[t]) ok = mbar_wait(ctx, &s.q_full[t], 0, 36);
-              if (!ok) break;
-              tc_fence_after();
-              issue_qk(t, st_next);
-            }
-          }
-          if (!ok) break;
-          // stages are released when every MMA issued so far has finished; a
-          // stage no tile used still has to be waited for before its release
-          if (!v_waited) ok = mbar_wait(ctx, &s.v_full[st], (i / kStages) & 1, 37);
-          if (ok) umma_commit(&s.v_empty[st]);
-          if (ok && n + 1 < u_hi) {
-            if (!k_waited) ok = mbar_wait(ctx, &s.k_full[st_next], ((i + 1) / kStages) & 1, 38);
-            if (ok) umma_commit(&s.k_empty[st_next]);
-          }
-        }
+        umma_commit(&s.pv_done);
+        umma_commit(&s.v_empty[vs]);
       }
-    } else if (warp == 4 * NT + 5 && lane == 0) {
-      // ------------------------------ TMA producer ------------------------------
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
-      bool ok = true;
-      auto load_k = [&](int n, int stage) {
-        mbar_arrive_expect_tx(&s.k_full[stage], nbox_qk * kBoxBytes);
+      const int i = n + kLA;
+      if (i < iters) {
+        ok = mbar_wait(ctx, &s.k_full[i % kKStages], (i / kKStages) & 1, 35);
+        if (!ok) break;
+        tc_fence_after();
+        issue_qk(i);
+      }
+    }
+  } else if (warp == 13 && lane == 0 && iters > 0) {
+    // ------------------------------ TMA producer ------------------------------
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_q);
+    mbar_arrive_expect_tx(&s.q_full, nbox_qk * kBoxBytes);
+    for (int bx = 0; bx < nbox_qk; ++bx)
+      tma_load_4d(s.q + bx * kBoxBytes, &tm_q, &s.q_full, bx * 64, h, qt * kBlockM, b);
+    bool ok = true;
+    // K runs kLA tiles ahead of V, the order in which the MMA thread consumes them
+    for (int i = 0; i < iters + kLA && ok; ++i) {
+      if (i < iters) {
+        const int st = i % kKStages;
+        if (i >= kKStages) ok = mbar_wait(ctx, &s.k_empty[st], ((i / kKStages) - 1) & 1, 40);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&s.k_full[st], nbox_qk * kBoxBytes);
         for (int bx = 0; bx < nbox_qk; ++bx)
-          tma_load_4d(s.k[stage] + bx * kBoxBytes, &tm_k, &s.k_full[stage], bx * 64, kvh, n * kBlockN, b);
-      };
-      auto load_v = [&](int n, int stage) {
-        mbar_arrive_expect_tx(&s.v_full[stage], nbox_v * kBoxBytes);
+          tma_load_4d(s.k[st] + bx * kBoxBytes, &tm_k, &s.k_full[st], bx * 64, kvh, (n_lo + i) * kBlockN, b);
+      }
+      const int iv = i - kLA;
+      if (iv >= 0) {
+        const int st = iv % kVStages;
+        if (iv >= kVStages) ok = mbar_wait(ctx, &s.v_empty[st], ((iv / kVStages) - 1) & 1, 41);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&s.v_full[st], nbox_v * kBoxBytes);
         for (int bx = 0; bx < nbox_v; ++bx)
-          tma_load_4d(s.v[stage] + bx * kBoxBytes, &tm_v, &s.v_full[stage], bx * 64, kvh, n * kBlockN, b);
-      };
-      if (u_hi > u_lo) {
-        // first K tile, then the query tiles, then the rest of the stream
-        load_k(u_lo, 0);
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-          if (n_hi[t] > n_lo[t]) {
-            mbar_arrive_expect_tx(&s.q_full[t], nbox_qk * kBoxBytes);
-            for (int bx = 0; bx < nbox_qk; ++bx)
-              tma_load_4d(s.q[t] + bx * kBoxBytes, &tm_q, &s.q_full[t], bx * 64, h, (grp * NT + t) * kBlockM, b);
-          }
-        }
-        for (int n = u_lo; n < u_hi && ok; ++n) {
-          const int i = n - u_lo;
-          const int st = i % kStages;
-          if (i > 0) {
-            if (i >= kStages) ok = mbar_wait(ctx, &s.k_empty[st], ((i / kStages) - 1) & 1, 40);
-            if (!ok) break;
-            load_k(n, st);
-          }
-          if (i >= kStages) ok = mbar_wait(ctx, &s.v_empty[st], ((i / kStages) - 1) & 1, 41);
-          if (!ok) break;
-          load_v(n, st);
-        }
+          tma_load_4d(s.v[st] + bx * kBoxBytes, &tm_v, &s.v_full[st], bx * 64, kvh, (n_lo + iv) * kBlockN, b);
       }
     }
   }
@@ -485,9 +412,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
-template <typename T, int HD, int NT, bool HP>
+template <typename T, int HD, bool HP>
 static int launch_fwd(const XattnFwdArgs& a, const FwdParams& p, cudaStream_t stream) {
-  using Smem = FwdSmem<HD, NT>;
+  using Smem = FwdSmem<HD>;
   CUtensorMap tq, tk, tv;
   if (make_tile_map(&tq, a.q, a.dtype, a.batch, a.q_len, a.q_heads, a.qk_dim, a.q_strides[0], a.q_strides[1],
                     a.q_strides[2], kBlockM)) return XATTN_E_INVALID;
@@ -496,11 +423,10 @@ static int launch_fwd(const XattnFwdArgs& a, const FwdParams& p, cudaStream_t st
   if (make_tile_map(&tv, a.v, a.dtype, a.batch, a.k_len, a.kv_heads, a.v_dim, a.v_strides[0], a.v_strides[1],
                     a.v_strides[2], kBlockN)) return XATTN_E_INVALID;
   const size_t smem = sizeof(Smem) + 1024;
-  auto kern = fwd_kernel<T, HD, NT, HP>;
+  auto kern = fwd_kernel<T, HD, HP>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_error("cudaFuncSetAttribute(fwd): %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
-  const int n_groups = (p.nQT + NT - 1) / NT;
-  const long long grid = (long long)n_groups * p.Hq * p.B;
+  const long long grid = (long long)p.nQT * p.Hq * p.B;
   if (grid <= 0 || grid > 0x7fffffffLL) { set_error("forward grid out of range"); return XATTN_E_INVALID; }
   {
     ProfileScope prof(kProfFwd, stream);
@@ -514,11 +440,10 @@ static int launch_fwd(const XattnFwdArgs& a, const FwdParams& p, cudaStream_t st
 template <typename T, bool HP>
 static int dispatch_fwd_dim(const XattnFwdArgs& a, const FwdParams& p, cudaStream_t stream) {
   const int hd = (int)(a.qk_dim > a.v_dim ? a.qk_dim : a.v_dim);
-  if (hd <= 64) return launch_fwd<T, 64, 2, HP>(a, p, stream);
-  if (hd <= 128) return launch_fwd<T, 128, 2, HP>(a, p, stream);
-  return launch_fwd<T, 256, 1, HP>(a, p, stream);
+  if (hd <= 64) return launch_fwd<T, 64, HP>(a, p, stream);
+  if (hd <= 128) return launch_fwd<T, 128, HP>(a, p, stream);
+  return launch_fwd<T, 256, HP>(a, p, stream);
 }
-
 
 int fwd_entry(const XattnFwdArgs* a, cudaStream_t stream) {
   if (!a) { set_error("null arguments"); return XATTN_E_INVALID; }
