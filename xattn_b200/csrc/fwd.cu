@@ -5,8 +5,10 @@
 //   warps 0-3 / 4-7   softmax warpgroups: thread = (query row, half of the key tile's 128 columns);
 //                     the two halves exchange their row maxima through shared memory
 //   warps 8-11        correction + epilogue warpgroup (rescales O in TMEM, writes y and lse)
-//   warp 12           tcgen05.mma issuer (one thread)
+//   warp 12           tcgen05.mma issuer of O += P V (one thread)
 //   warp 13           TMA producer (one thread); also owns the TMEM allocation
+//   warp 14           tcgen05.mma issuer of S = Q K^T (one thread): an issuing thread stalls while
+//                     its products run, so two of them keep the tensor pipe fed while one waits
 // S has two TMEM buffers, so S = Q K^T of the next key tiles is already running while the softmax of
 // the current one works: softmax in registers -> P (16-bit) into TMEM -> O += P V (P from TMEM, V
 // from shared memory, O in TMEM).  For head dimensions up to 128 P has TMEM columns of its own, so
@@ -18,6 +20,10 @@
 // (csrc/attention/hopper/epilogue_fwd.hpp:474-566), key tiles no row can see are skipped
 // (hopper/mainloop_fwd_sm90_tma_gmma_ws.hpp:1169-1172).
 #include "common.cuh"
+
+#ifndef XB_FWD_FMA_PAIRS
+#define XB_FWD_FMA_PAIRS 1
+#endif
 
 namespace xb {
 
@@ -39,7 +45,7 @@ struct FwdSmem {
   static constexpr int kTileBytes = kBlockM * HD * 2;
   static constexpr int kKStages = HD <= 128 ? 3 : 1;
   static constexpr int kVStages = HD <= 128 ? 2 : 1;
-  static constexpr int kLookahead = HD <= 128 ? 2 : 1;   // S tiles issued ahead of the softmax
+  static constexpr int kLookahead = HD <= 128 ? 2 : 1;   // K tiles the producer loads ahead of V
   alignas(1024) uint8_t q[kTileBytes];
   alignas(1024) uint8_t k[kKStages][kTileBytes];
   alignas(1024) uint8_t v[kVStages][kTileBytes];
@@ -50,7 +56,7 @@ struct FwdSmem {
   uint64_t q_full;
   uint64_t k_full[kKStages], k_empty[kKStages];
   uint64_t v_full[kVStages], v_empty[kVStages];
-  uint64_t s_full[2], p_full[2], max_x[2];
+  uint64_t s_full[2], s_free[2], p_full[2], max_x[2];
   uint64_t o_ready, pv_done, corr_full, final_full;
   uint32_t tmem_base;
   int abort_flag;
@@ -70,6 +76,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   // TMEM columns: S buffers at 0 / 128, O at 256, P buffers (64 packed columns each) at 384 / 448
   constexpr uint32_t cS = 0, cO = 256, cP = 384;
   constexpr int kFormat = Pack2<T>::kFormat;
+  // of every four pairs of exponentials, how many are computed on the FMA pipe (low precision only)
+  constexpr int kFmaPairs = XB_FWD_FMA_PAIRS;
 
   extern __shared__ uint8_t smem_raw[];
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -107,7 +115,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     mbar_init(&s.q_full, 1);
     for (int i = 0; i < kKStages; ++i) { mbar_init(&s.k_full[i], 1); mbar_init(&s.k_empty[i], 1); }
     for (int i = 0; i < kVStages; ++i) { mbar_init(&s.v_full[i], 1); mbar_init(&s.v_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s.s_full[i], 1); mbar_init(&s.p_full[i], 8); mbar_init(&s.max_x[i], 8); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.s_full[i], 1); mbar_init(&s.p_full[i], 8); mbar_init(&s.max_x[i], 8);
+      // an S buffer is free again once the softmax holds it in registers, or, where P lies over S,
+      // once the P V product has read it
+      mbar_init(&s.s_free[i], kAliasP ? 1 : 8);
+    }
     mbar_init(&s.o_ready, 4);
     mbar_init(&s.pv_done, 1);
     mbar_init(&s.corr_full, 4);
@@ -160,6 +173,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       tmem_ld_x32(t_s, reinterpret_cast<uint32_t*>(sc));
       tmem_ld_x32(t_s + 32, reinterpret_cast<uint32_t*>(sc) + 32);
       tc_wait_ld();
+      if (!kAliasP) {
+        tc_fence_before();
+        mbar_arrive_warp(&s.s_free[buf]);
+      }
       const bool tile_full = ((n_lo + j) * kBlockN >= full_lo) && ((n_lo + j + 1) * kBlockN <= full_hi);
       if (!tile_full) {
         const int rl = lo - col0, rh = hi - col0;
@@ -211,6 +228,25 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           pk[c >> 1] = Pack2<T>::pack(p0, p1);
         }
         sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      } else if (kFmaPairs > 0 && tile_full) {
+        // every element is finite here: a share of the exponentials moves to the FMA pipe, since
+        // the special-function unit (16 results per clock and SM) is what bounds this loop
+        const float2 cc = make_float2(c_log2, c_log2), nm = make_float2(neg_mc, neg_mc);
+        float2 s2a = make_float2(0.f, 0.f), s2b = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int c = 0; c < 64; c += 8) {
+          float2 pr[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 x = fma2(make_float2(sc[c + 2 * e], sc[c + 2 * e + 1]), cc, nm);
+            pr[e] = (e < kFmaPairs) ? ex2_pair_fma(x) : ex2_pair_sfu(x);
+            pk[(c >> 1) + e] = Pack2<T>::pack(pr[e].x, pr[e].y);
+          }
+          s2a = add2(s2a, add2(pr[0], pr[1]));
+          s2b = add2(s2b, add2(pr[2], pr[3]));
+        }
+        const float2 s2 = add2(s2a, s2b);
+        sum = s2.x + s2.y;
       } else {
         const float2 cc = make_float2(c_log2, c_log2), nm = make_float2(neg_mc, neg_mc);
         float2 s2a = make_float2(0.f, 0.f), s2b = make_float2(0.f, 0.f);
@@ -316,25 +352,29 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
       }
     }
-  } else if (warp == 12 && lane == 0 && iters > 0) {
-    // ------------------------------ MMA issuer ------------------------------
+  } else if (warp == 14 && lane == 0 && iters > 0) {
+    // ------------------------------ S = Q K^T issuer ------------------------------
     const uint32_t idesc_qk = make_idesc(kBlockM, kBlockN, kFormat, 0, 0);
-    const uint32_t idesc_pv = make_idesc(kBlockM, v_pad, kFormat, 0, 1);
-    auto issue_qk = [&](int i) {          // S of key tile i -> buffer i & 1
-      const uint32_t ka = smem_u32(s.k[i % kKStages]);
+    bool ok = mbar_wait(ctx, &s.q_full, 0, 30);
+    for (int i = 0; i < iters && ok; ++i) {
+      const int ks = i % kKStages;
+      ok = mbar_wait(ctx, &s.k_full[ks], (i / kKStages) & 1, 31);
+      if (ok && i >= 2) ok = mbar_wait(ctx, &s.s_free[i & 1], ((i >> 1) - 1) & 1, 35);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t ka = smem_u32(s.k[ks]);
       const uint32_t d = tmem + cS + (i & 1) * 128;
       for (int js = 0; js < ksteps_qk; ++js) {
         const uint32_t off = (js >> 2) * kBoxBytes + (js & 3) * 32;
         umma_ss(d, make_smem_desc(smem_u32(s.q) + off, 16, 1024), make_smem_desc(ka + off, 16, 1024), idesc_qk, js > 0);
       }
       umma_commit(&s.s_full[i & 1]);
-      umma_commit(&s.k_empty[i % kKStages]);
-    };
-    bool ok = mbar_wait(ctx, &s.q_full, 0, 30);
-    for (int i = 0; i < kLA && i < iters && ok; ++i) {
-      ok = mbar_wait(ctx, &s.k_full[i % kKStages], (i / kKStages) & 1, 31);
-      if (ok) { tc_fence_after(); issue_qk(i); }
+      umma_commit(&s.k_empty[ks]);
     }
+  } else if (warp == 12 && lane == 0 && iters > 0) {
+    // ------------------------------ O += P V issuer ------------------------------
+    const uint32_t idesc_pv = make_idesc(kBlockM, v_pad, kFormat, 0, 1);
+    bool ok = true;
     for (int n = 0; n < iters && ok; ++n) {
       const int vs = n % kVStages;
       ok = mbar_wait(ctx, &s.v_full[vs], (n / kVStages) & 1, 32);
@@ -342,26 +382,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       if (ok && n > 0) ok = mbar_wait(ctx, &s.o_ready, (n - 1) & 1, 34);
       if (!ok) break;
       tc_fence_after();
-      {
-        // O += P V
-        const uint32_t va = smem_u32(s.v[vs]);
+      const uint32_t va = smem_u32(s.v[vs]);
 #pragma unroll
-        for (int js = 0; js < kBlockN / 16; ++js) {
-          const uint32_t a_col = kAliasP ? tmem + cS + (n & 1) * 128 + (js >> 2) * 64 + (js & 3) * 8
-                                         : tmem + cP + (n & 1) * 64 + js * 8;
-          umma_ts(tmem + cO, a_col, make_smem_desc(va + js * 2048, kBoxBytes, 1024), idesc_pv,
-                  (n > 0 || js > 0) ? 1u : 0u);
-        }
-        umma_commit(&s.pv_done);
-        umma_commit(&s.v_empty[vs]);
+      for (int js = 0; js < kBlockN / 16; ++js) {
+        const uint32_t a_col = kAliasP ? tmem + cS + (n & 1) * 128 + (js >> 2) * 64 + (js & 3) * 8
+                                       : tmem + cP + (n & 1) * 64 + js * 8;
+        umma_ts(tmem + cO, a_col, make_smem_desc(va + js * 2048, kBoxBytes, 1024), idesc_pv,
+                (n > 0 || js > 0) ? 1u : 0u);
       }
-      const int i = n + kLA;
-      if (i < iters) {
-        ok = mbar_wait(ctx, &s.k_full[i % kKStages], (i / kKStages) & 1, 35);
-        if (!ok) break;
-        tc_fence_after();
-        issue_qk(i);
-      }
+      umma_commit(&s.pv_done);
+      umma_commit(&s.v_empty[vs]);
+      if (kAliasP) umma_commit(&s.s_free[n & 1]);
     }
   } else if (warp == 13 && lane == 0 && iters > 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -372,7 +403,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     for (int bx = 0; bx < nbox_qk; ++bx)
       tma_load_4d(s.q + bx * kBoxBytes, &tm_q, &s.q_full, bx * 64, h, qt * kBlockM, b);
     bool ok = true;
-    // K runs kLA tiles ahead of V, the order in which the MMA thread consumes them
+    // K runs kLA tiles ahead of V, the order in which the two products consume them
     for (int i = 0; i < iters + kLA && ok; ++i) {
       if (i < iters) {
         const int st = i % kKStages;

@@ -343,6 +343,24 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // 2^x for a pair on the special-function unit.
 __device__ __forceinline__ float2 ex2_pair_sfu(float2 x) { return make_float2(ex2_approx(x.x), ex2_approx(x.y)); }
 
+// 2^x for a pair on the FMA pipe instead: x = j + f with j = round(x) and |f| <= 1/2, a cubic for
+// 2^f (relative error 7.5e-5, below the rounding step of a 16-bit P) and j added to the exponent
+// field.  Inputs below -126 give 2^-126.
+__device__ __forceinline__ float2 ex2_pair_fma(float2 x) {
+  const float kRound = 12582912.f;   // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = add2(x, make_float2(kRound, kRound));
+  const float2 j = add2(t, make_float2(-kRound, -kRound));
+  const float2 f = fma2(j, make_float2(-1.f, -1.f), x);
+  float2 r = fma2(f, make_float2(0.05517132207751274f, 0.05517132207751274f), make_float2(0.24261054396629333f, 0.24261054396629333f));
+  r = fma2(r, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
+  r = fma2(r, f, make_float2(0.9999281167984009f, 0.9999281167984009f));
+  r.x = __int_as_float(__float_as_int(r.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(r.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
+
 template <typename T> struct Pack2;
 template <> struct Pack2<__nv_bfloat16> {
   static constexpr int kFormat = 1;
