@@ -180,8 +180,8 @@ int xattn_b200_bwd(const XattnBwdArgs* args, xattn_stream_t stream);
  * reference, whose ops allocate their workspaces themselves): a plugin host that owns the device
  * arena, or a serving loop that cannot afford the device-wide stall of a cudaMalloc.  `workspace`
  * in the arguments is ignored; the scratch lives in a fixed 8 MiB array inside the library that
- * every GPU loading it keeps until exit.  Limit: batch * q_heads * q_len <= 1048576, larger
- * problems return XATTN_E_INVALID.  Nothing is allocated or freed on any path.  All calls on a
+ * every GPU loading it keeps until exit.  Limit: batch * q_heads * q_len', with q_len' = q_len
+ * rounded up to a multiple of 128, at most 1048576; larger problems return XATTN_E_INVALID.  Nothing is allocated or freed on any path.  All calls on a
  * device share the array: nothing needs clearing between calls, but calls whose kernels overlap
  * on the GPU race, so serialise them.  The first call on a device looks up the array's address;
  * make it outside any stream capture. */

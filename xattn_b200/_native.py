@@ -348,8 +348,8 @@ def attention_bwd_static_scratch(dy: Tensor, q: Tensor, k: Tensor, v: Tensor, y:
     For callers that are not allowed to allocate on the device (a host application that owns all
     device memory and passes an op only its inputs and outputs; a serving loop that must not hit
     the device-wide stall of an allocation).  The kernel scratch is a fixed array inside the
-    library instead of a tensor, so ``batch * q_heads * q_len`` is limited to
-    ``STATIC_SCRATCH_MAX_ROWS``; calls on one device share that array and must not overlap on the
+    library instead of a tensor, so ``batch * q_heads * q_len`` (``q_len`` rounded up to a
+    multiple of 128) is limited to ``STATIC_SCRATCH_MAX_ROWS``; calls on one device share that array and must not overlap on the
     GPU.  Every tensor must already be laid out the way the kernels read it (unit last stride,
     16-byte aligned base and strides): nothing is copied or made contiguous here.  The first call
     on a device resolves the array's address and belongs outside any stream capture.

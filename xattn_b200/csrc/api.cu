@@ -37,7 +37,9 @@ int xattn_b200_fwd(const XattnFwdArgs* args, xattn_stream_t stream) {
 
 size_t xattn_b200_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len) {
   if (batch <= 0 || q_heads <= 0 || q_len <= 0) return 0;
-  return (size_t)batch * q_heads * q_len * 2 * sizeof(float);
+  // two FP32 words per (batch row, query head, query row), rows padded to whole 128-row tiles
+  const size_t padded = ((size_t)q_len + 127) / 128 * 128;
+  return (size_t)batch * q_heads * padded * 2 * sizeof(float);
 }
 
 int xattn_b200_bwd(const XattnBwdArgs* args, xattn_stream_t stream) {

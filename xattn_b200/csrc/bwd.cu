@@ -1,7 +1,7 @@
 // Backward attention for sm_100a: three kernels, all reductions in a fixed
 // order (bitwise repeatable; nothing is accumulated with atomics).
 //
-//   bwd_pre_kernel   delta = rowsum(dy * y), lse2 = lse * log2(e)      (HBM-bound)
+//   bwd_pre_kernel   -delta = -rowsum(dy * y), -lse2 = -lse * log2(e)   (HBM-bound)
 //   bwd_dq_kernel    query-stationary:  S = Q K^T, dP = dO V^T,
 //                    dS = P * (dP - delta),  dQ += dS K                 (tensor-bound)
 //   bwd_dkv_kernel   key-stationary, transposed:  S^T = K Q^T, dP^T = V dO^T,
@@ -30,8 +30,9 @@ struct BwdParams {
   const KeyTileInfo* k_tiles;
   const void* q;              // for direct loads in the dQ kernel
   int64_t q_sb, q_sl, q_sh;   // element strides of q
-  const float* lse2;          // [B][Hq][Lq]  lse * log2e, +inf for rows without keys
-  const float* delta;         // [B][Hq][Lq]
+  int LqPad;                  // q_len rounded up to whole 128-row tiles: row stride of nlse2 / ndelta
+  const float* nlse2;         // [B][Hq][LqPad]  -lse * log2e; -inf for rows without keys and padding
+  const float* ndelta;        // [B][Hq][LqPad]  -rowsum(dy * y); 0 in the padding
   void* dq;                   // [B][Lq][Hq][D]
   void* dk;                   // [B][Lk][Hkv][D]
   void* dv;                   // [B][Lk][Hkv][V]
@@ -45,15 +46,24 @@ template <typename T>
 __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, const T* __restrict__ y,
                                                       const float* __restrict__ lse, int B, int Lq, int Hq, int V,
                                                       int64_t dy_sb, int64_t dy_sl, int64_t dy_sh, int64_t y_sb,
-                                                      int64_t y_sl, int64_t y_sh, float* __restrict__ delta,
-                                                      float* __restrict__ lse2) {
+                                                      int64_t y_sl, int64_t y_sh, int LqPad,
+                                                      float* __restrict__ ndelta, float* __restrict__ nlse2) {
   const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (w >= (long long)B * Lq * Hq) return;
+  if (w >= (long long)B * LqPad * Hq) return;
   const int h = (int)(w % Hq);
   const long long bi = w / Hq;
-  const int i = (int)(bi % Lq);
-  const int b = (int)(bi / Lq);
+  const int i = (int)(bi % LqPad);
+  const int b = (int)(bi / LqPad);
+  if (i >= Lq) {
+    // padding up to whole tiles: rows that contribute nothing
+    if (lane == 0) {
+      const size_t idx = ((size_t)b * Hq + h) * LqPad + i;
+      ndelta[idx] = 0.f;
+      nlse2[idx] = -INFINITY;
+    }
+    return;
+  }
   const T* dyr = dy + b * dy_sb + i * dy_sl + h * dy_sh;
   const T* yr = y + b * y_sb + i * y_sl + h * y_sh;
   float acc = 0.f;
@@ -73,10 +83,10 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, 
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if (lane == 0) {
-    const size_t idx = ((size_t)b * Hq + h) * Lq + i;
-    delta[idx] = acc;
-    const float l = lse[idx];
-    lse2[idx] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
+    const size_t idx = ((size_t)b * Hq + h) * LqPad + i;
+    ndelta[idx] = -acc;
+    const float l = lse[((size_t)b * Hq + h) * Lq + i];
+    nlse2[idx] = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
   }
 }
 
@@ -215,12 +225,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
         mbar_arrive_warp(&s.q_ready);
       }
       int lo = 0, hi = 0;
-      float lse2 = INFINITY, delta = 0.f;
+      float nlse2 = -INFINITY, ndelta = 0.f;
       if (live) {
         lo = p.row_lo[(size_t)b * p.Lq + row];
         hi = p.row_hi[(size_t)b * p.Lq + row];
-        lse2 = p.lse2[((size_t)b * p.Hq + h) * p.Lq + row];
-        delta = p.delta[((size_t)b * p.Hq + h) * p.Lq + row];
+        nlse2 = p.nlse2[((size_t)b * p.Hq + h) * p.LqPad + row];
+        ndelta = p.ndelta[((size_t)b * p.Hq + h) * p.LqPad + row];
       }
       const float c_log2 = p.scale * 1.4426950408889634f;
       bool ok = true;
@@ -241,8 +251,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
         const bool tile_full = ((n_lo + i) * BN >= full_lo) && ((n_lo + i + 1) * BN <= full_hi);
         const int rl = lo - col0, rh = hi - col0;
         uint32_t pk[CH / 2];
-        const float2 cc = make_float2(c_log2, c_log2), nl = make_float2(-lse2, -lse2);
-        const float2 nd = make_float2(-delta, -delta);
+        const float2 cc = make_float2(c_log2, c_log2), nl = make_float2(nlse2, nlse2);
+        const float2 nd = make_float2(ndelta, ndelta);
 #pragma unroll
         for (int c = 0; c < CH; c += 2) {
           float2 pr = ex2_pair_sfu(fma2(make_float2(sv[c], sv[c + 1]), cc, nl));
@@ -397,20 +407,18 @@ struct DkvSmem {
   alignas(1024) uint8_t v[MODE == kDvOnly ? 1024 : kKvBytes];
   alignas(1024) uint8_t q[kStages][kQBytes];
   alignas(1024) uint8_t d_o[kStages][kQBytes];
-  // per-query scalars (-lse*log2e, -delta, lo, hi) of the sub-tiles in flight: one pair of
-  // buffers per element-wise warpgroup
-  alignas(16) float nlse2[2][2][SM];
-  alignas(16) float ndelta[2][2][SM];
-  alignas(16) int lo[2][2][SM];
-  alignas(16) int hi[2][2][SM];
   uint64_t kv_full;
   uint64_t q_full[kStages], q_empty[kStages];
-  uint64_t sdp_full[2], pds_full[2], scal_full[2][2], all_done;
+  // per TMEM buffer: S^T / dP^T written by their products, P^T / dS^T written by the warpgroups,
+  // and the two regions read by dV / dK and free for the next products
+  uint64_t s_full[2], dp_full[2], p_full[2], ds_full[2], s_free[2], dp_free[2];
+  uint64_t all_done;
   uint32_t tmem_base;
   int abort_flag;
-  // query-tile summaries [m_first, m_first + kTileCache) of this batch row, staged once
-  static constexpr int kTileCache = 256;
-  TileInfo tiles[kTileCache];
+  // one bit per query tile of [m_first, m_first + kTileCache): it sees this key tile at all / every
+  // one of its rows sees all of it.  Built once, so that stepping to the next item reads no table.
+  static constexpr int kTileCache = 768;
+  uint32_t overlap_bits[kTileCache / 32], full_bits[kTileCache / 32];
 };
 
 // Enumerates the (query head of the group, SM-row query sub-tile) pairs a key
@@ -419,17 +427,20 @@ template <int SM>
 struct DkvIter {
   static constexpr int kParts = kBlockM / SM;
   int g, m, part;        // head within the group, 128-row query tile, which SM-row part
-  int G, m_first, m_end, Lq, k0, k1;
+  int G, m_first, m_end, Lq, k0;
   const TileInfo* qt;        // global table of this batch row
-  const TileInfo* cache;     // shared-memory copy of entries [m_first, m_first + cache_n)
+  const uint32_t* bits;      // shared-memory bitmap over query tiles [m_first, m_first + cache_n)
   int cache_n;
-  __device__ __forceinline__ TileInfo tile(int mm) const {
+  uint32_t word;             // the bitmap word last read, and which one it is
+  int word_i;
+  __device__ __forceinline__ bool tile_overlaps(int mm) {
     const int rel = mm - m_first;
-    return (rel >= 0 && rel < cache_n) ? cache[rel] : qt[mm];
-  }
-  __device__ __forceinline__ bool tile_overlaps(int mm) const {
-    const TileInfo t = tile(mm);
-    return t.max_hi > t.min_lo && t.min_lo < k1 && t.max_hi > k0;
+    if (rel < cache_n) {
+      if ((rel >> 5) != word_i) { word_i = rel >> 5; word = bits[word_i]; }
+      return (word >> (rel & 31)) & 1u;
+    }
+    const TileInfo t = qt[mm];
+    return t.max_hi > t.min_lo && t.min_lo < k0 + kBlockN && t.max_hi > k0;
   }
   __device__ __forceinline__ bool valid() const { return g < G; }
   __device__ __forceinline__ int row0() const { return m * kBlockM + part * SM; }
@@ -444,9 +455,9 @@ struct DkvIter {
     }
   }
   __device__ __forceinline__ void init(int G_, int m_first_, int m_end_, int Lq_, int k0_, const TileInfo* qt_,
-                                       const TileInfo* cache_, int cache_n_) {
-    G = G_; m_first = m_first_; m_end = m_end_; Lq = Lq_; k0 = k0_; k1 = k0_ + kBlockN; qt = qt_;
-    cache = cache_; cache_n = cache_n_;
+                                       const uint32_t* bits_, int cache_n_) {
+    G = G_; m_first = m_first_; m_end = m_end_; Lq = Lq_; k0 = k0_; qt = qt_;
+    bits = bits_; cache_n = cache_n_; word = 0; word_i = -1;
     g = (m_end_ > m_first_) ? 0 : G_;
     m = m_first_; part = 0;
     settle();
@@ -454,8 +465,11 @@ struct DkvIter {
   __device__ __forceinline__ void next() { ++part; settle(); }
 };
 
-// warps 0-3 / 4-7: element-wise warpgroups (thread = key row); warpgroup w owns TMEM buffer w and
-// takes every other sub-tile.  warp 8: MMA issuer, warp 9: TMA producer + TMEM owner, warps 10-11 idle
+// warps 0-3 / 4-7: element-wise warpgroups, thread = (key row, half of the sub-tile's query columns).
+// warp 8: issuer of S^T / dP^T, warp 10: issuer of dV / dK (an issuing thread stalls while its
+// products run, so the two kinds get a thread each), warp 9: TMA producer + TMEM owner, warp 11 idle.
+// Sub-tiles alternate between two TMEM buffers, so the products of one run under the element-wise
+// work of the other.
 template <typename T, int HD, int MODE, int SM>
 __global__ void __launch_bounds__(384, 1)
 bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
@@ -490,15 +504,26 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     mbar_init(&s.kv_full, 1);
     for (int i = 0; i < kStages; ++i) { mbar_init(&s.q_full[i], 1); mbar_init(&s.q_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&s.sdp_full[i], 1); mbar_init(&s.pds_full[i], 4);
-      mbar_init(&s.scal_full[i][0], 4); mbar_init(&s.scal_full[i][1], 4);
+      mbar_init(&s.s_full[i], 1); mbar_init(&s.dp_full[i], 1);
+      mbar_init(&s.p_full[i], 8); mbar_init(&s.ds_full[i], 8);
+      mbar_init(&s.s_free[i], 1); mbar_init(&s.dp_free[i], 1);
     }
     mbar_init(&s.all_done, 1);
     fence_mbar_init();
   }
   if (warp == 9) { tmem_alloc(&s.tmem_base, kTmemCols); tmem_relinquish(); }
   const int cache_n = min(max(kti.m_end - kti.m_first, 0), Smem::kTileCache);
-  for (int i = tid; i < cache_n; i += blockDim.x) s.tiles[i] = qt_info[kti.m_first + i];
+  for (int base = 0; base < Smem::kTileCache; base += 384) {
+    const int i = base + tid;
+    bool sees = false, full = false;
+    if (i < cache_n) {
+      const TileInfo t = qt_info[kti.m_first + i];
+      sees = t.max_hi > t.min_lo && t.min_lo < (n + 1) * kBlockN && t.max_hi > n * kBlockN;
+      full = (n * kBlockN >= t.max_lo) && ((n + 1) * kBlockN <= t.min_hi);
+    }
+    const uint32_t ws = __ballot_sync(0xffffffffu, sees), wf = __ballot_sync(0xffffffffu, full);
+    if (lane == 0) { s.overlap_bits[i >> 5] = ws; s.full_bits[i >> 5] = wf; }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -511,14 +536,15 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int d_pad = (p.D + 15) & ~15, v_pad = (p.V + 15) & ~15;
 
   Iter it0;
-  it0.init(G, kti.m_first, kti.m_end, p.Lq, n * kBlockN, qt_info, s.tiles, cache_n);
+  it0.init(G, kti.m_first, kti.m_end, p.Lq, n * kBlockN, qt_info, s.overlap_bits, cache_n);
   const bool any_work = it0.valid();
 
-  if (warp < 8) setmaxnreg_inc<216>(); else setmaxnreg_dec<40>();
+  if (warp < 8) setmaxnreg_inc<216>(); else setmaxnreg_dec<72>();
   if (dead) {
   } else if (warp < 8) {
     // ------------------------ element-wise warpgroups ------------------------
-    const int wg = warp >> 2;                 // also the TMEM buffer this warpgroup owns
+    constexpr int kHalf = SM / 2;             // query columns per warpgroup and step
+    const int wg = warp >> 2;                 // which half of the columns
     const int wt = tid & 127;
     const int r = wt;                         // key row inside the tile
     const int key = n * kBlockN + r;
@@ -526,89 +552,129 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const float c_log2 = p.scale * 1.4426950408889634f;
     const float2 cc = make_float2(c_log2, c_log2);
     bool ok = true;
-    // per-query scalars of a sub-tile: thread t < 64 fetches lse2 / delta, t >= 64 fetches lo / hi
-    const int sq = wt & 63;
-    auto fetch = [&](const Iter& it, float& f0, float& f1, int& i0, int& i1) {
-      const int qrow = it.row0() + sq;
-      const int h = kvh * G + it.g;
-      f0 = -INFINITY; f1 = 0.f; i0 = 0; i1 = 0;
-      if (sq < SM && qrow < p.Lq) {
-        if (wt < 64) {
-          f0 = -p.lse2[((size_t)b * p.Hq + h) * p.Lq + qrow];
-          f1 = -p.delta[((size_t)b * p.Hq + h) * p.Lq + qrow];
-        } else {
-          i0 = p.row_lo[(size_t)b * p.Lq + qrow];
-          i1 = p.row_hi[(size_t)b * p.Lq + qrow];
+    // Bit of the bitmap word: every row of query tile mm sees all of this key tile, no masking.
+    // The word is fetched a step ahead and looked at only when needed.
+    auto full_word = [&](int mm, int& bit) -> uint32_t {
+      const int rel = mm - kti.m_first;
+      if (rel < cache_n) { bit = rel & 31; return s.full_bits[rel >> 5]; }
+      const TileInfo t = qt_info[mm];
+      bit = 0;
+      return ((n * kBlockN >= t.max_lo) && ((n + 1) * kBlockN <= t.min_hi)) ? 1u : 0u;
+    };
+    // Per-query scalars of this warpgroup's columns come straight from global memory into
+    // registers, a step ahead of their use and never touched in between (an instruction using a
+    // loaded value stalls the warp for the load's whole latency; shared memory is slow while the
+    // tensor pipe streams operands from it).  -lse2 and -delta: every thread reads the same kHalf
+    // values, into the registers the previous step just finished with.  lo / hi: lane c reads those
+    // of column c and a step that masks hands them round by shuffle.
+    auto scal_row = [&](const Iter& item, const float* base) -> const float4* {
+      return reinterpret_cast<const float4*>(base + ((size_t)b * p.Hq + kvh * G + item.g) * p.LqPad + item.row0() +
+                                             wg * kHalf);
+    };
+    auto bound_index = [&](const Iter& item) -> size_t {
+      const int qrow = item.row0() + wg * kHalf + (lane & (kHalf - 1));
+      return (size_t)b * p.Lq + (qrow < p.Lq ? qrow : p.Lq - 1);
+    };
+    float nl[kHalf], nd[kHalf];
+    int my_lo = 0, my_hi = 0;
+    Iter it = it0;
+    uint32_t fw = 0;
+    int fbit = 0;
+    if (it.valid()) {
+      const float4* l4 = scal_row(it, p.nlse2);
+      const float4* d4 = scal_row(it, p.ndelta);
+#pragma unroll
+      for (int c = 0; c < kHalf; c += 4) {
+        *reinterpret_cast<float4*>(nl + c) = __ldg(l4 + (c >> 2));
+        if (kWantDk) *reinterpret_cast<float4*>(nd + c) = __ldg(d4 + (c >> 2));
+      }
+      const size_t bi = bound_index(it);
+      my_lo = p.row_lo[bi]; my_hi = p.row_hi[bi];
+      fw = full_word(it.m, fbit);
+    }
+    int kk = 0;
+    while (it.valid() && ok) {
+      const int sub = kk & 1;                 // TMEM buffer of this step
+      Iter n1 = it; n1.next();
+      const bool tile_full = (fw >> fbit) & 1u;
+      // which of this thread's columns see its key, as bits
+      uint32_t seen = 0xffffffffu;
+      if (!tile_full) {
+        const bool col_live = it.row0() + wg * kHalf + (lane & (kHalf - 1)) < p.Lq;
+        const int lo_c = col_live ? my_lo : 0, hi_c = col_live ? my_hi : 0;
+        seen = 0u;
+#pragma unroll
+        for (int c = 0; c < kHalf; ++c) {
+          const int lo = __shfl_sync(0xffffffffu, lo_c, c), hi = __shfl_sync(0xffffffffu, hi_c, c);
+          seen |= (key >= lo && key < hi ? 1u : 0u) << c;
         }
       }
-    };
-    auto stash = [&](int sub, float f0, float f1, int i0, int i1) {
-      if (sq < SM) {
-        if (wt < 64) { s.nlse2[wg][sub][sq] = f0; s.ndelta[wg][sub][sq] = f1; }
-        else { s.lo[wg][sub][sq] = i0; s.hi[wg][sub][sq] = i1; }
+      if (n1.valid()) {
+        const size_t bi = bound_index(n1);
+        my_lo = p.row_lo[bi]; my_hi = p.row_hi[bi];
+        fw = full_word(n1.m, fbit);
       }
-      mbar_arrive_warp(&s.scal_full[wg][sub]);
-    };
-    Iter it = it0;
-    if (wg == 1 && it.valid()) it.next();     // warpgroup 1 starts at the second sub-tile
-    float f0, f1; int i0, i1;
-    if (it.valid()) { fetch(it, f0, f1, i0, i1); stash(0, f0, f1, i0, i1); }
-    int kk = 0;                               // steps taken by this warpgroup
-    while (it.valid() && ok) {
-      const int sub = kk & 1;
-      Iter nx = it; nx.next();
-      if (nx.valid()) nx.next();                                 // this warpgroup's next sub-tile
-      if (nx.valid()) fetch(nx, f0, f1, i0, i1);                 // in flight during this step
-      ok = mbar_wait(ctx, &s.scal_full[wg][sub], (kk >> 1) & 1, 82);  // scalars of this step are in shared memory
-      if (ok) ok = mbar_wait(ctx, &s.sdp_full[wg], kk & 1, 80);
+      const uint32_t t_s = tmem + lane_off + cS + sub * SM + wg * kHalf;
+      const uint32_t t_dp = tmem + lane_off + cDP + sub * SM + wg * kHalf;
+      // ---- P^T = exp2(S^T * c - lse2), masked ----
+      ok = mbar_wait(ctx, &s.s_full[sub], (kk >> 1) & 1, 80);
       if (!ok) break;
       tc_fence_after();
-      float sv[SM], dpv[SM];
-#pragma unroll
-      for (int c = 0; c < SM; c += 32) {
-        tmem_ld_x32(tmem + lane_off + cS + wg * SM + c, reinterpret_cast<uint32_t*>(sv) + c);
-        if (kWantDk) tmem_ld_x32(tmem + lane_off + cDP + wg * SM + c, reinterpret_cast<uint32_t*>(dpv) + c);
-      }
+      float pv[kHalf];
+      if (kHalf == 32) tmem_ld_x32(t_s, reinterpret_cast<uint32_t*>(pv));
+      else tmem_ld_x16(t_s, reinterpret_cast<uint32_t*>(pv));
       tc_wait_ld();
-      const TileInfo ti = it.tile(it.m);
-      const bool tile_full = (n * kBlockN >= ti.max_lo) && ((n + 1) * kBlockN <= ti.min_hi);
 #pragma unroll
-      for (int c0 = 0; c0 < SM; c0 += 32) {
-        uint32_t pp[16], pd[16];
-#pragma unroll
-        for (int c = c0; c < c0 + 32; c += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(&s.nlse2[wg][sub][c]);
-          float2 pa = ex2_pair_sfu(fma2(make_float2(sv[c], sv[c + 1]), cc, make_float2(l4.x, l4.y)));
-          float2 pb = ex2_pair_sfu(fma2(make_float2(sv[c + 2], sv[c + 3]), cc, make_float2(l4.z, l4.w)));
-          if (!tile_full) {
-            const int4 lo4 = *reinterpret_cast<const int4*>(&s.lo[wg][sub][c]);
-            const int4 hi4 = *reinterpret_cast<const int4*>(&s.hi[wg][sub][c]);
-            pa.x = (key >= lo4.x && key < hi4.x) ? pa.x : 0.f;
-            pa.y = (key >= lo4.y && key < hi4.y) ? pa.y : 0.f;
-            pb.x = (key >= lo4.z && key < hi4.z) ? pb.x : 0.f;
-            pb.y = (key >= lo4.w && key < hi4.w) ? pb.y : 0.f;
-          }
-          const int o = (c - c0) >> 1;
-          if (kWantDv) {
-            pp[o] = Pack2<T>::pack(pa.x, pa.y);
-            pp[o + 1] = Pack2<T>::pack(pb.x, pb.y);
-          }
-          if (kWantDk) {
-            const float4 d4 = *reinterpret_cast<const float4*>(&s.ndelta[wg][sub][c]);
-            const float2 da = mul2(pa, add2(make_float2(dpv[c], dpv[c + 1]), make_float2(d4.x, d4.y)));
-            const float2 db = mul2(pb, add2(make_float2(dpv[c + 2], dpv[c + 3]), make_float2(d4.z, d4.w)));
-            pd[o] = Pack2<T>::pack(da.x, da.y);
-            pd[o + 1] = Pack2<T>::pack(db.x, db.y);
-          }
-        }
-        if (kWantDv) tmem_st_x16(tmem + lane_off + cS + wg * SM + (c0 >> 1), pp);
-        if (kWantDk) tmem_st_x16(tmem + lane_off + cDP + wg * SM + (c0 >> 1), pd);
+      for (int c = 0; c < kHalf; c += 2) {
+        const float2 e = ex2_pair_sfu(fma2(make_float2(pv[c], pv[c + 1]), cc, make_float2(nl[c], nl[c + 1])));
+        pv[c] = e.x; pv[c + 1] = e.y;
       }
-      tc_wait_st();
+      if (!tile_full) {
+#pragma unroll
+        for (int c = 0; c < kHalf; ++c) pv[c] = ((seen >> c) & 1u) ? pv[c] : 0.f;
+      }
+      // the 16-bit results go over the first half of the warpgroup's own columns
+      if (kWantDv) {
+        uint32_t pp[kHalf / 2];
+#pragma unroll
+        for (int c = 0; c < kHalf; c += 2) pp[c >> 1] = Pack2<T>::pack(pv[c], pv[c + 1]);
+        if (kHalf == 32) tmem_st_x16(t_s, pp); else tmem_st_x8(t_s, pp);
+        tc_wait_st();
+      }
       tc_fence_before();
-      mbar_arrive_warp(&s.pds_full[wg]);
-      if (nx.valid()) stash(sub ^ 1, f0, f1, i0, i1);
-      it = nx;
+      mbar_arrive_warp(&s.p_full[sub]);       // also: S^T has been read
+      if (n1.valid()) {
+        const float4* l4 = scal_row(n1, p.nlse2);
+#pragma unroll
+        for (int c = 0; c < kHalf; c += 4) *reinterpret_cast<float4*>(nl + c) = __ldg(l4 + (c >> 2));
+      }
+      // ---- dS^T = P^T * (dP^T - delta) ----
+      if (kWantDk) {
+        ok = mbar_wait(ctx, &s.dp_full[sub], (kk >> 1) & 1, 83);
+        if (!ok) break;
+        tc_fence_after();
+        float dpv[kHalf];
+        if (kHalf == 32) tmem_ld_x32(t_dp, reinterpret_cast<uint32_t*>(dpv));
+        else tmem_ld_x16(t_dp, reinterpret_cast<uint32_t*>(dpv));
+        tc_wait_ld();
+        uint32_t pd[kHalf / 2];
+#pragma unroll
+        for (int c = 0; c < kHalf; c += 2) {
+          const float2 d = mul2(make_float2(pv[c], pv[c + 1]),
+                                add2(make_float2(dpv[c], dpv[c + 1]), make_float2(nd[c], nd[c + 1])));
+          pd[c >> 1] = Pack2<T>::pack(d.x, d.y);
+        }
+        if (kHalf == 32) tmem_st_x16(t_dp, pd); else tmem_st_x8(t_dp, pd);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive_warp(&s.ds_full[sub]);
+        if (n1.valid()) {
+          const float4* d4 = scal_row(n1, p.ndelta);
+#pragma unroll
+          for (int c = 0; c < kHalf; c += 4) *reinterpret_cast<float4*>(nd + c) = __ldg(d4 + (c >> 2));
+        }
+      }
+      it = n1;
       ++kk;
     }
     // epilogue: warpgroup 0 writes dK (scaled), warpgroup 1 writes dV
@@ -649,65 +715,70 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
     }
   } else if (warp == 8 && lane == 0 && any_work) {
-    // ------------------------------ MMA issuer ------------------------------
+    // ------------------------------ S^T / dP^T issuer ------------------------------
     const uint32_t idesc_st = make_idesc(kBlockN, SM, kFormat, 0, 0);
-    const uint32_t idesc_dv = make_idesc(kBlockN, v_pad, kFormat, 0, 1);
-    const uint32_t idesc_dk = make_idesc(kBlockN, d_pad, kFormat, 0, 1);
     const uint32_t ka = smem_u32(s.k), va = smem_u32(s.v);
-    auto issue_st = [&](int stage, int buf) {
-      const uint32_t qa = smem_u32(s.q[stage]), da = smem_u32(s.d_o[stage]);
+    bool ok = mbar_wait(ctx, &s.kv_full, 0, 90);
+    int cnt = 0;
+    for (Iter it = it0; it.valid() && ok; it.next(), ++cnt) {
+      const int buf = cnt & 1, st = cnt % kStages;
+      ok = mbar_wait(ctx, &s.q_full[st], (cnt / kStages) & 1, 91);
+      // the buffer's previous P^T has been read by its dV product
+      if (ok && cnt >= 2) ok = mbar_wait(ctx, &s.s_free[buf], ((cnt >> 1) - 1) & 1, 93);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t qa = smem_u32(s.q[st]), da = smem_u32(s.d_o[st]);
       for (int js = 0; js < ksteps_qk; ++js) {
         umma_ss(tmem + cS + buf * SM, make_smem_desc(ka + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024),
                 make_smem_desc(qa + (js >> 2) * kQBox + (js & 3) * 32, 16, 1024), idesc_st, js > 0);
       }
+      umma_commit(&s.s_full[buf]);
       if (kWantDk) {
+        if (cnt >= 2) ok = mbar_wait(ctx, &s.dp_free[buf], ((cnt >> 1) - 1) & 1, 95);
+        if (!ok) break;
+        tc_fence_after();
         for (int js = 0; js < ksteps_v; ++js) {
           umma_ss(tmem + cDP + buf * SM, make_smem_desc(va + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024),
                   make_smem_desc(da + (js >> 2) * kQBox + (js & 3) * 32, 16, 1024), idesc_st, js > 0);
         }
+        umma_commit(&s.dp_full[buf]);
       }
-      umma_commit(&s.sdp_full[buf]);
-    };
-    bool ok = mbar_wait(ctx, &s.kv_full, 0, 90);
-    Iter ahead = it0;      // item whose S^T / dP^T is issued next
-    int issued = 0, cnt = 0;
-    // prologue: S^T / dP^T of the first two items
-    for (int k2 = 0; k2 < 2 && ok && ahead.valid(); ++k2) {
-      ok = mbar_wait(ctx, &s.q_full[issued % kStages], (issued / kStages) & 1, 91);
-      if (!ok) break;
-      tc_fence_after();
-      issue_st(issued % kStages, issued & 1);
-      ++issued; ahead.next();
     }
-    while (cnt < issued && ok) {
+  } else if (warp == 10 && lane == 0 && any_work) {
+    // ------------------------------ dV / dK issuer ------------------------------
+    constexpr int kHalf = SM / 2, kStepsPerHalf = kHalf / 16;
+    const uint32_t idesc_dv = make_idesc(kBlockN, v_pad, kFormat, 0, 1);
+    const uint32_t idesc_dk = make_idesc(kBlockN, d_pad, kFormat, 0, 1);
+    bool ok = true;
+    int cnt = 0;
+    for (Iter it = it0; it.valid() && ok; it.next(), ++cnt) {
       const int buf = cnt & 1, st = cnt % kStages;
-      ok = mbar_wait(ctx, &s.pds_full[buf], (cnt >> 1) & 1, 92);
+      ok = mbar_wait(ctx, &s.q_full[st], (cnt / kStages) & 1, 94);
+      if (ok) ok = mbar_wait(ctx, &s.p_full[buf], (cnt >> 1) & 1, 92);
       if (!ok) break;
       tc_fence_after();
       const uint32_t qa = smem_u32(s.q[st]), da = smem_u32(s.d_o[st]);
+      // P^T / dS^T of column half w sit in the first packed columns of that half
       if (kWantDv) {
 #pragma unroll
         for (int js = 0; js < SM / 16; ++js) {
-          umma_ts(tmem + cDV, tmem + cS + buf * SM + js * 8, make_smem_desc(da + js * 2048, kQBox, 1024), idesc_dv,
-                  (cnt > 0 || js > 0) ? 1u : 0u);
+          const uint32_t a_col = tmem + cS + buf * SM + (js / kStepsPerHalf) * kHalf + (js % kStepsPerHalf) * 8;
+          umma_ts(tmem + cDV, a_col, make_smem_desc(da + js * 2048, kQBox, 1024), idesc_dv, (cnt > 0 || js > 0) ? 1u : 0u);
         }
       }
+      umma_commit(&s.s_free[buf]);
       if (kWantDk) {
-#pragma unroll
-        for (int js = 0; js < SM / 16; ++js) {
-          umma_ts(tmem + cDK, tmem + cDP + buf * SM + js * 8, make_smem_desc(qa + js * 2048, kQBox, 1024), idesc_dk,
-                  (cnt > 0 || js > 0) ? 1u : 0u);
-        }
-      }
-      umma_commit(&s.q_empty[st]);
-      ++cnt;
-      if (ahead.valid()) {
-        ok = mbar_wait(ctx, &s.q_full[issued % kStages], (issued / kStages) & 1, 93);
+        ok = mbar_wait(ctx, &s.ds_full[buf], (cnt >> 1) & 1, 96);
         if (!ok) break;
         tc_fence_after();
-        issue_st(issued % kStages, issued & 1);
-        ++issued; ahead.next();
+#pragma unroll
+        for (int js = 0; js < SM / 16; ++js) {
+          const uint32_t a_col = tmem + cDP + buf * SM + (js / kStepsPerHalf) * kHalf + (js % kStepsPerHalf) * 8;
+          umma_ts(tmem + cDK, a_col, make_smem_desc(qa + js * 2048, kQBox, 1024), idesc_dk, (cnt > 0 || js > 0) ? 1u : 0u);
+        }
+        umma_commit(&s.dp_free[buf]);
       }
+      umma_commit(&s.q_empty[st]);
     }
     if (ok) umma_commit(&s.all_done);
   } else if (warp == 9 && lane == 0 && any_work) {
@@ -787,16 +858,17 @@ static int launch_dkv(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t st
 template <typename T>
 static int launch_bwd(const XattnBwdArgs& a, BwdParams& p, cudaStream_t stream) {
   // 1. preprocess
-  float* delta = a.workspace;
-  float* lse2 = a.workspace + (size_t)p.B * p.Hq * p.Lq;
-  p.delta = delta; p.lse2 = lse2;
+  float* ndelta = a.workspace;
+  float* nlse2 = a.workspace + (size_t)p.B * p.Hq * p.LqPad;
+  p.ndelta = ndelta; p.nlse2 = nlse2;
   {
-    const long long warps = (long long)p.B * p.Lq * p.Hq;
+    const long long warps = (long long)p.B * p.LqPad * p.Hq;
     const long long blocks = (warps * 32 + 255) / 256;
     ProfileScope prof(kProfBwdPre, stream);
     bwd_pre_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
         reinterpret_cast<const T*>(a.dy), reinterpret_cast<const T*>(a.y), a.lse, p.B, p.Lq, p.Hq, p.V,
-        a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], a.y_strides[0], a.y_strides[1], a.y_strides[2], delta, lse2);
+        a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], a.y_strides[0], a.y_strides[1], a.y_strides[2], p.LqPad,
+        ndelta, nlse2);
   }
   const int hd = p.D > p.V ? p.D : p.V;
   int rc;
@@ -828,7 +900,8 @@ int bwd_entry(const XattnBwdArgs* a, cudaStream_t stream) {
   if (!(a->scale > 0.f) || !isfinite(a->scale)) { set_error("scale must be finite and positive"); return XATTN_E_INVALID; }
   if (!a->q || !a->k || !a->v || !a->y || !a->dy || !a->lse || !a->plan || !a->dq || !a->dk || !a->dv ||
       !a->workspace || !a->status) { set_error("null tensor pointer"); return XATTN_E_INVALID; }
-  for (const void* ptr : {a->q, a->y, a->dy, (const void*)a->dq, (const void*)a->dk, (const void*)a->dv}) {
+  for (const void* ptr : {a->q, a->y, a->dy, (const void*)a->dq, (const void*)a->dk, (const void*)a->dv,
+                          (const void*)a->workspace}) {
     if (reinterpret_cast<uintptr_t>(ptr) & 15) { set_error("tensors must be 16-byte aligned"); return XATTN_E_INVALID; }
   }
   for (const int64_t* st : {a->q_strides, a->y_strides, a->dy_strides}) {
@@ -839,6 +912,7 @@ int bwd_entry(const XattnBwdArgs* a, cudaStream_t stream) {
   p.D = (int)a->qk_dim; p.V = (int)a->v_dim;
   const PlanLayout pl(a->batch, a->q_len, a->k_len);
   p.nQT = (int)pl.nQT; p.nKT = (int)pl.nKT;
+  p.LqPad = p.nQT * kBlockM;
   p.scale = a->scale;
   p.row_lo = a->plan + pl.off_lo; p.row_hi = a->plan + pl.off_hi;
   p.q_tiles = reinterpret_cast<const TileInfo*>(a->plan + pl.off_qt);

@@ -1,7 +1,7 @@
 // Backward pass for callers that must not allocate device memory.
 //
 // The regular backward entry takes a caller-provided workspace (two FP32 words per batch row, query
-// head and query position: rowsum(dy*y) and lse*log2e).  Some callers cannot provide one: a plugin
+// head and query position, positions padded to whole 128-row tiles: -rowsum(dy*y) and -lse*log2e).  Some callers cannot provide one: a plugin
 // host that owns the whole device arena and hands an op nothing but its input and output buffers,
 // or a serving loop where a cudaMalloc would stall every stream of the device at an unpredictable
 // moment.  For them the same kernels run here with the workspace in a fixed array that lives in the
@@ -26,10 +26,10 @@ int bwd_entry(const XattnBwdArgs* a, cudaStream_t stream);
 
 namespace {
 
-constexpr long long kStaticRows = 1ll << 20;   // batch * q_heads * q_len, at most
+constexpr long long kStaticRows = 1ll << 20;   // batch * q_heads * (q_len rounded up to 128), at most
 constexpr int kMaxDevices = 64;
 
-// delta in the first half, lse*log2e in the second — the layout bwd_entry gives its workspace
+// bwd_entry lays its two arrays out back to back from the start of whatever workspace it is given
 static __device__ __align__(256) float g_static_workspace[2 * kStaticRows];
 
 std::mutex g_static_mutex;
@@ -61,9 +61,10 @@ int static_workspace(float** out) {
 int bwd_static_entry(const XattnBwdArgs* a, cudaStream_t stream) {
   if (!a) { set_error("null arguments"); return XATTN_E_INVALID; }
   if (a->batch <= 0 || a->q_heads <= 0 || a->q_len <= 0) { set_error("bad batch / head / length"); return XATTN_E_INVALID; }
-  const long long rows = (long long)a->batch * a->q_heads * a->q_len;
-  if (rows > kStaticRows || rows / a->batch / a->q_heads != a->q_len) {
-    set_error("batch * q_heads * q_len = %lld exceeds the static workspace of %lld rows; "
+  const long long padded = (a->q_len + 127) / 128 * 128;      // the kernels keep whole 128-row tiles
+  const long long rows = (long long)a->batch * a->q_heads * padded;
+  if (rows > kStaticRows || rows / a->batch / a->q_heads != padded) {
+    set_error("batch * q_heads * q_len (rounded up to 128) = %lld exceeds the static workspace of %lld rows; "
               "use xattn_b200_bwd with a caller-provided workspace", rows, kStaticRows);
     return XATTN_E_INVALID;
   }
