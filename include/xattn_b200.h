@@ -179,7 +179,7 @@ int xattn_b200_bwd(const XattnBwdArgs* args, xattn_stream_t stream);
 /* The same backward for callers that may not allocate device memory (no counterpart in the
  * reference, whose ops allocate their workspaces themselves): a plugin host that owns the device
  * arena, or a serving loop that cannot afford the device-wide stall of a cudaMalloc.  `workspace`
- * in the arguments is ignored; the scratch lives in a fixed 8 MiB array inside the library that
+ * in the arguments is ignored; the scratch lives in a fixed 40 MiB array inside the library that
  * every GPU loading it keeps until exit.  Limit: batch * q_heads * q_len', with q_len' = q_len
  * rounded up to a multiple of 128, at most 1048576; larger problems return XATTN_E_INVALID.  Nothing is allocated or freed on any path.  All calls on a
  * device share the array: nothing needs clearing between calls, but calls whose kernels overlap

@@ -40,7 +40,7 @@ def test_plan_bytes_layout():
     assert lib.xattn_b200_plan_bytes(0, 1, 1) == 0
     # rows padded to 4 words twice, 4 words per query tile, 2 per key tile padded to 4
     assert lib.xattn_b200_plan_bytes(1, 130, 300) == 4 * (2 * 132 + 4 * 2 + 8)
-    assert lib.xattn_b200_bwd_workspace_bytes(2, 4, 100) == 2 * 4 * 128 * 2 * 4   # rows padded to 128
+    assert lib.xattn_b200_bwd_workspace_bytes(2, 4, 100) == 2 * 4 * 128 * (2 * 4 + 32)   # rows padded to 128
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

@@ -37,9 +37,10 @@ int xattn_b200_fwd(const XattnFwdArgs* args, xattn_stream_t stream) {
 
 size_t xattn_b200_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len) {
   if (batch <= 0 || q_heads <= 0 || q_len <= 0) return 0;
-  // two FP32 words per (batch row, query head, query row), rows padded to whole 128-row tiles
+  // per (batch row, query head, query row), rows padded to whole 128-row tiles: two FP32 words
+  // (-delta, -lse * log2e) and one 32-byte row of extra GEMM columns carrying the same numbers
   const size_t padded = ((size_t)q_len + 127) / 128 * 128;
-  return (size_t)batch * q_heads * padded * 2 * sizeof(float);
+  return (size_t)batch * q_heads * padded * (2 * sizeof(float) + 32);
 }
 
 int xattn_b200_bwd(const XattnBwdArgs* args, xattn_stream_t stream) {

@@ -33,6 +33,7 @@ struct BwdParams {
   int LqPad;                  // q_len rounded up to whole 128-row tiles: row stride of nlse2 / ndelta
   const float* nlse2;         // [B][Hq][LqPad]  -lse * log2e; -inf for rows without keys and padding
   const float* ndelta;        // [B][Hq][LqPad]  -rowsum(dy * y); 0 in the padding
+  const void* row_terms;      // [B][Hq][LqPad][16] bf16: the same two numbers as extra GEMM columns
   void* dq;                   // [B][Lq][Hq][D]
   void* dk;                   // [B][Lk][Hkv][D]
   void* dv;                   // [B][Lk][Hkv][V]
@@ -42,12 +43,37 @@ struct BwdParams {
 // ---------------------------------------------------------------------------
 // preprocess: one warp per (batch, row, head)
 // ---------------------------------------------------------------------------
+// The dK / dV kernel works on S^T and dP^T, where the per-query numbers lse and delta belong to
+// COLUMNS: every thread would need all of them for every step, and filling registers with them
+// costs more load bandwidth than the tensor products leave.  So they ride along in the products
+// instead.  One extra k-step of 16 columns is appended to Q and dO (this 32-byte row per query)
+// and to K and V (constant rows of ones and zeros):
+//   S^T + (-lse / scale)  =  [K | 1 1 1 0 ..] [Q | t0 t1 t2 0 ..]^T     t0 + t1 + t2 = -lse / scale
+//   dP^T + (-delta)       =  [V | 0 0 0 1 1 1 0 ..] [dO | 0 0 0 d0 d1 d2 0 ..]^T
+// with each number split into three bf16 terms (24 significant bits) and FP32 accumulation.
+// Rows without keys and padding rows get a huge negative first term, so that P = 0 for them.
+__device__ __forceinline__ void write_row_terms(uint4* dst, float t, float d) {
+  if (!(t > -1e30f)) t = -1.2676506e30f;          // -2^100, exact in bf16
+  const __nv_bfloat16 t0 = __float2bfloat16_rn(t);
+  const float tr = t - __bfloat162float(t0);
+  const __nv_bfloat16 t1 = __float2bfloat16_rn(tr);
+  const __nv_bfloat16 t2 = __float2bfloat16_rn(tr - __bfloat162float(t1));
+  const __nv_bfloat16 d0 = __float2bfloat16_rn(d);
+  const float dr = d - __bfloat162float(d0);
+  const __nv_bfloat16 d1 = __float2bfloat16_rn(dr);
+  const __nv_bfloat16 d2 = __float2bfloat16_rn(dr - __bfloat162float(d1));
+  auto bits = [](__nv_bfloat16 x) -> uint32_t { return (uint32_t)__bfloat16_as_ushort(x); };
+  dst[0] = make_uint4(bits(t0) | (bits(t1) << 16), bits(t2) | (bits(d0) << 16), bits(d1) | (bits(d2) << 16), 0u);
+  dst[1] = make_uint4(0u, 0u, 0u, 0u);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, const T* __restrict__ y,
                                                       const float* __restrict__ lse, int B, int Lq, int Hq, int V,
                                                       int64_t dy_sb, int64_t dy_sl, int64_t dy_sh, int64_t y_sb,
-                                                      int64_t y_sl, int64_t y_sh, int LqPad,
-                                                      float* __restrict__ ndelta, float* __restrict__ nlse2) {
+                                                      int64_t y_sl, int64_t y_sh, int LqPad, float scale,
+                                                      float* __restrict__ ndelta, float* __restrict__ nlse2,
+                                                      uint4* __restrict__ row_terms) {
   const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (w >= (long long)B * LqPad * Hq) return;
@@ -61,6 +87,7 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, 
       const size_t idx = ((size_t)b * Hq + h) * LqPad + i;
       ndelta[idx] = 0.f;
       nlse2[idx] = -INFINITY;
+      write_row_terms(row_terms + 2 * idx, -INFINITY, 0.f);
     }
     return;
   }
@@ -87,6 +114,7 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, 
     ndelta[idx] = -acc;
     const float l = lse[((size_t)b * Hq + h) * Lq + i];
     nlse2[idx] = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
+    write_row_terms(row_terms + 2 * idx, (l == -INFINITY) ? -INFINITY : -l / scale, -acc);
   }
 }
 
@@ -402,11 +430,16 @@ template <int HD, int MODE, int SM>
 struct DkvSmem {
   static constexpr int kKvBytes = kBlockN * HD * 2;
   static constexpr int kQBytes = SM * HD * 2;
-  static constexpr int kStages = MODE == kDkvBoth ? 4 : 2;
+  static constexpr int kStages = (MODE == kDkvBoth && SM <= 64) ? 4 : 2;
   alignas(1024) uint8_t k[kKvBytes];
   alignas(1024) uint8_t v[MODE == kDvOnly ? 1024 : kKvBytes];
   alignas(1024) uint8_t q[kStages][kQBytes];
   alignas(1024) uint8_t d_o[kStages][kQBytes];
+  // the extra k-step: per-query rows (-lse / scale and -delta in bf16 terms) of each stage, and the
+  // constant rows of ones that pick them up on the key side (32-byte rows, 32-byte swizzle)
+  alignas(1024) uint8_t terms[kStages][SM * 32];
+  alignas(1024) uint8_t ones_s[kBlockN * 32];
+  alignas(1024) uint8_t ones_dp[kBlockN * 32];
   uint64_t kv_full;
   uint64_t q_full[kStages], q_empty[kStages];
   // per TMEM buffer: S^T / dP^T written by their products, P^T / dS^T written by the warpgroups,
@@ -468,13 +501,14 @@ struct DkvIter {
 // warps 0-3 / 4-7: element-wise warpgroups, thread = (key row, half of the sub-tile's query columns).
 // warp 8: issuer of S^T / dP^T, warp 10: issuer of dV / dK (an issuing thread stalls while its
 // products run, so the two kinds get a thread each), warp 9: TMA producer + TMEM owner, warp 11 idle.
-// Sub-tiles alternate between two TMEM buffers, so the products of one run under the element-wise
-// work of the other.
+// With two S^T / dP^T buffers (SM <= 64) sub-tiles alternate between them.  With one (SM = 128, the
+// widest products: a tcgen05.mma costs about the same for 64 columns as for 128) the
+// S^T -> P^T -> dV and dP^T -> dS^T -> dK chains of a step overlap each other and the next step's S^T.
 template <typename T, int HD, int MODE, int SM>
 __global__ void __launch_bounds__(384, 1)
 bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-               const BwdParams p) {
+               const __grid_constant__ CUtensorMap tm_terms, const BwdParams p) {
   using Smem = DkvSmem<HD, MODE, SM>;
   using Iter = DkvIter<SM>;
   constexpr int kStages = Smem::kStages;
@@ -483,7 +517,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   constexpr int kQBox = SM * 64 * 2;           // 64-column box of an SM-row tile
   constexpr uint32_t kTmemCols = 512;
   constexpr int kFormat = Pack2<T>::kFormat;
-  // TMEM columns: S^T buffers at 0 / SM, dP^T buffers at 128 / 128 + SM, accumulators from 256
+  // TMEM columns: S^T buffer(s) from 0, dP^T buffer(s) from 128, accumulators from 256.  Two
+  // buffers of each while they fit 128 columns (SM <= 64), else one.
+  constexpr int kBufs = SM <= 64 ? 2 : 1;
   constexpr uint32_t cS = 0, cDP = 128;
   constexpr uint32_t cDK = 256, cDV = MODE == kDkvBoth ? 384 : 256;
 
@@ -512,6 +548,17 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     fence_mbar_init();
   }
   if (warp == 9) { tmem_alloc(&s.tmem_base, kTmemCols); tmem_relinquish(); }
+  if (tid < kBlockN) {
+    // key-side rows of the extra k-step: bf16 ones in columns 0-2 (S^T) or 3-5 (dP^T), the same
+    // in both 16-byte halves of the row so that the swizzle cannot matter (the query-side rows
+    // are zero in their second half)
+    const uint4 os = make_uint4(0x3f803f80u, 0x00003f80u, 0u, 0u);
+    const uint4 od = make_uint4(0u, 0x3f800000u, 0x3f803f80u, 0u);
+    uint4* ps = reinterpret_cast<uint4*>(s.ones_s + tid * 32);
+    uint4* pd = reinterpret_cast<uint4*>(s.ones_dp + tid * 32);
+    ps[0] = os; ps[1] = os; pd[0] = od; pd[1] = od;
+    fence_proxy_async_smem();
+  }
   const int cache_n = min(max(kti.m_end - kti.m_first, 0), Smem::kTileCache);
   for (int base = 0; base < Smem::kTileCache; base += 384) {
     const int i = base + tid;
@@ -544,6 +591,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   } else if (warp < 8) {
     // ------------------------ element-wise warpgroups ------------------------
     constexpr int kHalf = SM / 2;             // query columns per warpgroup and step
+    constexpr int kChunk = kHalf < 32 ? kHalf : 32;   // columns per TMEM load / store
+    constexpr int kPerLane = kHalf / kChunk;  // lo / hi columns each lane looks after
     const int wg = warp >> 2;                 // which half of the columns
     const int wt = tid & 127;
     const int r = wt;                         // key row inside the tile
@@ -561,118 +610,115 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       bit = 0;
       return ((n * kBlockN >= t.max_lo) && ((n + 1) * kBlockN <= t.min_hi)) ? 1u : 0u;
     };
-    // Per-query scalars of this warpgroup's columns come straight from global memory into
-    // registers, a step ahead of their use and never touched in between (an instruction using a
-    // loaded value stalls the warp for the load's whole latency; shared memory is slow while the
-    // tensor pipe streams operands from it).  -lse2 and -delta: every thread reads the same kHalf
-    // values, into the registers the previous step just finished with.  lo / hi: lane c reads those
-    // of column c and a step that masks hands them round by shuffle.
-    auto scal_row = [&](const Iter& item, const float* base) -> const float4* {
-      return reinterpret_cast<const float4*>(base + ((size_t)b * p.Hq + kvh * G + item.g) * p.LqPad + item.row0() +
-                                             wg * kHalf);
-    };
-    auto bound_index = [&](const Iter& item) -> size_t {
-      const int qrow = item.row0() + wg * kHalf + (lane & (kHalf - 1));
+    // lse and delta of the query columns arrive inside S^T and dP^T (the extra k-step), so the
+    // only per-column numbers left are the visible-key bounds of a step that masks: lane c reads
+    // lo / hi of columns c, c + 32, ... straight from global memory a step ahead, never touching
+    // them in between (an instruction using a loaded value stalls the warp for the load's whole
+    // latency), and hands them round by shuffle.
+    auto bound_index = [&](const Iter& item, int j) -> size_t {
+      const int qrow = item.row0() + wg * kHalf + j * kChunk + (lane & (kChunk - 1));
       return (size_t)b * p.Lq + (qrow < p.Lq ? qrow : p.Lq - 1);
     };
-    float nl[kHalf], nd[kHalf];
-    int my_lo = 0, my_hi = 0;
+    int my_lo[kPerLane], my_hi[kPerLane];
     Iter it = it0;
     uint32_t fw = 0;
     int fbit = 0;
     if (it.valid()) {
-      const float4* l4 = scal_row(it, p.nlse2);
-      const float4* d4 = scal_row(it, p.ndelta);
 #pragma unroll
-      for (int c = 0; c < kHalf; c += 4) {
-        *reinterpret_cast<float4*>(nl + c) = __ldg(l4 + (c >> 2));
-        if (kWantDk) *reinterpret_cast<float4*>(nd + c) = __ldg(d4 + (c >> 2));
+      for (int j = 0; j < kPerLane; ++j) {
+        const size_t bi = bound_index(it, j);
+        my_lo[j] = p.row_lo[bi]; my_hi[j] = p.row_hi[bi];
       }
-      const size_t bi = bound_index(it);
-      my_lo = p.row_lo[bi]; my_hi = p.row_hi[bi];
       fw = full_word(it.m, fbit);
     }
     int kk = 0;
     while (it.valid() && ok) {
-      const int sub = kk & 1;                 // TMEM buffer of this step
+      const int sub = kk % kBufs;             // TMEM buffer of this step
+      const uint32_t ph = (kk / kBufs) & 1;   // and the phase of its barriers
       Iter n1 = it; n1.next();
       const bool tile_full = (fw >> fbit) & 1u;
       // which of this thread's columns see its key, as bits
-      uint32_t seen = 0xffffffffu;
-      if (!tile_full) {
-        const bool col_live = it.row0() + wg * kHalf + (lane & (kHalf - 1)) < p.Lq;
-        const int lo_c = col_live ? my_lo : 0, hi_c = col_live ? my_hi : 0;
-        seen = 0u;
+      uint32_t seen[kPerLane];
 #pragma unroll
-        for (int c = 0; c < kHalf; ++c) {
-          const int lo = __shfl_sync(0xffffffffu, lo_c, c), hi = __shfl_sync(0xffffffffu, hi_c, c);
-          seen |= (key >= lo && key < hi ? 1u : 0u) << c;
+      for (int j = 0; j < kPerLane; ++j) {
+        seen[j] = 0xffffffffu;
+        if (!tile_full) {
+          const bool col_live = it.row0() + wg * kHalf + j * kChunk + (lane & (kChunk - 1)) < p.Lq;
+          const int lo_c = col_live ? my_lo[j] : 0, hi_c = col_live ? my_hi[j] : 0;
+          seen[j] = 0u;
+#pragma unroll
+          for (int c = 0; c < kChunk; ++c) {
+            const int lo = __shfl_sync(0xffffffffu, lo_c, c), hi = __shfl_sync(0xffffffffu, hi_c, c);
+            seen[j] |= (key >= lo && key < hi ? 1u : 0u) << c;
+          }
         }
       }
       if (n1.valid()) {
-        const size_t bi = bound_index(n1);
-        my_lo = p.row_lo[bi]; my_hi = p.row_hi[bi];
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j) {
+          const size_t bi = bound_index(n1, j);
+          my_lo[j] = p.row_lo[bi]; my_hi[j] = p.row_hi[bi];
+        }
         fw = full_word(n1.m, fbit);
       }
       const uint32_t t_s = tmem + lane_off + cS + sub * SM + wg * kHalf;
       const uint32_t t_dp = tmem + lane_off + cDP + sub * SM + wg * kHalf;
-      // ---- P^T = exp2(S^T * c - lse2), masked ----
-      ok = mbar_wait(ctx, &s.s_full[sub], (kk >> 1) & 1, 80);
+      // ---- P^T = exp2((S^T - lse / scale) * c), masked ----
+      ok = mbar_wait(ctx, &s.s_full[sub], ph, 80);
       if (!ok) break;
       tc_fence_after();
       float pv[kHalf];
-      if (kHalf == 32) tmem_ld_x32(t_s, reinterpret_cast<uint32_t*>(pv));
-      else tmem_ld_x16(t_s, reinterpret_cast<uint32_t*>(pv));
+#pragma unroll
+      for (int j = 0; j < kPerLane; ++j) {
+        if (kChunk == 32) tmem_ld_x32(t_s + j * kChunk, reinterpret_cast<uint32_t*>(pv) + j * kChunk);
+        else tmem_ld_x16(t_s + j * kChunk, reinterpret_cast<uint32_t*>(pv) + j * kChunk);
+      }
       tc_wait_ld();
 #pragma unroll
-      for (int c = 0; c < kHalf; c += 2) {
-        const float2 e = ex2_pair_sfu(fma2(make_float2(pv[c], pv[c + 1]), cc, make_float2(nl[c], nl[c + 1])));
-        pv[c] = e.x; pv[c + 1] = e.y;
-      }
-      if (!tile_full) {
+      for (int j = 0; j < kPerLane; ++j) {
 #pragma unroll
-        for (int c = 0; c < kHalf; ++c) pv[c] = ((seen >> c) & 1u) ? pv[c] : 0.f;
-      }
-      // the 16-bit results go over the first half of the warpgroup's own columns
-      if (kWantDv) {
-        uint32_t pp[kHalf / 2];
+        for (int c = j * kChunk; c < (j + 1) * kChunk; c += 2) {
+          const float2 e = ex2_pair_sfu(mul2(make_float2(pv[c], pv[c + 1]), cc));
+          pv[c] = e.x; pv[c + 1] = e.y;
+        }
+        if (!tile_full) {
 #pragma unroll
-        for (int c = 0; c < kHalf; c += 2) pp[c >> 1] = Pack2<T>::pack(pv[c], pv[c + 1]);
-        if (kHalf == 32) tmem_st_x16(t_s, pp); else tmem_st_x8(t_s, pp);
-        tc_wait_st();
+          for (int c = 0; c < kChunk; ++c) pv[j * kChunk + c] = ((seen[j] >> c) & 1u) ? pv[j * kChunk + c] : 0.f;
+        }
+        // the 16-bit results go over the first half of the chunk's own columns
+        if (kWantDv) {
+          uint32_t pp[kChunk / 2];
+#pragma unroll
+          for (int c = 0; c < kChunk; c += 2) pp[c >> 1] = Pack2<T>::pack(pv[j * kChunk + c], pv[j * kChunk + c + 1]);
+          if (kChunk == 32) tmem_st_x16(t_s + j * kChunk, pp); else tmem_st_x8(t_s + j * kChunk, pp);
+        }
       }
+      if (kWantDv) tc_wait_st();
       tc_fence_before();
       mbar_arrive_warp(&s.p_full[sub]);       // also: S^T has been read
-      if (n1.valid()) {
-        const float4* l4 = scal_row(n1, p.nlse2);
-#pragma unroll
-        for (int c = 0; c < kHalf; c += 4) *reinterpret_cast<float4*>(nl + c) = __ldg(l4 + (c >> 2));
-      }
-      // ---- dS^T = P^T * (dP^T - delta) ----
+      // ---- dS^T = P^T * (dP^T - delta), the subtraction already done by the product ----
       if (kWantDk) {
-        ok = mbar_wait(ctx, &s.dp_full[sub], (kk >> 1) & 1, 83);
+        ok = mbar_wait(ctx, &s.dp_full[sub], ph, 83);
         if (!ok) break;
         tc_fence_after();
-        float dpv[kHalf];
-        if (kHalf == 32) tmem_ld_x32(t_dp, reinterpret_cast<uint32_t*>(dpv));
-        else tmem_ld_x16(t_dp, reinterpret_cast<uint32_t*>(dpv));
-        tc_wait_ld();
-        uint32_t pd[kHalf / 2];
 #pragma unroll
-        for (int c = 0; c < kHalf; c += 2) {
-          const float2 d = mul2(make_float2(pv[c], pv[c + 1]),
-                                add2(make_float2(dpv[c], dpv[c + 1]), make_float2(nd[c], nd[c + 1])));
-          pd[c >> 1] = Pack2<T>::pack(d.x, d.y);
+        for (int j = 0; j < kPerLane; ++j) {
+          float dpv[kChunk];
+          if (kChunk == 32) tmem_ld_x32(t_dp + j * kChunk, reinterpret_cast<uint32_t*>(dpv));
+          else tmem_ld_x16(t_dp + j * kChunk, reinterpret_cast<uint32_t*>(dpv));
+          tc_wait_ld();
+          uint32_t pd[kChunk / 2];
+#pragma unroll
+          for (int c = 0; c < kChunk; c += 2) {
+            const int g2 = j * kChunk + c;
+            const float2 d = mul2(make_float2(pv[g2], pv[g2 + 1]), make_float2(dpv[c], dpv[c + 1]));
+            pd[c >> 1] = Pack2<T>::pack(d.x, d.y);
+          }
+          if (kChunk == 32) tmem_st_x16(t_dp + j * kChunk, pd); else tmem_st_x8(t_dp + j * kChunk, pd);
         }
-        if (kHalf == 32) tmem_st_x16(t_dp, pd); else tmem_st_x8(t_dp, pd);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive_warp(&s.ds_full[sub]);
-        if (n1.valid()) {
-          const float4* d4 = scal_row(n1, p.ndelta);
-#pragma unroll
-          for (int c = 0; c < kHalf; c += 4) *reinterpret_cast<float4*>(nd + c) = __ldg(d4 + (c >> 2));
-        }
       }
       it = n1;
       ++kk;
@@ -717,14 +763,16 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   } else if (warp == 8 && lane == 0 && any_work) {
     // ------------------------------ S^T / dP^T issuer ------------------------------
     const uint32_t idesc_st = make_idesc(kBlockN, SM, kFormat, 0, 0);
+    const uint32_t idesc_terms = make_idesc(kBlockN, SM, 1, 0, 0);      // the extra k-step is bf16 whatever T is
     const uint32_t ka = smem_u32(s.k), va = smem_u32(s.v);
     bool ok = mbar_wait(ctx, &s.kv_full, 0, 90);
     int cnt = 0;
     for (Iter it = it0; it.valid() && ok; it.next(), ++cnt) {
-      const int buf = cnt & 1, st = cnt % kStages;
+      const int buf = cnt % kBufs, st = cnt % kStages;
+      const uint32_t prev = ((cnt / kBufs) - 1) & 1;     // phase of the buffer's previous use
       ok = mbar_wait(ctx, &s.q_full[st], (cnt / kStages) & 1, 91);
       // the buffer's previous P^T has been read by its dV product
-      if (ok && cnt >= 2) ok = mbar_wait(ctx, &s.s_free[buf], ((cnt >> 1) - 1) & 1, 93);
+      if (ok && cnt >= kBufs) ok = mbar_wait(ctx, &s.s_free[buf], prev, 93);
       if (!ok) break;
       tc_fence_after();
       const uint32_t qa = smem_u32(s.q[st]), da = smem_u32(s.d_o[st]);
@@ -732,29 +780,36 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         umma_ss(tmem + cS + buf * SM, make_smem_desc(ka + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024),
                 make_smem_desc(qa + (js >> 2) * kQBox + (js & 3) * 32, 16, 1024), idesc_st, js > 0);
       }
+      umma_ss(tmem + cS + buf * SM, make_smem_desc_sw32(smem_u32(s.ones_s)), make_smem_desc_sw32(smem_u32(s.terms[st])),
+              idesc_terms, 1u);
       umma_commit(&s.s_full[buf]);
       if (kWantDk) {
-        if (cnt >= 2) ok = mbar_wait(ctx, &s.dp_free[buf], ((cnt >> 1) - 1) & 1, 95);
+        if (cnt >= kBufs) ok = mbar_wait(ctx, &s.dp_free[buf], prev, 95);
         if (!ok) break;
         tc_fence_after();
         for (int js = 0; js < ksteps_v; ++js) {
           umma_ss(tmem + cDP + buf * SM, make_smem_desc(va + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024),
                   make_smem_desc(da + (js >> 2) * kQBox + (js & 3) * 32, 16, 1024), idesc_st, js > 0);
         }
+        umma_ss(tmem + cDP + buf * SM, make_smem_desc_sw32(smem_u32(s.ones_dp)),
+                make_smem_desc_sw32(smem_u32(s.terms[st])), idesc_terms, 1u);
         umma_commit(&s.dp_full[buf]);
       }
     }
   } else if (warp == 10 && lane == 0 && any_work) {
     // ------------------------------ dV / dK issuer ------------------------------
-    constexpr int kHalf = SM / 2, kStepsPerHalf = kHalf / 16;
+    // P^T / dS^T: each 32-column chunk (16 for SM = 32) of S^T / dP^T holds its packed results in
+    // its own first half, so k-step js (16 query rows) sits at chunk js / kStepsPerChunk
+    constexpr int kChunk = SM / 2 < 32 ? SM / 2 : 32, kStepsPerChunk = kChunk / 16;
     const uint32_t idesc_dv = make_idesc(kBlockN, v_pad, kFormat, 0, 1);
     const uint32_t idesc_dk = make_idesc(kBlockN, d_pad, kFormat, 0, 1);
     bool ok = true;
     int cnt = 0;
     for (Iter it = it0; it.valid() && ok; it.next(), ++cnt) {
-      const int buf = cnt & 1, st = cnt % kStages;
+      const int buf = cnt % kBufs, st = cnt % kStages;
+      const uint32_t ph = (cnt / kBufs) & 1;
       ok = mbar_wait(ctx, &s.q_full[st], (cnt / kStages) & 1, 94);
-      if (ok) ok = mbar_wait(ctx, &s.p_full[buf], (cnt >> 1) & 1, 92);
+      if (ok) ok = mbar_wait(ctx, &s.p_full[buf], ph, 92);
       if (!ok) break;
       tc_fence_after();
       const uint32_t qa = smem_u32(s.q[st]), da = smem_u32(s.d_o[st]);
@@ -762,18 +817,18 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (kWantDv) {
 #pragma unroll
         for (int js = 0; js < SM / 16; ++js) {
-          const uint32_t a_col = tmem + cS + buf * SM + (js / kStepsPerHalf) * kHalf + (js % kStepsPerHalf) * 8;
+          const uint32_t a_col = tmem + cS + buf * SM + (js / kStepsPerChunk) * kChunk + (js % kStepsPerChunk) * 8;
           umma_ts(tmem + cDV, a_col, make_smem_desc(da + js * 2048, kQBox, 1024), idesc_dv, (cnt > 0 || js > 0) ? 1u : 0u);
         }
       }
       umma_commit(&s.s_free[buf]);
       if (kWantDk) {
-        ok = mbar_wait(ctx, &s.ds_full[buf], (cnt >> 1) & 1, 96);
+        ok = mbar_wait(ctx, &s.ds_full[buf], ph, 96);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int js = 0; js < SM / 16; ++js) {
-          const uint32_t a_col = tmem + cDP + buf * SM + (js / kStepsPerHalf) * kHalf + (js % kStepsPerHalf) * 8;
+          const uint32_t a_col = tmem + cDP + buf * SM + (js / kStepsPerChunk) * kChunk + (js % kStepsPerChunk) * 8;
           umma_ts(tmem + cDK, a_col, make_smem_desc(qa + js * 2048, kQBox, 1024), idesc_dk, (cnt > 0 || js > 0) ? 1u : 0u);
         }
         umma_commit(&s.dp_free[buf]);
@@ -784,6 +839,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   } else if (warp == 9 && lane == 0 && any_work) {
     // ------------------------------ TMA producer ------------------------------
     tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_do); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_terms);
     mbar_arrive_expect_tx(&s.kv_full, nbox_qk * kKvBox + (kWantDk ? nbox_v * kKvBox : 0));
     for (int bx = 0; bx < nbox_qk; ++bx) tma_load_4d(s.k + bx * kKvBox, &tm_k, &s.kv_full, bx * 64, kvh, n * kBlockN, b);
     if (kWantDk) {
@@ -797,7 +853,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (!ok) break;
       const int h = kvh * G + it.g;
       const int row0 = it.row0();
-      mbar_arrive_expect_tx(&s.q_full[st], (nbox_qk + nbox_v) * kQBox);
+      mbar_arrive_expect_tx(&s.q_full[st], (nbox_qk + nbox_v) * kQBox + SM * 32);
+      tma_load_4d(s.terms[st], &tm_terms, &s.q_full[st], 0, row0, h, b);
       for (int bx = 0; bx < nbox_qk; ++bx) tma_load_4d(s.q[st] + bx * kQBox, &tm_q, &s.q_full[st], bx * 64, h, row0, b);
       for (int bx = 0; bx < nbox_v; ++bx) tma_load_4d(s.d_o[st] + bx * kQBox, &tm_do, &s.q_full[st], bx * 64, h, row0, b);
     }
@@ -842,6 +899,8 @@ static int launch_dkv(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t st
   if (make_tile_map(&tdo, a.dy, a.dtype, a.batch, a.q_len, a.q_heads, a.v_dim, a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], SM)) return XATTN_E_INVALID;
   if (make_tile_map(&tk, a.k, a.dtype, a.batch, a.k_len, a.kv_heads, a.qk_dim, a.k_strides[0], a.k_strides[1], a.k_strides[2], kBlockN)) return XATTN_E_INVALID;
   if (make_tile_map(&tv, a.v, a.dtype, a.batch, a.k_len, a.kv_heads, a.v_dim, a.v_strides[0], a.v_strides[1], a.v_strides[2], kBlockN)) return XATTN_E_INVALID;
+  CUtensorMap tt;
+  if (make_row_map(&tt, p.row_terms, p.B, p.Hq, p.LqPad, SM)) return XATTN_E_INVALID;
   auto kern = bwd_dkv_kernel<T, HD, MODE, SM>;
   const size_t smem = sizeof(DkvSmem<HD, MODE, SM>) + 1024;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -850,7 +909,7 @@ static int launch_dkv(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t st
   if (grid > 0x7fffffffLL) { set_error("dK/dV grid out of range"); return XATTN_E_INVALID; }
   {
     ProfileScope prof(kProfBwdDkv, stream);
-    kern<<<(unsigned)grid, 384, smem, stream>>>(tq, tdo, tk, tv, p);
+    kern<<<(unsigned)grid, 384, smem, stream>>>(tq, tdo, tk, tv, tt, p);
   }
   return XATTN_OK;
 }
@@ -858,9 +917,12 @@ static int launch_dkv(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t st
 template <typename T>
 static int launch_bwd(const XattnBwdArgs& a, BwdParams& p, cudaStream_t stream) {
   // 1. preprocess
+  // workspace: -delta, -lse2 (FP32 each), then the 32-byte rows of extra GEMM columns
+  const size_t rows = (size_t)p.B * p.Hq * p.LqPad;
   float* ndelta = a.workspace;
-  float* nlse2 = a.workspace + (size_t)p.B * p.Hq * p.LqPad;
-  p.ndelta = ndelta; p.nlse2 = nlse2;
+  float* nlse2 = a.workspace + rows;
+  uint4* row_terms = reinterpret_cast<uint4*>(a.workspace + 2 * rows);
+  p.ndelta = ndelta; p.nlse2 = nlse2; p.row_terms = row_terms;
   {
     const long long warps = (long long)p.B * p.LqPad * p.Hq;
     const long long blocks = (warps * 32 + 255) / 256;
@@ -868,17 +930,17 @@ static int launch_bwd(const XattnBwdArgs& a, BwdParams& p, cudaStream_t stream) 
     bwd_pre_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
         reinterpret_cast<const T*>(a.dy), reinterpret_cast<const T*>(a.y), a.lse, p.B, p.Lq, p.Hq, p.V,
         a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], a.y_strides[0], a.y_strides[1], a.y_strides[2], p.LqPad,
-        ndelta, nlse2);
+        p.scale, ndelta, nlse2, row_terms);
   }
   const int hd = p.D > p.V ? p.D : p.V;
   int rc;
   // 2. dQ   3. dK / dV
   if (hd <= 64) {
     if ((rc = launch_dq<T, 64, 128>(a, p, stream))) return rc;
-    if ((rc = launch_dkv<T, 64, kDkvBoth, 64>(a, p, stream))) return rc;
+    if ((rc = launch_dkv<T, 64, kDkvBoth, 128>(a, p, stream))) return rc;
   } else if (hd <= 128) {
     if ((rc = launch_dq<T, 128, 128>(a, p, stream))) return rc;
-    if ((rc = launch_dkv<T, 128, kDkvBoth, 64>(a, p, stream))) return rc;
+    if ((rc = launch_dkv<T, 128, kDkvBoth, 128>(a, p, stream))) return rc;
   } else {
     if ((rc = launch_dq<T, 256, 64>(a, p, stream))) return rc;
     if ((rc = launch_dkv<T, 256, kDvOnly, 64>(a, p, stream))) return rc;

@@ -1,7 +1,8 @@
 // Backward pass for callers that must not allocate device memory.
 //
 // The regular backward entry takes a caller-provided workspace (two FP32 words per batch row, query
-// head and query position, positions padded to whole 128-row tiles: -rowsum(dy*y) and -lse*log2e).  Some callers cannot provide one: a plugin
+// head and query position, positions padded to whole 128-row tiles: -rowsum(dy*y) and -lse*log2e,
+// plus a 32-byte row that carries the same two numbers into the tensor products).  Some callers cannot provide one: a plugin
 // host that owns the whole device arena and hands an op nothing but its input and output buffers,
 // or a serving loop where a cudaMalloc would stall every stream of the device at an unpredictable
 // moment.  For them the same kernels run here with the workspace in a fixed array that lives in the
@@ -9,7 +10,7 @@
 //
 // Costs and rules:
 //  * the array is part of the module, so every GPU that loads the library holds its
-//    kStaticRows * 8 bytes (8 MiB) until the process exits, used or not;
+//    kStaticRows * 40 bytes (40 MiB) until the process exits, used or not;
 //  * batch * q_heads * q_len may not exceed kStaticRows; larger problems are refused with
 //    XATTN_E_INVALID before anything is launched;
 //  * every call on a device shares the one array.  The preprocess kernel rewrites all entries it
@@ -30,7 +31,7 @@ constexpr long long kStaticRows = 1ll << 20;   // batch * q_heads * (q_len round
 constexpr int kMaxDevices = 64;
 
 // bwd_entry lays its two arrays out back to back from the start of whatever workspace it is given
-static __device__ __align__(256) float g_static_workspace[2 * kStaticRows];
+static __device__ __align__(256) float g_static_workspace[10 * kStaticRows];   // 40 bytes per row
 
 std::mutex g_static_mutex;
 float* g_static_ptr[kMaxDevices] = {};

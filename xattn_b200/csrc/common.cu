@@ -57,6 +57,21 @@ int make_tile_map(CUtensorMap* out, const void* base, int dtype, int64_t B, int6
   return 0;
 }
 
+int make_row_map(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_t L, int box_rows) {
+  TensorMapEncodeFn enc = tensor_map_encoder();
+  if (!enc) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return -1; }
+  if (reinterpret_cast<uintptr_t>(base) & 15) { set_error("tensor base must be 16-byte aligned"); return -1; }
+  cuuint64_t dims[4] = {16, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {32, (cuuint64_t)L * 32, (cuuint64_t)H * L * 32};
+  cuuint32_t box[4] = {16, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t elem[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (row map) failed with code %d", (int)r); return -1; }
+  return 0;
+}
+
 // ---- optional per-kernel timing -------------------------------------------------
 namespace {
 struct ProfRecord { int kind; cudaEvent_t start, stop; };

@@ -60,6 +60,10 @@ TensorMapEncodeFn tensor_map_encoder();
 // Returns 0 on success.
 int make_tile_map(CUtensorMap* out, const void* base, int dtype, int64_t B, int64_t L, int64_t H, int64_t D,
                   int64_t sb, int64_t sl, int64_t sh, int box_rows);
+// Tensor map over a contiguous [B][H][L][16] bf16 tensor (32-byte rows): boxes of `box_rows` rows of
+// one (batch, head), written to shared memory in the 32-byte-swizzle K-major layout.
+// Coordinates: (0, row, head, batch).
+int make_row_map(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_t L, int box_rows);
 
 // Last error text of this thread (set by the host entry points).
 void set_error(const char* fmt, ...);

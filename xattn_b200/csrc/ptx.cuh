@@ -206,6 +206,18 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
   return d;
 }
 
+// K-major operand with 32-byte rows (one k-step of 16 16-bit elements) in the 32-byte swizzle:
+// row pitch 32 bytes, groups of 8 rows 256 bytes apart.  The tile base must be 256-byte aligned.
+__device__ __forceinline__ uint64_t make_smem_desc_sw32(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;            // leading offset: unused with a single 32-byte atom in K
+  d |= static_cast<uint64_t>(256 >> 4) << 32;     // 8-row groups
+  d |= static_cast<uint64_t>(1) << 46;            // descriptor version (Blackwell)
+  d |= static_cast<uint64_t>(6) << 61;            // SWIZZLE_32B
+  return d;
+}
+
 // Instruction descriptor for tcgen05.mma kind::f16 with FP32 accumulation.
 //   ab_format: 0 = fp16, 1 = bf16.  *_mn_major: 1 when the operand's M/N
 //   dimension is the contiguous one in shared memory.
