@@ -18,6 +18,15 @@
 // :1261-1324), dQ here has its own query-stationary kernel.
 #include "common.cuh"
 
+// of every four pairs of exponentials, how many run on the FMA pipe instead of the special-function
+// unit: dK / dV kernel (no gain measured there) and dQ kernel
+#ifndef XB_DKV_FMA_PAIRS
+#define XB_DKV_FMA_PAIRS 0
+#endif
+#ifndef XB_DQ_FMA_PAIRS
+#define XB_DQ_FMA_PAIRS 1
+#endif
+
 namespace xb {
 
 struct BwdParams {
@@ -122,47 +131,55 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, 
 // ---------------------------------------------------------------------------
 // dQ kernel
 // ---------------------------------------------------------------------------
-// HD <= 128: key tiles of BN = 128; TMEM holds Q (packed), dS, S, dP and dQ side by side, so
-//            S / dP of the next key tile are issued while dS of the current one is being built.
-// HD  = 256: BN = 64 and dS overwrites S in place (Q takes 128 columns and dQ 256), so the
-//            tensor core alternates S, dP -> dQ per key tile.
+// One CTA owns 128 query rows of one head and walks the key tiles they see:
+//   S = Q K^T, dP = dO V^T  ->  P = exp2(S c - lse2), dS = P (dP - delta)  ->  dQ += dS K.
+// Q, the A operand of S for the whole life of the CTA, is staged in TMEM (packed); dO stays in
+// shared memory.
+// HD <= 128: key tiles of BN = 128.  TMEM: Q 0, dS 64 (packed), S 128, dP 256, dQ 384.
+// HD  = 256: BN = 64; no room for dS, which is written over dP.  TMEM: Q 0 (128 columns), S 128,
+//            dP 192, dQ 256.
+// S and dP are handed to the element-wise warpgroups separately, and the products have two issuing
+// threads (one stalls while its products run): S of the next key tile is issued as soon as this
+// one's S sits in registers, dP likewise (HD = 256: once dQ has read the dS lying over it), and dQ
+// as soon as dS is in TMEM.
 template <int HD, int BN>
 struct DqSmem {
   static constexpr int kDoBytes = kBlockM * HD * 2;
   static constexpr int kKvBytes = BN * HD * 2;
-  // K is held from S of its key tile until dQ of the same tile, V only for dP: one more K stage
-  // keeps the next S from waiting for a K buffer that dQ has just released
+  // K is held from S of its key tile until dQ of the same tile, V only for dP
   static constexpr int kKStages = HD <= 128 ? 3 : 2;
   alignas(1024) uint8_t d_o[kDoBytes];
   alignas(1024) uint8_t k[kKStages][kKvBytes];
   alignas(1024) uint8_t v[2][kKvBytes];
   uint64_t do_full, q_ready;
   uint64_t k_full[kKStages], k_empty[kKStages], v_full[2], v_empty[2];
-  uint64_t sdp_full, sdp_free, ds_full, dq_done;
+  uint64_t s_full, s_free, dp_full, dp_free, ds_full, dq_done;
   uint32_t tmem_base;
   int abort_flag;
 };
 
 // warps 0-3 / 4-7: element-wise warpgroups (thread = query row; first / second half of the key-tile columns)
-// warp 8: MMA issuer, warp 9: TMA producer + TMEM owner, warps 10-11: idle
+// warp 8: issuer of S and dP, warp 10: issuer of dQ (an issuing thread stalls while its products
+// run), warp 9: TMA producer + TMEM owner, warp 11: idle
 template <typename T, int HD, int BN>
 __global__ void __launch_bounds__(384, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const BwdParams p) {
   using Smem = DqSmem<HD, BN>;
-  constexpr bool kAlias = HD > 128;
+  constexpr bool kDsOverDp = HD > 128;          // no TMEM columns left for dS
   constexpr int kKStages = Smem::kKStages;
   constexpr int kDoBox = kBlockM * 64 * 2;     // 64-column box of the 128-row dO tile
   constexpr int kKvBox = BN * 64 * 2;          // 64-column box of a BN-row K / V tile
   constexpr int CH = BN / 2;                   // key columns per element-wise thread
   constexpr uint32_t kTmemCols = 512;
   constexpr int kFormat = Pack2<T>::kFormat;
-  // TMEM columns
-  constexpr uint32_t cQ = 0;
-  constexpr uint32_t cS = 128, cDP = kAlias ? 192 : 256;
-  constexpr uint32_t cDS = kAlias ? cS : 64;   // half hf of dS starts at cDS + hf * kDsStride
-  constexpr uint32_t kDsStride = kAlias ? CH : CH / 2;
-  constexpr uint32_t cDQ = kAlias ? 256 : 384;
+  // of every four pairs of exponentials, how many run on the FMA pipe
+  constexpr int kFmaPairs = XB_DQ_FMA_PAIRS;
+  // TMEM columns.  dS, packed: 16 columns per 32-column chunk of dP, side by side from cDS, or
+  // (HD = 256) over the first 16 columns of the chunk itself.
+  constexpr uint32_t cQ = 0, cDS = 64;
+  constexpr uint32_t cS = 128, cDP = kDsOverDp ? 192 : 256;
+  constexpr uint32_t cDQ = kDsOverDp ? 256 : 384;
 
   extern __shared__ uint8_t smem_raw[];
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -195,8 +212,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
     mbar_init(&s.q_ready, 8);
     for (int i = 0; i < kKStages; ++i) { mbar_init(&s.k_full[i], 1); mbar_init(&s.k_empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&s.v_full[i], 1); mbar_init(&s.v_empty[i], 1); }
-    mbar_init(&s.sdp_full, 1);
-    mbar_init(&s.sdp_free, 8);
+    mbar_init(&s.s_full, 1);
+    mbar_init(&s.s_free, 8);
+    mbar_init(&s.dp_full, 1);
+    mbar_init(&s.dp_free, 8);
     mbar_init(&s.ds_full, 8);
     mbar_init(&s.dq_done, 1);
     fence_mbar_init();
@@ -213,9 +232,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
   const int ksteps_qk = (p.D + 15) / 16, ksteps_v = (p.V + 15) / 16;
   const int d_pad = (p.D + 15) & ~15;
 
-  // 384 threads start with 168 registers each; the element-wise warpgroups take the MMA / TMA
-  // warpgroup's share
-  if (warp < 8) setmaxnreg_inc<216>(); else setmaxnreg_dec<40>();
+  // 384 threads start with 168 registers each; the element-wise warpgroups take most of the other
+  // warps' share
+  if (warp < 8) setmaxnreg_inc<216>(); else setmaxnreg_dec<72>();
   if (dead) {
   } else if (warp < 8) {
     const int hf = warp >> 2;                 // which half of the key-tile columns
@@ -230,28 +249,28 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
           *reinterpret_cast<uint4*>(dq_row + c) = make_uint4(0, 0, 0, 0);
       }
     } else {
-      // stage this thread's half of the Q row in TMEM (packed pairs, row = lane)
-      {
-        const T* q_row = reinterpret_cast<const T*>(p.q) + b * p.q_sb + (live ? row : 0) * p.q_sl + h * p.q_sh;
+      // stage this thread's half of the Q row in TMEM: packed pairs, row = lane
+      auto stage_row = [&](const T* src, int width, uint32_t col) {
         constexpr int kCols = HD / 4;           // packed columns per half
         constexpr int kStep = kCols < 32 ? kCols : 32;
 #pragma unroll
         for (int c0 = 0; c0 < kCols; c0 += kStep) {
-          uint32_t qv[kStep];
+          uint32_t w[kStep];
 #pragma unroll
           for (int c = 0; c < kStep; c += 4) {
             const int e = (hf * kCols + c0 + c) * 2;   // first element of this 16-byte chunk
             uint4 u = make_uint4(0, 0, 0, 0);
-            if (live && e < p.D) u = *reinterpret_cast<const uint4*>(q_row + e);
-            qv[c] = u.x; qv[c + 1] = u.y; qv[c + 2] = u.z; qv[c + 3] = u.w;
+            if (live && e < width) u = *reinterpret_cast<const uint4*>(src + e);
+            w[c] = u.x; w[c + 1] = u.y; w[c + 2] = u.z; w[c + 3] = u.w;
           }
-          if (kStep == 32) tmem_st_x32(tmem + lane_off + cQ + hf * kCols + c0, qv);
-          else tmem_st_x16(tmem + lane_off + cQ + hf * kCols + c0, qv);
+          if (kStep == 32) tmem_st_x32(tmem + lane_off + col + hf * kCols + c0, w);
+          else tmem_st_x16(tmem + lane_off + col + hf * kCols + c0, w);
         }
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive_warp(&s.q_ready);
-      }
+      };
+      stage_row(reinterpret_cast<const T*>(p.q) + b * p.q_sb + (live ? row : 0) * p.q_sl + h * p.q_sh, p.D, cQ);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive_warp(&s.q_ready);
       int lo = 0, hi = 0;
       float nlse2 = -INFINITY, ndelta = 0.f;
       if (live) {
@@ -261,43 +280,63 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
         ndelta = p.ndelta[((size_t)b * p.Hq + h) * p.LqPad + row];
       }
       const float c_log2 = p.scale * 1.4426950408889634f;
+      const float2 cc = make_float2(c_log2, c_log2), nl = make_float2(nlse2, nlse2);
+      const float2 nd = make_float2(ndelta, ndelta);
       bool ok = true;
       for (int i = 0; i < iters && ok; ++i) {
         const int col0 = (n_lo + i) * BN + hf * CH;
-        ok = mbar_wait(ctx, &s.sdp_full, i & 1, 50);
+        // ---- P = exp2(S c - lse2), masked ----
+        ok = mbar_wait(ctx, &s.s_full, i & 1, 50);
         if (!ok) break;
         tc_fence_after();
-        float sv[CH], dpv[CH];
+        float pv[CH];
 #pragma unroll
-        for (int c = 0; c < CH; c += 32) {
-          tmem_ld_x32(tmem + lane_off + cS + hf * CH + c, reinterpret_cast<uint32_t*>(sv) + c);
-          tmem_ld_x32(tmem + lane_off + cDP + hf * CH + c, reinterpret_cast<uint32_t*>(dpv) + c);
-        }
+        for (int c = 0; c < CH; c += 32) tmem_ld_x32(tmem + lane_off + cS + hf * CH + c, reinterpret_cast<uint32_t*>(pv) + c);
         tc_wait_ld();
         tc_fence_before();
-        mbar_arrive_warp(&s.sdp_free);
+        mbar_arrive_warp(&s.s_free);
         const bool tile_full = ((n_lo + i) * BN >= full_lo) && ((n_lo + i + 1) * BN <= full_hi);
         const int rl = lo - col0, rh = hi - col0;
-        uint32_t pk[CH / 2];
-        const float2 cc = make_float2(c_log2, c_log2), nl = make_float2(nlse2, nlse2);
-        const float2 nd = make_float2(ndelta, ndelta);
 #pragma unroll
         for (int c = 0; c < CH; c += 2) {
-          float2 pr = ex2_pair_sfu(fma2(make_float2(sv[c], sv[c + 1]), cc, nl));
+          // a share of the exponentials on the FMA pipe: the special-function unit bounds this loop
+          const float2 x = fma2(make_float2(pv[c], pv[c + 1]), cc, nl);
+          float2 pr = ((c >> 1) & 3) < kFmaPairs ? ex2_pair_fma(x) : ex2_pair_sfu(x);
           if (!tile_full) {
             pr.x = (c >= rl && c < rh) ? pr.x : 0.f;
             pr.y = (c + 1 >= rl && c + 1 < rh) ? pr.y : 0.f;
           }
-          const float2 ds = mul2(pr, add2(make_float2(dpv[c], dpv[c + 1]), nd));
-          pk[c >> 1] = Pack2<T>::pack(ds.x, ds.y);
+          pv[c] = pr.x; pv[c + 1] = pr.y;
         }
-        if (!kAlias && i > 0) {
-          ok = mbar_wait(ctx, &s.dq_done, (i - 1) & 1, 51);
-          if (!ok) break;
-          tc_fence_after();
+        // ---- dS = P (dP - delta) ----
+        ok = mbar_wait(ctx, &s.dp_full, i & 1, 51);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t pk[CH / 2];
+#pragma unroll
+        for (int c0 = 0; c0 < CH; c0 += 32) {
+          float dpv[32];
+          const uint32_t t_dp = tmem + lane_off + cDP + hf * CH + c0;
+          tmem_ld_x32(t_dp, reinterpret_cast<uint32_t*>(dpv));
+          tc_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            const float2 ds = mul2(make_float2(pv[c0 + c], pv[c0 + c + 1]), add2(make_float2(dpv[c], dpv[c + 1]), nd));
+            pk[(c0 + c) >> 1] = Pack2<T>::pack(ds.x, ds.y);
+          }
+          if (kDsOverDp) tmem_st_x16(t_dp, pk + (c0 >> 1));
         }
-        if (CH == 64) tmem_st_x32(tmem + lane_off + cDS + hf * kDsStride, pk);
-        else tmem_st_x16(tmem + lane_off + cDS + hf * kDsStride, pk);
+        if (!kDsOverDp) {
+          tc_fence_before();
+          mbar_arrive_warp(&s.dp_free);        // dP sits in registers: the next one may be issued
+          if (i > 0) {
+            ok = mbar_wait(ctx, &s.dq_done, (i - 1) & 1, 53);   // dQ has read the previous dS
+            if (!ok) break;
+            tc_fence_after();
+          }
+#pragma unroll
+          for (int c0 = 0; c0 < CH; c0 += 32) tmem_st_x16(tmem + lane_off + cDS + (hf * CH + c0) / 2, pk + (c0 >> 1));
+        }
         tc_wait_st();
         tc_fence_before();
         mbar_arrive_warp(&s.ds_full);
@@ -329,62 +368,54 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
       }
     }
   } else if (warp == 8 && lane == 0 && iters > 0) {
-    // ------------------------------ MMA issuer ------------------------------
+    // ------------------------------ S / dP issuer ------------------------------
     const uint32_t idesc_s = make_idesc(kBlockM, BN, kFormat, 0, 0);
-    const uint32_t idesc_dq = make_idesc(kBlockM, d_pad, kFormat, 0, 1);
-    auto issue_s_dp = [&](int i) {
-      const int stage = i & 1;
-      const uint32_t ka = smem_u32(s.k[i % kKStages]), va = smem_u32(s.v[stage]), da = smem_u32(s.d_o);
+    bool ok = mbar_wait(ctx, &s.q_ready, 0, 61);
+    if (ok) ok = mbar_wait(ctx, &s.do_full, 0, 60);
+    for (int i = 0; i < iters && ok; ++i) {
+      const int ks = i % kKStages, vs = i & 1;
+      ok = mbar_wait(ctx, &s.k_full[ks], (i / kKStages) & 1, 62);
+      if (ok && i > 0) ok = mbar_wait(ctx, &s.s_free, (i - 1) & 1, 66);     // S of the tile before sits in registers
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t ka = smem_u32(s.k[ks]), va = smem_u32(s.v[vs]), da = smem_u32(s.d_o);
       for (int js = 0; js < ksteps_qk; ++js) {
         umma_ts(tmem + cS, tmem + cQ + js * 8, make_smem_desc(ka + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024),
                 idesc_s, js > 0);
       }
+      umma_commit(&s.s_full);
+      ok = mbar_wait(ctx, &s.v_full[vs], (i >> 1) & 1, 63);
+      // dP of the tile before sits in registers, or (dS lying over it) its dS has been read
+      if (ok && i > 0) ok = mbar_wait(ctx, kDsOverDp ? &s.dq_done : &s.dp_free, (i - 1) & 1, 64);
+      if (!ok) break;
+      tc_fence_after();
       for (int js = 0; js < ksteps_v; ++js) {
-        umma_ss(tmem + cDP, make_smem_desc(da + (js >> 2) * kDoBox + (js & 3) * 32, 16, 1024),
-                make_smem_desc(va + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024), idesc_s, js > 0);
+        const uint64_t bv = make_smem_desc(va + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024);
+        umma_ss(tmem + cDP, make_smem_desc(da + (js >> 2) * kDoBox + (js & 3) * 32, 16, 1024), bv, idesc_s, js > 0);
       }
-      umma_commit(&s.sdp_full);
-      umma_commit(&s.v_empty[stage]);
-    };
-    auto issue_dq = [&](int i) {
-      const uint32_t ka = smem_u32(s.k[i % kKStages]);
+      umma_commit(&s.dp_full);
+      umma_commit(&s.v_empty[vs]);
+    }
+  } else if (warp == 10 && lane == 0 && iters > 0) {
+    // ------------------------------ dQ issuer ------------------------------
+    const uint32_t idesc_dq = make_idesc(kBlockM, d_pad, kFormat, 0, 1);
+    bool ok = true;
+    for (int i = 0; i < iters && ok; ++i) {
+      const int ks = i % kKStages;
+      ok = mbar_wait(ctx, &s.k_full[ks], (i / kKStages) & 1, 65);
+      if (ok) ok = mbar_wait(ctx, &s.ds_full, i & 1, 67);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t ka = smem_u32(s.k[ks]);
 #pragma unroll
       for (int js = 0; js < BN / 16; ++js) {
-        const uint32_t a_col = cDS + (js / (CH / 16)) * kDsStride + (js % (CH / 16)) * 8;
+        // k-step js (16 keys) of dS: 8 packed columns
+        const uint32_t a_col = kDsOverDp ? cDP + (js >> 1) * 32 + (js & 1) * 8 : cDS + js * 8;
         umma_ts(tmem + cDQ, tmem + a_col, make_smem_desc(ka + js * 2048, kKvBox, 1024), idesc_dq,
                 (i > 0 || js > 0) ? 1u : 0u);
       }
       umma_commit(&s.dq_done);
-      umma_commit(&s.k_empty[i % kKStages]);
-    };
-    bool ok = mbar_wait(ctx, &s.do_full, 0, 60);
-    if (ok) ok = mbar_wait(ctx, &s.q_ready, 0, 61);
-    if (ok) ok = mbar_wait(ctx, &s.k_full[0], 0, 62);
-    if (ok) ok = mbar_wait(ctx, &s.v_full[0], 0, 63);
-    if (ok) { tc_fence_after(); issue_s_dp(0); }
-    for (int i = 0; i < iters && ok; ++i) {
-      if (kAlias) {
-        // dS sits on top of S: dQ of this tile first, then S / dP of the next
-        ok = mbar_wait(ctx, &s.ds_full, i & 1, 67);
-        if (!ok) break;
-        tc_fence_after();
-        issue_dq(i);
-      }
-      if (i + 1 < iters) {
-        const int sn = (i + 1) & 1;
-        ok = mbar_wait(ctx, &s.k_full[(i + 1) % kKStages], ((i + 1) / kKStages) & 1, 64);
-        if (ok) ok = mbar_wait(ctx, &s.v_full[sn], ((i + 1) >> 1) & 1, 65);
-        if (ok && !kAlias) ok = mbar_wait(ctx, &s.sdp_free, i & 1, 66);
-        if (!ok) break;
-        tc_fence_after();
-        issue_s_dp(i + 1);
-      }
-      if (!kAlias) {
-        ok = mbar_wait(ctx, &s.ds_full, i & 1, 67);
-        if (!ok) break;
-        tc_fence_after();
-        issue_dq(i);
-      }
+      umma_commit(&s.k_empty[ks]);
     }
   } else if (warp == 9 && lane == 0 && iters > 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -444,7 +475,7 @@ struct DkvSmem {
   uint64_t q_full[kStages], q_empty[kStages];
   // per TMEM buffer: S^T / dP^T written by their products, P^T / dS^T written by the warpgroups,
   // and the two regions read by dV / dK and free for the next products
-  uint64_t s_full[2], dp_full[2], p_full[2], ds_full[2], s_free[2], dp_free[2];
+  uint64_t s_full[2], dp_full[2], p_full[2][2], ds_full[2], s_free[2], dp_free[2];   // p_full: per chunk
   uint64_t all_done;
   uint32_t tmem_base;
   int abort_flag;
@@ -541,7 +572,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     for (int i = 0; i < kStages; ++i) { mbar_init(&s.q_full[i], 1); mbar_init(&s.q_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.s_full[i], 1); mbar_init(&s.dp_full[i], 1);
-      mbar_init(&s.p_full[i], 8); mbar_init(&s.ds_full[i], 8);
+      mbar_init(&s.p_full[i][0], 8); mbar_init(&s.p_full[i][1], 8); mbar_init(&s.ds_full[i], 8);
       mbar_init(&s.s_free[i], 1); mbar_init(&s.dp_free[i], 1);
     }
     mbar_init(&s.all_done, 1);
@@ -678,7 +709,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       for (int j = 0; j < kPerLane; ++j) {
 #pragma unroll
         for (int c = j * kChunk; c < (j + 1) * kChunk; c += 2) {
-          const float2 e = ex2_pair_sfu(mul2(make_float2(pv[c], pv[c + 1]), cc));
+          // a share of the exponentials on the FMA pipe: the special-function unit bounds this loop
+          const float2 x = mul2(make_float2(pv[c], pv[c + 1]), cc);
+          const float2 e = ((c >> 1) & 3) < XB_DKV_FMA_PAIRS ? ex2_pair_fma(x) : ex2_pair_sfu(x);
           pv[c] = e.x; pv[c + 1] = e.y;
         }
         if (!tile_full) {
@@ -691,11 +724,12 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
           for (int c = 0; c < kChunk; c += 2) pp[c >> 1] = Pack2<T>::pack(pv[j * kChunk + c], pv[j * kChunk + c + 1]);
           if (kChunk == 32) tmem_st_x16(t_s + j * kChunk, pp); else tmem_st_x8(t_s + j * kChunk, pp);
+          tc_wait_st();
         }
+        // chunk by chunk, so that dV starts on the first while the second is still being computed
+        tc_fence_before();
+        mbar_arrive_warp(&s.p_full[sub][j]);  // also: this chunk of S^T has been read
       }
-      if (kWantDv) tc_wait_st();
-      tc_fence_before();
-      mbar_arrive_warp(&s.p_full[sub]);       // also: S^T has been read
       // ---- dS^T = P^T * (dP^T - delta), the subtraction already done by the product ----
       if (kWantDk) {
         ok = mbar_wait(ctx, &s.dp_full[sub], ph, 83);
@@ -801,6 +835,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // P^T / dS^T: each 32-column chunk (16 for SM = 32) of S^T / dP^T holds its packed results in
     // its own first half, so k-step js (16 query rows) sits at chunk js / kStepsPerChunk
     constexpr int kChunk = SM / 2 < 32 ? SM / 2 : 32, kStepsPerChunk = kChunk / 16;
+    constexpr int kChunksPerWg = SM / 2 / kChunk;
     const uint32_t idesc_dv = make_idesc(kBlockN, v_pad, kFormat, 0, 1);
     const uint32_t idesc_dk = make_idesc(kBlockN, d_pad, kFormat, 0, 1);
     bool ok = true;
@@ -809,18 +844,30 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const int buf = cnt % kBufs, st = cnt % kStages;
       const uint32_t ph = (cnt / kBufs) & 1;
       ok = mbar_wait(ctx, &s.q_full[st], (cnt / kStages) & 1, 94);
-      if (ok) ok = mbar_wait(ctx, &s.p_full[buf], ph, 92);
       if (!ok) break;
-      tc_fence_after();
       const uint32_t qa = smem_u32(s.q[st]), da = smem_u32(s.d_o[st]);
-      // P^T / dS^T of column half w sit in the first packed columns of that half
-      if (kWantDv) {
+      // chunk j of both warpgroups arrives together: its k-steps go first
+      bool fresh = cnt == 0;
 #pragma unroll
-        for (int js = 0; js < SM / 16; ++js) {
-          const uint32_t a_col = tmem + cS + buf * SM + (js / kStepsPerChunk) * kChunk + (js % kStepsPerChunk) * 8;
-          umma_ts(tmem + cDV, a_col, make_smem_desc(da + js * 2048, kQBox, 1024), idesc_dv, (cnt > 0 || js > 0) ? 1u : 0u);
+      for (int j = 0; j < kChunksPerWg; ++j) {
+        ok = mbar_wait(ctx, &s.p_full[buf][j], ph, 92);
+        if (!ok) break;
+        tc_fence_after();
+        if (kWantDv) {
+#pragma unroll
+          for (int w = 0; w < 2; ++w) {
+#pragma unroll
+            for (int i = 0; i < kStepsPerChunk; ++i) {
+              const int chunk = w * kChunksPerWg + j;
+              const int js = chunk * kStepsPerChunk + i;       // k-step: 16 query rows
+              const uint32_t a_col = tmem + cS + buf * SM + chunk * kChunk + i * 8;
+              umma_ts(tmem + cDV, a_col, make_smem_desc(da + js * 2048, kQBox, 1024), idesc_dv, fresh ? 0u : 1u);
+              fresh = false;
+            }
+          }
         }
       }
+      if (!ok) break;
       umma_commit(&s.s_free[buf]);
       if (kWantDk) {
         ok = mbar_wait(ctx, &s.ds_full[buf], ph, 96);

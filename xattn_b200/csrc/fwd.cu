@@ -228,9 +228,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           pk[c >> 1] = Pack2<T>::pack(p0, p1);
         }
         sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      } else if (kFmaPairs > 0 && tile_full) {
-        // every element is finite here: a share of the exponentials moves to the FMA pipe, since
-        // the special-function unit (16 results per clock and SM) is what bounds this loop
+      } else {
+        // A share of the exponentials runs on the FMA pipe: the special-function unit (16 results
+        // per clock and SM) is what bounds this loop.  Which elements take which route does not
+        // depend on the tile, so that a row gets the same bits however its neighbours are masked;
+        // the FMA route cannot return 0 for -inf, hence the extra selects on tiles that mask.
         const float2 cc = make_float2(c_log2, c_log2), nm = make_float2(neg_mc, neg_mc);
         float2 s2a = make_float2(0.f, 0.f), s2b = make_float2(0.f, 0.f);
 #pragma unroll
@@ -239,25 +241,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float2 x = fma2(make_float2(sc[c + 2 * e], sc[c + 2 * e + 1]), cc, nm);
-            pr[e] = (e < kFmaPairs) ? ex2_pair_fma(x) : ex2_pair_sfu(x);
+            if (e < kFmaPairs) {
+              pr[e] = ex2_pair_fma(x);
+              if (!tile_full) {
+                pr[e].x = sc[c + 2 * e] == -INFINITY ? 0.f : pr[e].x;
+                pr[e].y = sc[c + 2 * e + 1] == -INFINITY ? 0.f : pr[e].y;
+              }
+            } else {
+              pr[e] = ex2_pair_sfu(x);
+            }
             pk[(c >> 1) + e] = Pack2<T>::pack(pr[e].x, pr[e].y);
           }
           s2a = add2(s2a, add2(pr[0], pr[1]));
           s2b = add2(s2b, add2(pr[2], pr[3]));
-        }
-        const float2 s2 = add2(s2a, s2b);
-        sum = s2.x + s2.y;
-      } else {
-        const float2 cc = make_float2(c_log2, c_log2), nm = make_float2(neg_mc, neg_mc);
-        float2 s2a = make_float2(0.f, 0.f), s2b = make_float2(0.f, 0.f);
-#pragma unroll
-        for (int c = 0; c < 64; c += 4) {
-          const float2 pa = ex2_pair_sfu(fma2(make_float2(sc[c], sc[c + 1]), cc, nm));
-          const float2 pb = ex2_pair_sfu(fma2(make_float2(sc[c + 2], sc[c + 3]), cc, nm));
-          s2a = add2(s2a, pa);
-          s2b = add2(s2b, pb);
-          pk[c >> 1] = Pack2<T>::pack(pa.x, pa.y);
-          pk[(c >> 1) + 1] = Pack2<T>::pack(pb.x, pb.y);
         }
         const float2 s2 = add2(s2a, s2b);
         sum = s2.x + s2.y;

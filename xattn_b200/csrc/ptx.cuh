@@ -364,11 +364,11 @@ __device__ __forceinline__ float2 ex2_pair_sfu(float2 x) { return make_float2(ex
 
 // 2^x for a pair on the FMA pipe instead: x = j + f with j = round(x) and |f| <= 1/2, a cubic for
 // 2^f (relative error 7.5e-5, below the rounding step of a 16-bit P) and j added to the exponent
-// field.  Inputs below -126 give 2^-126.
+// field.  Inputs below -125 give 2^-125.
 __device__ __forceinline__ float2 ex2_pair_fma(float2 x) {
   const float kRound = 12582912.f;   // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
-  x.x = fmaxf(x.x, -126.f);
-  x.y = fmaxf(x.y, -126.f);
+  x.x = fmaxf(x.x, -125.f);
+  x.y = fmaxf(x.y, -125.f);
   const float2 t = add2(x, make_float2(kRound, kRound));
   const float2 j = add2(t, make_float2(-kRound, -kRound));
   const float2 f = fma2(j, make_float2(-1.f, -1.f), x);
