@@ -50,7 +50,7 @@ struct BwdParams {
 };
 
 // ---------------------------------------------------------------------------
-// preprocess: one warp per (batch, row, head)
+// preprocess
 // ---------------------------------------------------------------------------
 // The dK / dV kernel works on S^T and dP^T, where the per-query numbers lse and delta belong to
 // COLUMNS: every thread would need all of them for every step, and filling registers with them
@@ -76,6 +76,10 @@ __device__ __forceinline__ void write_row_terms(uint4* dst, float t, float d) {
   dst[1] = make_uint4(0u, 0u, 0u, 0u);
 }
 
+// A group of 8, 16 or 32 lanes (one 16-byte chunk of the row each) takes a (batch, row, head); a warp
+// works on kPrePasses * 32 / group consecutive ones with all their loads issued before the first use.
+constexpr int kPrePasses = 4;
+
 template <typename T>
 __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, const T* __restrict__ y,
                                                       const float* __restrict__ lse, int B, int Lq, int Hq, int V,
@@ -83,31 +87,43 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, 
                                                       int64_t y_sl, int64_t y_sh, int LqPad, float scale,
                                                       float* __restrict__ ndelta, float* __restrict__ nlse2,
                                                       uint4* __restrict__ row_terms) {
-  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int chunks = V >> 3;
+  const int group = chunks <= 8 ? 8 : (chunks <= 16 ? 16 : 32);
+  const int per_pass = 32 / group;
   const int lane = threadIdx.x & 31;
-  if (w >= (long long)B * LqPad * Hq) return;
-  const int h = (int)(w % Hq);
-  const long long bi = w / Hq;
-  const int i = (int)(bi % LqPad);
-  const int b = (int)(bi / LqPad);
-  if (i >= Lq) {
-    // padding up to whole tiles: rows that contribute nothing
-    if (lane == 0) {
-      const size_t idx = ((size_t)b * Hq + h) * LqPad + i;
-      ndelta[idx] = 0.f;
-      nlse2[idx] = -INFINITY;
-      write_row_terms(row_terms + 2 * idx, -INFINITY, 0.f);
-    }
-    return;
+  const int sub = lane / group, ch = lane % group;
+  const long long total = (long long)B * LqPad * Hq;
+  const long long first = (((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * (per_pass * kPrePasses) + sub;
+  // decode (batch, row, head) once with 64-bit divisions; the other passes are a few heads further on
+  int h0, i0, b0;
+  {
+    const long long f = first < total ? first : total - 1;
+    h0 = (int)(f % Hq);
+    const long long bi = f / Hq;
+    i0 = (int)(bi % LqPad);
+    b0 = (int)(bi / LqPad);
   }
-  const T* dyr = dy + b * dy_sb + i * dy_sl + h * dy_sh;
-  const T* yr = y + b * y_sb + i * y_sl + h * y_sh;
-  float acc = 0.f;
-  for (int c = lane * 8; c < V; c += 256) {
-    const uint4 a = *reinterpret_cast<const uint4*>(dyr + c);
-    const uint4 o = *reinterpret_cast<const uint4*>(yr + c);
-    const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
-    const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+  uint4 a[kPrePasses], o[kPrePasses];
+  int hh[kPrePasses], ii[kPrePasses], bb[kPrePasses];
+#pragma unroll
+  for (int ps = 0; ps < kPrePasses; ++ps) {
+    int h = h0 + ps * per_pass, i = i0, b = b0;
+    while (h >= Hq) { h -= Hq; ++i; }
+    while (i >= LqPad) { i -= LqPad; ++b; }
+    if (first >= total) b = B;                 // nothing left for this lane
+    hh[ps] = h; ii[ps] = i; bb[ps] = b;
+    a[ps] = make_uint4(0, 0, 0, 0);
+    o[ps] = make_uint4(0, 0, 0, 0);
+    if (b < B && i < Lq && ch < chunks) {
+      a[ps] = __ldg(reinterpret_cast<const uint4*>(dy + b * dy_sb + i * dy_sl + h * dy_sh + ch * 8));
+      o[ps] = __ldg(reinterpret_cast<const uint4*>(y + b * y_sb + i * y_sl + h * y_sh + ch * 8));
+    }
+  }
+#pragma unroll
+  for (int ps = 0; ps < kPrePasses; ++ps) {
+    const uint32_t aw[4] = {a[ps].x, a[ps].y, a[ps].z, a[ps].w};
+    const uint32_t ow[4] = {o[ps].x, o[ps].y, o[ps].z, o[ps].w};
+    float acc = 0.f;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const float2 fa = Pack2<T>::unpack(aw[k]);
@@ -115,15 +131,22 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, 
       acc = fmaf(fa.x, fo.x, acc);
       acc = fmaf(fa.y, fo.y, acc);
     }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) {
-    const size_t idx = ((size_t)b * Hq + h) * LqPad + i;
-    ndelta[idx] = -acc;
-    const float l = lse[((size_t)b * Hq + h) * Lq + i];
-    nlse2[idx] = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
-    write_row_terms(row_terms + 2 * idx, (l == -INFINITY) ? -INFINITY : -l / scale, -acc);
+    for (int off = group >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    const int h = hh[ps], i = ii[ps], b = bb[ps];
+    if (ch == 0 && b < B) {
+      const size_t idx = ((size_t)b * Hq + h) * LqPad + i;
+      if (i >= Lq) {
+        // padding up to whole tiles: rows that contribute nothing
+        ndelta[idx] = 0.f;
+        nlse2[idx] = -INFINITY;
+        write_row_terms(row_terms + 2 * idx, -INFINITY, 0.f);
+      } else {
+        const float l = lse[((size_t)b * Hq + h) * Lq + i];
+        ndelta[idx] = -acc;
+        nlse2[idx] = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
+        write_row_terms(row_terms + 2 * idx, (l == -INFINITY) ? -INFINITY : -l / scale, -acc);
+      }
+    }
   }
 }
 
@@ -971,7 +994,9 @@ static int launch_bwd(const XattnBwdArgs& a, BwdParams& p, cudaStream_t stream) 
   uint4* row_terms = reinterpret_cast<uint4*>(a.workspace + 2 * rows);
   p.ndelta = ndelta; p.nlse2 = nlse2; p.row_terms = row_terms;
   {
-    const long long warps = (long long)p.B * p.LqPad * p.Hq;
+    const int chunks = p.V >> 3;
+    const int per_warp = kPrePasses * 32 / (chunks <= 8 ? 8 : (chunks <= 16 ? 16 : 32));
+    const long long warps = ((long long)p.B * p.LqPad * p.Hq + per_warp - 1) / per_warp;
     const long long blocks = (warps * 32 + 255) / 256;
     ProfileScope prof(kProfBwdPre, stream);
     bwd_pre_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
