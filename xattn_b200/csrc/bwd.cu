@@ -161,8 +161,8 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, 
 // HD <= 128: key tiles of BN = 128.  TMEM: Q 0, dS 64 (packed), S 128, dP 256, dQ 384.
 // HD  = 256: BN = 64; no room for dS, which is written over dP.  TMEM: Q 0 (128 columns), S 128,
 //            dP 192, dQ 256.
-// S and dP are handed to the element-wise warpgroups separately, and the products have two issuing
-// threads (one stalls while its products run): S of the next key tile is issued as soon as this
+// S and dP are handed to the element-wise warpgroups separately, and the three products have an
+// issuing thread each: S of the next key tile is issued as soon as this
 // one's S sits in registers, dP likewise (HD = 256: once dQ has read the dS lying over it), and dQ
 // as soon as dS is in TMEM.
 template <int HD, int BN>
@@ -170,7 +170,10 @@ struct DqSmem {
   static constexpr int kDoBytes = kBlockM * HD * 2;
   static constexpr int kKvBytes = BN * HD * 2;
   // K is held from S of its key tile until dQ of the same tile, V only for dP
-  static constexpr int kKStages = HD <= 128 ? 3 : 2;
+#ifndef XB_DQ_KSTAGES
+#define XB_DQ_KSTAGES 3
+#endif
+  static constexpr int kKStages = HD <= 128 ? XB_DQ_KSTAGES : 2;
   alignas(1024) uint8_t d_o[kDoBytes];
   alignas(1024) uint8_t k[kKStages][kKvBytes];
   alignas(1024) uint8_t v[2][kKvBytes];
@@ -182,8 +185,8 @@ struct DqSmem {
 };
 
 // warps 0-3 / 4-7: element-wise warpgroups (thread = query row; first / second half of the key-tile columns)
-// warp 8: issuer of S and dP, warp 10: issuer of dQ (an issuing thread stalls while its products
-// run), warp 9: TMA producer + TMEM owner, warp 11: idle
+// warps 8, 11, 10: issuers of S, dP and dQ (an issuing thread stalls while its products run, so each
+// product has its own and none holds another back), warp 9: TMA producer + TMEM owner
 template <typename T, int HD, int BN>
 __global__ void __launch_bounds__(384, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_k,
@@ -324,12 +327,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
         for (int c = 0; c < CH; c += 2) {
           // a share of the exponentials on the FMA pipe: the special-function unit bounds this loop
           const float2 x = fma2(make_float2(pv[c], pv[c + 1]), cc, nl);
-          float2 pr = ((c >> 1) & 3) < kFmaPairs ? ex2_pair_fma(x) : ex2_pair_sfu(x);
-          if (!tile_full) {
-            pr.x = (c >= rl && c < rh) ? pr.x : 0.f;
-            pr.y = (c + 1 >= rl && c + 1 < rh) ? pr.y : 0.f;
-          }
+          const float2 pr = ((c >> 1) & 3) < kFmaPairs ? ex2_pair_fma(x) : ex2_pair_sfu(x);
           pv[c] = pr.x; pv[c + 1] = pr.y;
+        }
+        if (!tile_full) {
+#pragma unroll
+          for (int c = 0; c < CH; ++c) pv[c] = (c >= rl && c < rh) ? pv[c] : 0.f;
         }
         // ---- dS = P (dP - delta) ----
         ok = mbar_wait(ctx, &s.dp_full, i & 1, 51);
@@ -391,27 +394,34 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
       }
     }
   } else if (warp == 8 && lane == 0 && iters > 0) {
-    // ------------------------------ S / dP issuer ------------------------------
+    // ------------------------------ S issuer ------------------------------
     const uint32_t idesc_s = make_idesc(kBlockM, BN, kFormat, 0, 0);
     bool ok = mbar_wait(ctx, &s.q_ready, 0, 61);
-    if (ok) ok = mbar_wait(ctx, &s.do_full, 0, 60);
     for (int i = 0; i < iters && ok; ++i) {
-      const int ks = i % kKStages, vs = i & 1;
+      const int ks = i % kKStages;
       ok = mbar_wait(ctx, &s.k_full[ks], (i / kKStages) & 1, 62);
       if (ok && i > 0) ok = mbar_wait(ctx, &s.s_free, (i - 1) & 1, 66);     // S of the tile before sits in registers
       if (!ok) break;
       tc_fence_after();
-      const uint32_t ka = smem_u32(s.k[ks]), va = smem_u32(s.v[vs]), da = smem_u32(s.d_o);
+      const uint32_t ka = smem_u32(s.k[ks]);
       for (int js = 0; js < ksteps_qk; ++js) {
         umma_ts(tmem + cS, tmem + cQ + js * 8, make_smem_desc(ka + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024),
                 idesc_s, js > 0);
       }
       umma_commit(&s.s_full);
+    }
+  } else if (warp == 11 && lane == 0 && iters > 0) {
+    // ------------------------------ dP issuer ------------------------------
+    const uint32_t idesc_s = make_idesc(kBlockM, BN, kFormat, 0, 0);
+    bool ok = mbar_wait(ctx, &s.do_full, 0, 60);
+    for (int i = 0; i < iters && ok; ++i) {
+      const int vs = i & 1;
       ok = mbar_wait(ctx, &s.v_full[vs], (i >> 1) & 1, 63);
       // dP of the tile before sits in registers, or (dS lying over it) its dS has been read
       if (ok && i > 0) ok = mbar_wait(ctx, kDsOverDp ? &s.dq_done : &s.dp_free, (i - 1) & 1, 64);
       if (!ok) break;
       tc_fence_after();
+      const uint32_t va = smem_u32(s.v[vs]), da = smem_u32(s.d_o);
       for (int js = 0; js < ksteps_v; ++js) {
         const uint64_t bv = make_smem_desc(va + (js >> 2) * kKvBox + (js & 3) * 32, 16, 1024);
         umma_ss(tmem + cDP, make_smem_desc(da + (js >> 2) * kDoBox + (js & 3) * 32, 16, 1024), bv, idesc_s, js > 0);
@@ -554,7 +564,8 @@ struct DkvIter {
 
 // warps 0-3 / 4-7: element-wise warpgroups, thread = (key row, half of the sub-tile's query columns).
 // warp 8: issuer of S^T / dP^T, warp 10: issuer of dV / dK (an issuing thread stalls while its
-// products run, so the two kinds get a thread each), warp 9: TMA producer + TMEM owner, warp 11 idle.
+// products run, so the two kinds get a thread each; a third thread, splitting S^T from dP^T, was
+// measured slower), warp 9: TMA producer + TMEM owner, warp 11 idle.
 // With two S^T / dP^T buffers (SM <= 64) sub-tiles alternate between them.  With one (SM = 128, the
 // widest products: a tcgen05.mma costs about the same for 64 columns as for 128) the
 // S^T -> P^T -> dV and dP^T -> dS^T -> dK chains of a step overlap each other and the next step's S^T.
