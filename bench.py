@@ -11,7 +11,9 @@ Inputs are seeded synthetic N(0,1) tensors.  Rank 0 prints ONE JSON line.
 * ``value``     throughput with inputs resident in HBM (CUDA events, max over ranks), in TFLOP/s of
                 algorithmic work: 14 * D * (visible query-key pairs over query heads).
 * ``e2e``       the same through the public ops with HOST buffers: every step copies q, k, v, dy
-                from pinned memory and copies y, dq, dk, dv back, inside the timed region.
+                from pinned memory and copies y, dq, dk, dv back, inside the timed region.  Batch
+                rows are independent, so the step is pipelined over them (copies of the next and
+                of the previous row run beside the kernels of the current one).
 * ``roofline``  the dominant kernel's algorithmic FLOP/s from per-launch CUDA events, against the
                 measured dense bf16 peak of MEASURED_PEAKS.json.
 * ``cpu_baseline`` the CPU oracle timed on the host cores (rank 0, N=1 only), on the reference's own
@@ -254,15 +256,43 @@ def run_ours(args, w):
     out_host = None
     h2d = sum(t.numel() * t.element_size() for t in pinned[:4])
 
+    # Batch rows are independent, so the step is pipelined over them: row b + 1 comes in over PCIe
+    # and row b - 1 goes out while row b is computed (one copy stream per direction).
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    Bn = w["B"]
+    dev_in = [torch.empty_like(t, device=dev) for t in pinned[:4]]
+    ids_rows = None if ids is None else [ids[b:b + 1] for b in range(Bn)]
+
     def e2e_step():
         nonlocal out_host
-        dq_, dk_, dv_, ddy_ = (t.to(dev, non_blocking=True) for t in pinned[:4])
-        y_, lse_ = xattn.causal_flash_attn_fwd(dq_, dk_, dv_, **meta)
-        outs = (y_, *xattn.causal_flash_attn_bwd(ddy_, dq_, dk_, dv_, y_, lse_, **meta))
-        if out_host is None:
-            out_host = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
-        for dst, src in zip(out_host, outs):
-            dst.copy_(src, non_blocking=True)
+        main = torch.cuda.current_stream(dev)
+        s_in.wait_stream(main)
+        s_out.wait_stream(main)
+        arrived = []
+        with torch.cuda.stream(s_in):
+            for b in range(Bn):
+                for dst, src in zip(dev_in, pinned[:4]):
+                    dst[b:b + 1].copy_(src[b:b + 1], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(s_in)
+                arrived.append(ev)
+        for b in range(Bn):
+            main.wait_event(arrived[b])
+            q_, k_, v_, dy_ = (t[b:b + 1] for t in dev_in)
+            meta_b = {} if ids_rows is None else {"segment_idx": ids_rows[b]}
+            y_, lse_ = xattn.causal_flash_attn_fwd(q_, k_, v_, **meta_b)
+            outs = (y_, *xattn.causal_flash_attn_bwd(dy_, q_, k_, v_, y_, lse_, **meta_b))
+            if out_host is None:
+                out_host = [torch.empty((Bn,) + tuple(o.shape[1:]), dtype=o.dtype).pin_memory() for o in outs]
+            done = torch.cuda.Event()
+            done.record(main)
+            s_out.wait_event(done)
+            with torch.cuda.stream(s_out):
+                for dst, src in zip(out_host, outs):
+                    src.record_stream(s_out)
+                    dst[b:b + 1].copy_(src, non_blocking=True)
+        main.wait_stream(s_out)
+        main.wait_stream(s_in)
 
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 10))
