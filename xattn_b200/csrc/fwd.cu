@@ -56,7 +56,7 @@ struct FwdSmem {
   uint64_t q_full;
   uint64_t k_full[kKStages], k_empty[kKStages];
   uint64_t v_full[kVStages], v_empty[kVStages];
-  uint64_t s_full[2], s_free[2], p_full[2], max_x[2];
+  uint64_t s_full[2], s_free[2], p_full[2], p_free[2], max_x[2];
   uint64_t o_ready, pv_done, corr_full, final_full;
   uint32_t tmem_base;
   int abort_flag;
@@ -117,6 +117,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     for (int i = 0; i < kVStages; ++i) { mbar_init(&s.v_full[i], 1); mbar_init(&s.v_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.s_full[i], 1); mbar_init(&s.p_full[i], 8); mbar_init(&s.max_x[i], 8);
+      mbar_init(&s.p_free[i], 1);              // the P V product has read the P buffer
       // an S buffer is free again once the softmax holds it in registers, or, where P lies over S,
       // once the P V product has read it
       mbar_init(&s.s_free[i], kAliasP ? 1 : 8);
@@ -258,8 +259,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const float2 s2 = add2(s2a, s2b);
         sum = s2.x + s2.y;
       }
-      // 32 packed columns per half: next to each other in the P buffer, or (HD = 256) over the first
-      // 32 of the half's own S columns
+      // 32 packed columns per half: next to each other in the P buffer (once the product two tiles
+      // back has read it), or (HD = 256) over the first 32 of the half's own S columns
+      if (!kAliasP && j >= 2) {
+        ok = mbar_wait(ctx, &s.p_free[buf], ((j >> 1) - 1) & 1, 12);
+        if (!ok) break;
+        tc_fence_after();
+      }
       tmem_st_x32(kAliasP ? t_s : tmem + lane_off + cP + buf * 64 + hf * 32, pk);
       l = l * factor + sum;
       tc_wait_st();
@@ -388,6 +394,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
       umma_commit(&s.pv_done);
       umma_commit(&s.v_empty[vs]);
+      umma_commit(&s.p_free[n & 1]);
       if (kAliasP) umma_commit(&s.s_free[n & 1]);
     }
   } else if (warp == 13 && lane == 0 && iters > 0) {
