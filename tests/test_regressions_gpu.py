@@ -37,10 +37,11 @@ def test_large_batch_equals_chunked_batches(cuda_device):
 
 
 @pytest.mark.parametrize("operation", OPS)
-@pytest.mark.parametrize("length", (4096, 65536))
+@pytest.mark.parametrize("length", (4096, 65536, 102400))
 def test_long_sequences_on_sampled_rows(operation, length, cuda_device):
     """Sampled query rows against all keys; the gradient of those rows alone (sparse dO) is checked on
-    the full-sized dq, dk, dv."""
+    the full-sized dq, dk, dv.  At 102400 a key tile is seen by 800 query tiles, more than the dK / dV
+    kernel keeps tile bits for in shared memory (768): the last sampled rows go through its fallback."""
     dev = cuda_device
     dtype = torch.bfloat16
     span = 255
