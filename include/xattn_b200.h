@@ -196,6 +196,10 @@ int xattn_b200_bwd_static_scratch(const XattnBwdArgs* args, xattn_stream_t strea
  *   backward:  read            = y + sigmoid(g) * neg_read               (recovered query read)
  *              dneg_read[rows][Hkv][V] = - sum over the group of sigmoid(g) * dy
  *              dg[rows][H]     = - sigmoid'(g) * <dy, neg_read>
+ * With value_groups = C > 1 (the reference's internal value-group layout,
+ * xattn/ops/softdelta_attention.py `_SoftDeltaFunc`, v [B, L, Hkv, C, Dg], g [B, Lq, H, C, 1]) there is
+ * one gate per group of v_dim / C consecutive channels: g and dg are [rows][H][C] and each group's
+ * dg takes its own share of <dy, neg_read>.
  * ---------------------------------------------------------------------- */
 typedef struct {
   int dtype;
@@ -208,6 +212,7 @@ typedef struct {
   const void* dy;                /* backward only                              */
   void* dneg_read;               /* backward only, dtype                       */
   void* dg;                      /* backward only, dtype                       */
+  int64_t value_groups;          /* 0 or 1: one gate per head; C > 1 must divide v_dim */
 } XattnGateArgs;
 
 int xattn_b200_softdelta_gate_fwd(const XattnGateArgs* args, xattn_stream_t stream);

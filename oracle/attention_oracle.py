@@ -172,7 +172,13 @@ def softdelta(
     span: Optional[int] = None,
     reset_position_per_segment: bool = False,
 ):
-    """SoftDelta, tests/softdelta/reference.py:9-71 (scalar gates).  Returns (y, read, neg_read)."""
+    """SoftDelta, tests/softdelta/reference.py:9-71.  Scalar gates (``v`` [B, L, Hkv, V], ``g`` [B, Lq, H])
+    or value groups (``v`` [B, L, Hkv, C, Dg], ``g`` [B, Lq, H, C, 1]: one gate per group of Dg channels,
+    :36-71); the outputs follow the input layout.  Returns (y, read, neg_read)."""
+    scalar = v.dim() == 4
+    if scalar:
+        v, g = v.unsqueeze(3), g[..., None, None]
+        prev_v = None if prev_v is None else prev_v.unsqueeze(3)
     batch, length, q_heads, _ = q.shape
     if k_read is None:
         k_read = k[:, k.shape[1] - length:]
@@ -180,15 +186,23 @@ def softdelta(
         k = torch.cat((prev_k, k), dim=1)
         v = torch.cat((prev_v, v), dim=1)
     kv_heads = k.shape[2]
+    groups, group_dim = v.shape[3:]
     s = q.shape[-1] ** -0.5 if scale is None else float(scale)
     inc, strict = allowed_masks(length, k.shape[1], batch, visibility, span,
                                 q_segment_idx, k_segment_idx, reset_position_per_segment)
-    read = attention_from_mask(q, k, v, inc, s)
-    neg = attention_from_mask(k_read, k, v, strict, s)
+    flat_v = v.flatten(3)
+    read = attention_from_mask(q, k, flat_v, inc, s)
+    neg = attention_from_mask(k_read, k, flat_v, strict, s)
     rep = q_heads // kv_heads
-    gate = torch.sigmoid(g).reshape(batch, length, kv_heads, rep, 1)
-    y = read.reshape(batch, length, kv_heads, rep, -1) - gate * neg[:, :, :, None, :]
-    return y.reshape(batch, length, q_heads, -1), read, neg
+    read = read.reshape(batch, length, kv_heads, rep, groups, group_dim)
+    neg = neg.reshape(batch, length, kv_heads, 1, groups, group_dim)
+    gate = torch.sigmoid(g).reshape(batch, length, kv_heads, rep, groups, 1)
+    y = (read - gate * neg).reshape(batch, length, q_heads, groups, group_dim)
+    read = read.reshape(batch, length, q_heads, groups, group_dim)
+    neg = neg.reshape(batch, length, kv_heads, groups, group_dim)
+    if scalar:
+        y, read, neg = y.flatten(3), read.flatten(3), neg.flatten(3)
+    return y, read, neg
 
 
 def row_intervals(

@@ -8,9 +8,10 @@ import torch
 
 
 def _case(name, B, Lq, Lk, Hq, Hkv, D, V, vis="full", span=None, seg=None, reset=False, strict=False,
-          q_ids="suffix", softdelta=False):
+          q_ids="suffix", softdelta=False, groups=None):
+    """``groups``: SoftDelta value groups (v seen as [.., groups, V / groups], one gate per group)."""
     return dict(name=name, B=B, Lq=Lq, Lk=Lk, Hq=Hq, Hkv=Hkv, D=D, V=V, vis=vis, span=span, seg=seg,
-                reset=reset, strict=strict, q_ids=q_ids, softdelta=softdelta)
+                reset=reset, strict=strict, q_ids=q_ids, softdelta=softdelta, groups=groups)
 
 
 GOLDEN_CASES = (
@@ -33,6 +34,8 @@ GOLDEN_CASES = (
     _case("reset-long-q-run", 1, 9, 23, 2, 1, 8, 8, vis="chunk", span=3, seg=8, reset=True, q_ids="long_run"),
     _case("unmatched", 1, 6, 14, 2, 1, 8, 8, seg=5, q_ids="unmatched"),
     _case("future-only", 1, 4, 9, 2, 1, 8, 8, seg=5, q_ids="future"),
+    _case("groups-causal", 2, 18, 18, 4, 2, 8, 12, softdelta=True, groups=3),
+    _case("groups-segment-window", 1, 20, 20, 2, 1, 8, 16, vis="window", span=4, seg=6, softdelta=True, groups=2),
 )
 
 
@@ -45,7 +48,8 @@ def golden_inputs(case):
         "k": torch.from_numpy(rs.standard_normal((B, Lk, Hkv, D))),
         "v": torch.from_numpy(rs.standard_normal((B, Lk, Hkv, V))),
         "dy": torch.from_numpy(rs.standard_normal((B, Lq, Hq, V))),
-        "g": torch.from_numpy(rs.standard_normal((B, Lq, Hq))),
+        "g": torch.from_numpy(rs.standard_normal((B, Lq, Hq) if not case.get("groups") else
+                                                 (B, Lq, Hq, case["groups"], 1))),
         "q_ids": None,
         "k_ids": None,
     }

@@ -47,10 +47,15 @@ def main() -> None:
         if case.get("softdelta"):
             g = t["g"].clone().requires_grad_()
             q2, k2, v2 = (t[n].clone().requires_grad_() for n in ("q", "k", "v"))
+            dy2 = dy
+            if case.get("groups"):       # the reference's internal value-group layout
+                shape = (case["groups"], case["V"] // case["groups"])
+                v2 = t["v"].unflatten(3, shape).clone().requires_grad_()
+                dy2 = dy.unflatten(3, shape)
             ys = softdelta_fp64_oracle(q2, k2, v2, g, None, scale=scale, q_segment_idx=t["q_ids"],
                                        k_segment_idx=t["k_ids"], visibility=case["vis"], span=case["span"],
                                        reset_position_per_segment=case["reset"])
-            grads = torch.autograd.grad(ys, (q2, k2, v2, g), dy)
+            grads = torch.autograd.grad(ys, (q2, k2, v2, g), dy2)
             out[name + "/sd_y"] = ys.detach().numpy()
             for key, val in zip(("sd_dq", "sd_dk", "sd_dv", "sd_dg"), grads):
                 out[f"{name}/{key}"] = val.numpy()

@@ -35,10 +35,15 @@ def test_oracle_matches_reference_golden(case):
         np.testing.assert_allclose(val.detach().numpy(), GOLDEN[f"{name}/{key}"], rtol=1e-12, atol=1e-13)
     if case["softdelta"]:
         q, k, v, g = (t[x].clone().requires_grad_() for x in ("q", "k", "v", "g"))
+        dy = t["dy"]
+        if case.get("groups"):
+            shape = (case["groups"], case["V"] // case["groups"])
+            v = t["v"].unflatten(3, shape).clone().requires_grad_()
+            dy = dy.unflatten(3, shape)
         ys, _, _ = O.softdelta(q, k, v, g, None, scale=case["D"] ** -0.5, q_segment_idx=t["q_ids"],
                                k_segment_idx=t["k_ids"], visibility=case["vis"], span=case["span"],
                                reset_position_per_segment=case["reset"])
-        gs = torch.autograd.grad(ys, (q, k, v, g), t["dy"])
+        gs = torch.autograd.grad(ys, (q, k, v, g), dy)
         for val, key in zip((ys, *gs), ("sd_y", "sd_dq", "sd_dk", "sd_dv", "sd_dg")):
             np.testing.assert_allclose(val.detach().numpy(), GOLDEN[f"{name}/{key}"], rtol=1e-12, atol=1e-13)
 

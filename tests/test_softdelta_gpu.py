@@ -186,3 +186,63 @@ def test_k_read_none_folds_into_dk(cuda_device):
     assert out[4] is None
     out2 = xattn.sliding_chunk_softdelta_attention_bwd(dy, t["q"], t["k"], None, t["v"], t["g"], y, neg_read, lse, 4096)
     assert len(out2) == 7 and out2[5] is None and out2[6] is None
+
+
+# ---- value groups (the reference's internal layout: tests/softdelta/test_value_groups.py) --------
+# (D, groups, group_dim): group widths of 64 channels and one that is not a multiple of 8
+GROUP_DIMS = {"d128c2": (128, 2, 64), "d192c3": (192, 3, 64), "d64c4-composed": (64, 4, 12)}
+GROUP_SUPPORTS = {"causal": ("full", None), "window40": ("window", 40), "chunk32": ("chunk", 32)}
+
+
+@pytest.mark.parametrize("dims", list(GROUP_DIMS))
+@pytest.mark.parametrize("support", list(GROUP_SUPPORTS))
+@pytest.mark.parametrize("heads", ((8, 2), (16, 1)), ids=("h8kv2", "h16kv1"))
+@pytest.mark.parametrize("segments", (False, True), ids=("dense", "segments"))
+@pytest.mark.parametrize("with_k_read", (False, True), ids=("neg-key", "neg-given"))
+@pytest.mark.parametrize("dtype", (torch.float16, torch.bfloat16), ids=("fp16", "bf16"))
+@pytest.mark.parametrize("level", (0, 1))
+def test_value_groups_match_oracle(dims, support, heads, segments, with_k_read, dtype, level, cuda_device):
+    """v [B, L, Hkv, C, Dg] with a gate per group of Dg channels (g [B, L, H, C, 1]), driven through the
+    internal autograd function as the reference's own test does."""
+    from xattn_b200.ops.softdelta_attention import _softdelta_value_groups
+    dev = cuda_device
+    qk_dim, groups, group_dim = GROUP_DIMS[dims]
+    visibility, span = GROUP_SUPPORTS[support]
+    batch, length = 2, 150
+    gen = torch.Generator(device="cpu").manual_seed(20261025)
+    r = lambda *s: torch.randn(s, generator=gen).to(device=dev, dtype=dtype)
+    t = dict(
+        q=F.normalize(r(batch, length, heads[0], qk_dim), dim=-1),
+        k=F.normalize(r(batch, length, heads[1], qk_dim), dim=-1),
+        v=F.silu(r(batch, length, heads[1], groups, group_dim)) + 0.1,
+        g=r(batch, length, heads[0], groups, 1) * 0.75,
+    )
+    if with_k_read:
+        t["k_read"] = F.normalize(F.silu(r(batch, length, heads[1], qk_dim)), dim=-1)
+    ids = run_lengths(batch, length, (1, 2, 40, 3, 64, 7), dev) if segments else None
+    leaves = {n: x.detach().clone().requires_grad_() for n, x in t.items()}
+    y = _softdelta_value_groups(leaves["q"], leaves["k"], leaves["v"], leaves["g"], leaves.get("k_read"),
+                                q_segment_idx=ids, k_segment_idx=ids, visibility=visibility, span=span,
+                                high_precision_level=level)
+    ref = {n: x.detach().double().cpu().requires_grad_() for n, x in t.items()}
+    ids_cpu = None if ids is None else ids.cpu()
+    expected, read, neg = O.softdelta(ref["q"], ref["k"], ref["v"], ref["g"], ref.get("k_read"),
+                                      q_segment_idx=ids_cpu, k_segment_idx=ids_cpu, visibility=visibility, span=span)
+    assert y.shape == expected.shape == (batch, length, heads[0], groups, group_dim)
+    assert y.dtype == dtype and torch.isfinite(y).all()
+    rep = heads[0] // heads[1]
+    gate = torch.sigmoid(ref["g"].detach())
+    a, r_ = O.ATOL[dtype], O.RTOL[dtype]
+    bound = (a + r_ * read.abs() + gate * (a + r_ * neg.repeat_interleave(rep, 2).abs()) + a + r_ * expected.abs()).detach()
+    err = (y.detach().double().cpu() - expected.detach()).abs()
+    assert bool((err <= bound).all()), f"composed error ratio {(err / bound).max().item()}"
+    dy = (torch.randn(y.shape, generator=gen) / y.numel() ** 0.5).to(device=dev, dtype=dtype)
+    grads = torch.autograd.grad(y, list(leaves.values()), dy)
+    expected_grads = torch.autograd.grad(expected, list(ref.values()), dy.double().cpu())
+    for name, g_, e in zip(leaves, grads, expected_grads):
+        assert g_.dtype == dtype and g_.shape == e.shape, name
+        torch.testing.assert_close(g_.cpu(), e.to(dtype), rtol=O.RTOL[dtype], atol=O.GRAD_ATOL[dtype],
+                                   msg=lambda m: f"{name}: {m}")
+        floor = O.GRAD_ATOL[dtype] * e.numel() ** 0.5
+        rel = ((g_.double().cpu() - e).norm() / e.norm().clamp_min(floor)).item()
+        assert rel < GRAD_REL_NORM[dtype], f"{name}: relative norm error {rel}"

@@ -76,6 +76,7 @@ class GateArgs(C.Structure):
         ("rows", C.c_int64), ("q_heads", C.c_int64), ("kv_heads", C.c_int64), ("v_dim", C.c_int64),
         ("g", C.c_void_p), ("neg_read", C.c_void_p), ("read", C.c_void_p), ("y", C.c_void_p),
         ("dy", C.c_void_p), ("dneg_read", C.c_void_p), ("dg", C.c_void_p),
+        ("value_groups", C.c_int64),
     ]
 
 

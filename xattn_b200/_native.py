@@ -286,11 +286,13 @@ def zero_constant_key_rows(dq: Tensor, k_all: Tensor, plan: Tensor) -> Tensor:
 
 
 def _gate_args(g: Tensor, neg_read: Tensor, q_heads: int) -> "_lib.GateArgs":
+    """``g`` is [B, L, H] (one gate per head) or [B, L, H, C] (one per group of V / C channels)."""
     args = _lib.GateArgs()
     args.dtype = _DTYPES[g.dtype]
     args.neg_is_f32 = int(neg_read.dtype == torch.float32)
     B, L, Hkv, V = neg_read.shape
     args.rows, args.q_heads, args.kv_heads, args.v_dim = B * L, q_heads, Hkv, V
+    args.value_groups = g.shape[3] if g.dim() == 4 else 1
     args.g, args.neg_read = g.data_ptr(), neg_read.data_ptr()
     return args
 

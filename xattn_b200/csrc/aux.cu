@@ -41,11 +41,12 @@ template <typename T> __device__ __forceinline__ T from_f32(float x);
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32(float x) { return __float2bfloat16(x); }
 template <> __device__ __forceinline__ __half from_f32(float x) { return __float2half(x); }
 
-// rows = B * L; read / y: [rows][H][V], neg: [rows][Hkv][V], g: [rows][H]
+// rows = B * L; read / y: [rows][H][V], neg: [rows][Hkv][V], g: [rows][H][C] with one gate per
+// group of Dg = V / C consecutive channels (C = 1: one gate per head)
 template <typename T, bool NEG_F32>
 __global__ void __launch_bounds__(256) gate_fwd_kernel(const T* __restrict__ read, const void* __restrict__ neg_,
                                                        const T* __restrict__ g, T* __restrict__ y, long long rows,
-                                                       int H, int Hkv, int V) {
+                                                       int H, int Hkv, int V, int C, int Dg) {
   const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (w >= rows * Hkv) return;
@@ -58,11 +59,17 @@ __global__ void __launch_bounds__(256) gate_fwd_kernel(const T* __restrict__ rea
     else load8<T>(reinterpret_cast<const T*>(neg_) + (row * Hkv + kv) * V + c, n);
     for (int r = 0; r < G; ++r) {
       const int h = kv * G + r;
-      const float gate = sigmoid_f32(to_f32<T>(g[row * H + h]));
+      const T* gh = g + (row * H + h) * C;
       float x[8];
       load8<T>(read + (row * H + h) * V + c, x);
+      if (C == 1) {
+        const float gate = sigmoid_f32(to_f32<T>(gh[0]));
 #pragma unroll
-      for (int e = 0; e < 8; ++e) x[e] = x[e] - gate * n[e];
+        for (int e = 0; e < 8; ++e) x[e] = x[e] - gate * n[e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = x[e] - sigmoid_f32(to_f32<T>(gh[(c + e) / Dg])) * n[e];
+      }
       store8<T>(y + (row * H + h) * V + c, x);
     }
   }
@@ -72,7 +79,7 @@ template <typename T, bool NEG_F32>
 __global__ void __launch_bounds__(256) gate_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ y,
                                                        const void* __restrict__ neg_, const T* __restrict__ g,
                                                        T* __restrict__ read, T* __restrict__ dneg, T* __restrict__ dg,
-                                                       long long rows, int H, int Hkv, int V) {
+                                                       long long rows, int H, int Hkv, int V, int C, int Dg) {
   const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (w >= rows * Hkv) return;
@@ -91,24 +98,53 @@ __global__ void __launch_bounds__(256) gate_bwd_kernel(const T* __restrict__ dy,
   }
   for (int r = 0; r < G; ++r) {
     const int h = kv * G + r;
-    const float gate = sigmoid_f32(to_f32<T>(g[row * H + h]));
-    float d[8], yy[8], dot = 0.f;
+    const T* gh = g + (row * H + h) * C;
+    float d[8], yy[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) { d[e] = 0.f; yy[e] = 0.f; }
     if (act) {
       load8<T>(dy + (row * H + h) * V + c, d);
       load8<T>(y + (row * H + h) * V + c, yy);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        dn[e] -= gate * d[e];
-        dot += d[e] * n[e];
-        yy[e] += gate * n[e];
-      }
-      store8<T>(read + (row * H + h) * V + c, yy);
     }
+    if (C == 1) {
+      const float gate = sigmoid_f32(to_f32<T>(gh[0]));
+      float dot = 0.f;
+      if (act) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    if (lane == 0) dg[row * H + h] = from_f32<T>(-dot * gate * (1.f - gate));
+        for (int e = 0; e < 8; ++e) {
+          dn[e] -= gate * d[e];
+          dot += d[e] * n[e];
+          yy[e] += gate * n[e];
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      if (lane == 0) dg[row * H + h] = from_f32<T>(-dot * gate * (1.f - gate));
+    } else {
+      if (act) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float gate = sigmoid_f32(to_f32<T>(gh[(c + e) / Dg]));
+          dn[e] -= gate * d[e];
+          yy[e] += gate * n[e];
+        }
+      }
+      // one gate gradient per value group: the group's share of <dy, neg_read>
+      for (int j = 0; j < C; ++j) {
+        float dot = 0.f;
+        if (act) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) dot += ((c + e) / Dg == j) ? d[e] * n[e] : 0.f;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (lane == 0) {
+          const float gate = sigmoid_f32(to_f32<T>(gh[j]));
+          dg[(row * H + h) * C + j] = from_f32<T>(-dot * gate * (1.f - gate));
+        }
+      }
+    }
+    if (act) store8<T>(read + (row * H + h) * V + c, yy);
   }
   if (act) store8<T>(dneg + (row * Hkv + kv) * V + c, dn);
 }
@@ -187,26 +223,31 @@ static int check_gate(const XattnGateArgs* a) {
     set_error("bad gate sizes"); return XATTN_E_INVALID;
   }
   if (!a->y || !a->neg_read || !a->g) { set_error("null tensor pointer"); return XATTN_E_INVALID; }
+  if (a->value_groups < 0 || (a->value_groups > 1 && a->v_dim % a->value_groups)) {
+    set_error("value_groups must divide v_dim"); return XATTN_E_INVALID;
+  }
   return XATTN_OK;
 }
 
 template <typename T>
 static void launch_gate_fwd(const XattnGateArgs* a, cudaStream_t s) {
+  const int groups = a->value_groups > 1 ? (int)a->value_groups : 1;
   const long long warps = a->rows * a->kv_heads;
   const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
   if (a->neg_is_f32)
-    gate_fwd_kernel<T, true><<<blocks, 256, 0, s>>>((const T*)a->read, a->neg_read, (const T*)a->g, (T*)a->y, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim);
+    gate_fwd_kernel<T, true><<<blocks, 256, 0, s>>>((const T*)a->read, a->neg_read, (const T*)a->g, (T*)a->y, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim, groups, (int)a->v_dim / groups);
   else
-    gate_fwd_kernel<T, false><<<blocks, 256, 0, s>>>((const T*)a->read, a->neg_read, (const T*)a->g, (T*)a->y, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim);
+    gate_fwd_kernel<T, false><<<blocks, 256, 0, s>>>((const T*)a->read, a->neg_read, (const T*)a->g, (T*)a->y, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim, groups, (int)a->v_dim / groups);
 }
 template <typename T>
 static void launch_gate_bwd(const XattnGateArgs* a, cudaStream_t s) {
+  const int groups = a->value_groups > 1 ? (int)a->value_groups : 1;
   const long long warps = a->rows * a->kv_heads;
   const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
   if (a->neg_is_f32)
-    gate_bwd_kernel<T, true><<<blocks, 256, 0, s>>>((const T*)a->dy, (const T*)a->y, a->neg_read, (const T*)a->g, (T*)a->read, (T*)a->dneg_read, (T*)a->dg, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim);
+    gate_bwd_kernel<T, true><<<blocks, 256, 0, s>>>((const T*)a->dy, (const T*)a->y, a->neg_read, (const T*)a->g, (T*)a->read, (T*)a->dneg_read, (T*)a->dg, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim, groups, (int)a->v_dim / groups);
   else
-    gate_bwd_kernel<T, false><<<blocks, 256, 0, s>>>((const T*)a->dy, (const T*)a->y, a->neg_read, (const T*)a->g, (T*)a->read, (T*)a->dneg_read, (T*)a->dg, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim);
+    gate_bwd_kernel<T, false><<<blocks, 256, 0, s>>>((const T*)a->dy, (const T*)a->y, a->neg_read, (const T*)a->g, (T*)a->read, (T*)a->dneg_read, (T*)a->dg, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim, groups, (int)a->v_dim / groups);
 }
 
 int gate_fwd_entry(const XattnGateArgs* a, cudaStream_t s) {

@@ -238,20 +238,54 @@ def _torch_plan(q, k, v, g, k_read, prev_k, prev_v, q_ids, k_ids, scale, support
 
 
 class _SoftDeltaFunction(torch.autograd.Function):
+    """Scalar gates (the public layout: ``v`` [B, L, Hkv, V], ``g`` [B, Lq, H]) or the reference's internal
+    value groups (``v`` [B, L, Hkv, C, Dg], ``g`` [B, Lq, H, C, 1], one gate per group of ``Dg`` channels:
+    xattn/ops/softdelta_attention.py ``_SoftDeltaFunc``, tests/softdelta/test_value_groups.py:1-7).  Both
+    reads are linear in V, so the grouped form runs them on the flattened values and differs only in the
+    gate kernel; outputs and gradients follow the input layout."""
+
     @staticmethod
     def forward(ctx, q, k, v, g, k_read, prev_k, prev_v, q_ids, k_ids, scale, level, support):
+        groups = None
+        if v.dim() == 5:
+            groups = tuple(v.shape[3:])
+            if g.shape != (*q.shape[:3], groups[0], 1):
+                raise ValueError("grouped SoftDelta expects g of shape [B, Lq, H, C, 1]")
+            v = v.flatten(3)
+            prev_v = None if prev_v is None else prev_v.flatten(3)
+            g = g.squeeze(-1)
         y, neg_read, lse = _forward(q, k, v, g, k_read, prev_k, prev_v, q_ids, k_ids, scale, level, support)
         ctx.save_for_backward(q, k, v, g, k_read, prev_k, prev_v, q_ids, k_ids, y, neg_read, lse)
-        ctx.scale, ctx.level, ctx.support = scale, level, support
-        return y
+        ctx.scale, ctx.level, ctx.support, ctx.groups = scale, level, support, groups
+        return y if groups is None else y.unflatten(3, groups)
 
     @staticmethod
     def backward(ctx, dy):
         q, k, v, g, k_read, prev_k, prev_v, q_ids, k_ids, y, neg_read, lse = ctx.saved_tensors
+        groups = ctx.groups
+        if groups is not None:
+            dy = dy.flatten(3)
         dq, dk, dv, dg, dk_read, dpk, dpv = _backward(
             dy, q, k, v, g, k_read, prev_k, prev_v, q_ids, k_ids, y, neg_read, lse,
             ctx.scale, ctx.level, ctx.support)
+        if groups is not None:
+            dv = dv.unflatten(3, groups)
+            dg = dg.unsqueeze(-1)
+            dpv = None if dpv is None else dpv.unflatten(3, groups)
         return dq, dk, dv, dg, dk_read, dpk, dpv, None, None, None, None, None
+
+
+def _softdelta_value_groups(q, k, v, g, k_read=None, *, scale=None, q_segment_idx=None, k_segment_idx=None,
+                            visibility="full", span=None, high_precision_level=0):
+    """Internal entry for the value-group layout (no public API takes it yet, as in the reference):
+    ``v`` [B, L, Hkv, C, Dg], ``g`` [B, Lq, H, C, 1]; ``visibility`` full / window / chunk with ``span``."""
+    if v.dim() != 5 or g.dim() != 5:
+        raise ValueError("value-group SoftDelta expects 5D v and g")
+    support = _core.Support(visibility, span, False, False)
+    resolved = q.shape[-1] ** -0.5 if scale is None else float(scale)
+    return _SoftDeltaFunction.apply(q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(),
+                                    None if k_read is None else k_read.contiguous(), None, None,
+                                    q_segment_idx, k_segment_idx, resolved, int(high_precision_level), support)
 
 
 # ---- shared call paths --------------------------------------------------------------------------
