@@ -260,6 +260,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
 
   // 384 threads start with 168 registers each; the element-wise warpgroups take most of the other
   // warps' share
+  // registers move between warps of this CTA only: the gain must not exceed what the others give up
+  static_assert(256 * (216 - 168) <= 128 * (168 - 72), "register budget");
   if (warp < 8) setmaxnreg_inc<216>(); else setmaxnreg_dec<72>();
   if (dead) {
   } else if (warp < 8) {
@@ -651,6 +653,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   it0.init(G, kti.m_first, kti.m_end, p.Lq, n * kBlockN, qt_info, s.overlap_bits, cache_n);
   const bool any_work = it0.valid();
 
+  // registers move between warps of this CTA only: the gain must not exceed what the others give up
+  static_assert(256 * (216 - 168) <= 128 * (168 - 72), "register budget");
   if (warp < 8) setmaxnreg_inc<216>(); else setmaxnreg_dec<72>();
   if (dead) {
   } else if (warp < 8) {

@@ -1,9 +1,9 @@
 // Forward attention for sm_100a.
 //
 // One CTA owns one tile of 128 query rows of one (batch, query head) and walks the key tiles its
-// visible-key intervals touch.  Roles (16 warps):
-//   warps 0-3 / 4-7   softmax warpgroups: thread = (query row, half of the key tile's 128 columns);
-//                     the two halves exchange their row maxima through shared memory
+// visible-key intervals touch.  Roles (XB_FWD_PARTS = 2: 16 warps):
+//   warps 0-7         two softmax warpgroups: thread = (query row, half of the key tile's 128
+//                     columns); the parts exchange their row maxima through shared memory
 //   warps 8-11        correction + epilogue warpgroup (rescales O in TMEM, writes y and lse)
 //   warp 12           tcgen05.mma issuer of O += P V (one thread)
 //   warp 13           TMA producer (one thread); also owns the TMEM allocation
@@ -23,6 +23,12 @@
 
 #ifndef XB_FWD_FMA_PAIRS
 #define XB_FWD_FMA_PAIRS 1
+#endif
+// softmax warpgroups per CTA: each takes 128 / XB_FWD_PARTS columns of a key tile.  2 or 4; four
+// (24 warps, 32 columns per thread) measured 10 % slower than two: the per-tile synchronisation of a
+// softmax warp costs as much as its arithmetic then.
+#ifndef XB_FWD_PARTS
+#define XB_FWD_PARTS 2
 #endif
 
 namespace xb {
@@ -50,8 +56,8 @@ struct FwdSmem {
   alignas(1024) uint8_t k[kKStages][kTileBytes];
   alignas(1024) uint8_t v[kVStages][kTileBytes];
   float scale_buf[2][kBlockM];       // rescale factors, double-buffered by iteration parity
-  float xmax[2][2][kBlockM];         // row maxima of the two column halves, by iteration parity
-  float final_l[2][kBlockM];
+  float xmax[2][XB_FWD_PARTS][kBlockM];   // row maxima of the column parts, by iteration parity
+  float final_l[XB_FWD_PARTS][kBlockM];
   float final_m[kBlockM];
   uint64_t q_full;
   uint64_t k_full[kKStages], k_empty[kKStages];
@@ -64,8 +70,11 @@ struct FwdSmem {
 
 // T: __nv_bfloat16 or __half.  HD: padded head dimension of the shared-memory tiles (64, 128 or 256).
 // HP: high-precision softmax.
+constexpr int kFwdParts = XB_FWD_PARTS;                 // softmax warpgroups
+constexpr int kFwdThreads = (4 * kFwdParts + 8) * 32;   // + correction warpgroup + issuers / TMA
+
 template <typename T, int HD, bool HP>
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
   using Smem = FwdSmem<HD>;
@@ -76,6 +85,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   // TMEM columns: S buffers at 0 / 128, O at 256, P buffers (64 packed columns each) at 384 / 448
   constexpr uint32_t cS = 0, cO = 256, cP = 384;
   constexpr int kFormat = Pack2<T>::kFormat;
+  constexpr int kParts = kFwdParts;                     // softmax warpgroups
+  constexpr int kCols = kBlockN / kParts;               // key-tile columns per softmax thread
+  constexpr int kCorrWarp = 4 * kParts, kPvWarp = kCorrWarp + 4, kTmaWarp = kCorrWarp + 5, kQkWarp = kCorrWarp + 6;
   // of every four pairs of exponentials, how many are computed on the FMA pipe (low precision only)
   constexpr int kFmaPairs = XB_FWD_FMA_PAIRS;
 
@@ -116,19 +128,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     for (int i = 0; i < kKStages; ++i) { mbar_init(&s.k_full[i], 1); mbar_init(&s.k_empty[i], 1); }
     for (int i = 0; i < kVStages; ++i) { mbar_init(&s.v_full[i], 1); mbar_init(&s.v_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&s.s_full[i], 1); mbar_init(&s.p_full[i], 8); mbar_init(&s.max_x[i], 8);
+      mbar_init(&s.s_full[i], 1); mbar_init(&s.p_full[i], 4 * kParts); mbar_init(&s.max_x[i], 4 * kParts);
       mbar_init(&s.p_free[i], 1);              // the P V product has read the P buffer
       // an S buffer is free again once the softmax holds it in registers, or, where P lies over S,
       // once the P V product has read it
-      mbar_init(&s.s_free[i], kAliasP ? 1 : 8);
+      mbar_init(&s.s_free[i], kAliasP ? 1 : 4 * kParts);
     }
     mbar_init(&s.o_ready, 4);
     mbar_init(&s.pv_done, 1);
     mbar_init(&s.corr_full, 4);
-    mbar_init(&s.final_full, 8);
+    mbar_init(&s.final_full, 4 * kParts);
     fence_mbar_init();
   }
-  if (warp == 13) {
+  if (warp == kTmaWarp) {
     tmem_alloc(&s.tmem_base, kTmemCols);
     tmem_relinquish();
   }
@@ -144,14 +156,21 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const int v_pad = (p.V + 15) & ~15;
   const bool dead = s.abort_flag != 0;
 
-  // 512 threads start with 128 registers each
-  if (warp < 8) setmaxnreg_inc<152>(); else if (warp < 12) setmaxnreg_dec<104>(); else setmaxnreg_dec<48>();
+  // Registers move between warps of this CTA only: what the softmax warps gain must not exceed what
+  // the others give up, or setmaxnreg.inc waits for ever.  512 threads start with 128 each, 768 with 80.
+  if (kParts == 2) {
+    static_assert(kParts != 2 || 256 * (152 - 128) <= 128 * (128 - 104) + 128 * (128 - 48), "register budget");
+    if (warp < 8) setmaxnreg_inc<152>(); else if (warp < 12) setmaxnreg_dec<104>(); else setmaxnreg_dec<48>();
+  } else {
+    static_assert(kParts != 4 || 512 * (88 - 80) <= 128 * (80 - 40), "register budget");
+    if (warp < 16) setmaxnreg_inc<88>(); else if (warp >= 20) setmaxnreg_dec<40>();
+  }
 
   if (dead) {
     // nothing to do
-  } else if (warp < 8) {
+  } else if (warp < 4 * kParts) {
     // =========================== softmax warpgroups ===========================
-    const int hf = warp >> 2;                   // which half of the key-tile columns
+    const int hf = warp >> 2;                   // which part of the key-tile columns
     const int r = tid & 127;
     const int row = qt * kBlockM + r;
     int lo = 0, hi = 0;
@@ -165,14 +184,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     bool ok = true;
     for (int j = 0; j < iters && ok; ++j) {
       const int buf = j & 1;
-      const int col0 = (n_lo + j) * kBlockN + hf * 64;
-      const uint32_t t_s = tmem + lane_off + cS + buf * 128 + hf * 64;
+      const int col0 = (n_lo + j) * kBlockN + hf * kCols;
+      const uint32_t t_s = tmem + lane_off + cS + buf * 128 + hf * kCols;
       ok = mbar_wait(ctx, &s.s_full[buf], (j >> 1) & 1, 10);
       if (!ok) break;
       tc_fence_after();
-      float sc[64];
-      tmem_ld_x32(t_s, reinterpret_cast<uint32_t*>(sc));
-      tmem_ld_x32(t_s + 32, reinterpret_cast<uint32_t*>(sc) + 32);
+      float sc[kCols];
+#pragma unroll
+      for (int c = 0; c < kCols; c += 32) tmem_ld_x32(t_s + c, reinterpret_cast<uint32_t*>(sc) + c);
       tc_wait_ld();
       if (!kAliasP) {
         tc_fence_before();
@@ -182,26 +201,33 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       if (!tile_full) {
         const int rl = lo - col0, rh = hi - col0;
 #pragma unroll
-        for (int c = 0; c < 64; ++c) sc[c] = (c >= rl && c < rh) ? sc[c] : -INFINITY;
+        for (int c = 0; c < kCols; ++c) sc[c] = (c >= rl && c < rh) ? sc[c] : -INFINITY;
       }
-      float mxa = max3(sc[0], sc[1], sc[2]), mxb = max3(sc[3], sc[4], sc[5]);
-      float mxc = max3(sc[6], sc[7], sc[8]), mxd = max3(sc[9], sc[10], sc[11]);
+      float mx4[4];
 #pragma unroll
-      for (int c = 12; c < 60; c += 8) {
-        mxa = max3(mxa, sc[c], sc[c + 1]);
-        mxb = max3(mxb, sc[c + 2], sc[c + 3]);
-        mxc = max3(mxc, sc[c + 4], sc[c + 5]);
-        mxd = max3(mxd, sc[c + 6], sc[c + 7]);
+      for (int e = 0; e < 4; ++e) mx4[e] = max3(sc[8 * e], sc[8 * e + 1], sc[8 * e + 2]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        mx4[e] = max3(mx4[e], sc[8 * e + 3], sc[8 * e + 4]);
+        mx4[e] = max3(mx4[e], sc[8 * e + 5], sc[8 * e + 6]);
+        mx4[e] = fmaxf(mx4[e], sc[8 * e + 7]);
       }
-      mxa = max3(mxa, sc[60], sc[61]);
-      mxb = max3(mxb, sc[62], sc[63]);
-      float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
-      // the row maximum over both halves
+#pragma unroll
+      for (int c = 32; c < kCols; c += 8) {
+        const int e = (c >> 3) & 3;
+        mx4[e] = max3(mx4[e], sc[c], sc[c + 1]);
+        mx4[e] = max3(mx4[e], sc[c + 2], sc[c + 3]);
+        mx4[e] = max3(mx4[e], sc[c + 4], sc[c + 5]);
+        mx4[e] = max3(mx4[e], sc[c + 6], sc[c + 7]);
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // the row maximum over all column parts
       s.xmax[buf][hf][r] = mx;
       mbar_arrive_warp(&s.max_x[buf]);
       ok = mbar_wait(ctx, &s.max_x[buf], (j >> 1) & 1, 11);
       if (!ok) break;
-      mx = fmaxf(mx, s.xmax[buf][hf ^ 1][r]);
+#pragma unroll
+      for (int o = 1; o < kParts; ++o) mx = fmaxf(mx, s.xmax[buf][(hf + o) % kParts][r]);
       float m_new = fmaxf(m, mx);
       if (!HP) {
         // keep the old reference while the maximum grew by less than 2^8: the accumulator is then
@@ -217,12 +243,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       m = m_new;
       const float m_ref = (m == -INFINITY) ? 0.f : m;
       const float neg_mc = -m_ref * c_log2;
-      uint32_t pk[32];
+      uint32_t pk[kCols / 2];
       float sum = 0.f;
       if (HP) {
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < 64; c += 2) {
+        for (int c = 0; c < kCols; c += 2) {
           const float p0 = exp2f(__fmul_rn(__fsub_rn(sc[c], m_ref), c_log2));
           const float p1 = exp2f(__fmul_rn(__fsub_rn(sc[c + 1], m_ref), c_log2));
           sum4[(c >> 1) & 3] += p0 + p1;
@@ -237,7 +263,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const float2 cc = make_float2(c_log2, c_log2), nm = make_float2(neg_mc, neg_mc);
         float2 s2a = make_float2(0.f, 0.f), s2b = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int c = 0; c < 64; c += 8) {
+        for (int c = 0; c < kCols; c += 8) {
           float2 pr[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -259,14 +285,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const float2 s2 = add2(s2a, s2b);
         sum = s2.x + s2.y;
       }
-      // 32 packed columns per half: next to each other in the P buffer (once the product two tiles
-      // back has read it), or (HD = 256) over the first 32 of the half's own S columns
+      // kCols / 2 packed columns per part: next to each other in the P buffer (once the product two
+      // tiles back has read it), or (HD = 256) over the first half of the part's own S columns
       if (!kAliasP && j >= 2) {
         ok = mbar_wait(ctx, &s.p_free[buf], ((j >> 1) - 1) & 1, 12);
         if (!ok) break;
         tc_fence_after();
       }
-      tmem_st_x32(kAliasP ? t_s : tmem + lane_off + cP + buf * 64 + hf * 32, pk);
+      {
+        const uint32_t t_p = kAliasP ? t_s : tmem + lane_off + cP + buf * 64 + hf * (kCols / 2);
+        if (kCols == 64) tmem_st_x32(t_p, pk); else tmem_st_x16(t_p, pk);
+      }
       l = l * factor + sum;
       tc_wait_st();
       tc_fence_before();
@@ -276,7 +305,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     s.final_l[hf][r] = l;
     if (hf == 0) s.final_m[r] = m;
     mbar_arrive_warp(&s.final_full);
-  } else if (warp < 12) {
+  } else if (warp < kCorrWarp + 4) {
     // ======================= correction + epilogue warpgroup =======================
     const int r = tid & 127;
     const int row = qt * kBlockM + r;
@@ -310,7 +339,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     if (ok && iters > 0) ok = mbar_wait(ctx, &s.pv_done, (iters - 1) & 1, 26);
     if (ok) {
       tc_fence_after();
-      const float l = s.final_l[0][r] + s.final_l[1][r];
+      float l = 0.f;
+#pragma unroll
+      for (int o = 0; o < kParts; ++o) l += s.final_l[o][r];
       const float m = s.final_m[r];
       const bool has = l > 0.f && iters > 0;
       float inv = 0.f;
@@ -354,7 +385,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
       }
     }
-  } else if (warp == 14 && lane == 0 && iters > 0) {
+  } else if (warp == kQkWarp && lane == 0 && iters > 0) {
     // ------------------------------ S = Q K^T issuer ------------------------------
     const uint32_t idesc_qk = make_idesc(kBlockM, kBlockN, kFormat, 0, 0);
     bool ok = mbar_wait(ctx, &s.q_full, 0, 30);
@@ -373,7 +404,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       umma_commit(&s.s_full[i & 1]);
       umma_commit(&s.k_empty[ks]);
     }
-  } else if (warp == 12 && lane == 0 && iters > 0) {
+  } else if (warp == kPvWarp && lane == 0 && iters > 0) {
     // ------------------------------ O += P V issuer ------------------------------
     const uint32_t idesc_pv = make_idesc(kBlockM, v_pad, kFormat, 0, 1);
     bool ok = true;
@@ -387,7 +418,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const uint32_t va = smem_u32(s.v[vs]);
 #pragma unroll
       for (int js = 0; js < kBlockN / 16; ++js) {
-        const uint32_t a_col = kAliasP ? tmem + cS + (n & 1) * 128 + (js >> 2) * 64 + (js & 3) * 8
+        // k-step js = 16 keys = 8 packed columns; over S they sit at the start of their part's columns
+        constexpr int kStepsPerPart = kCols / 16;
+        const uint32_t a_col = kAliasP ? tmem + cS + (n & 1) * 128 + (js / kStepsPerPart) * kCols + (js % kStepsPerPart) * 8
                                        : tmem + cP + (n & 1) * 64 + js * 8;
         umma_ts(tmem + cO, a_col, make_smem_desc(va + js * 2048, kBoxBytes, 1024), idesc_pv,
                 (n > 0 || js > 0) ? 1u : 0u);
@@ -397,7 +430,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       umma_commit(&s.p_free[n & 1]);
       if (kAliasP) umma_commit(&s.s_free[n & 1]);
     }
-  } else if (warp == 13 && lane == 0 && iters > 0) {
+  } else if (warp == kTmaWarp && lane == 0 && iters > 0) {
     // ------------------------------ TMA producer ------------------------------
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
@@ -437,7 +470,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     while (globaltimer_ns() - t0 < 200000ull) { }
     __syncthreads();
   }
-  if (warp == 13) {
+  if (warp == kTmaWarp) {
     __syncwarp();
     tmem_dealloc(tmem, kTmemCols);
   }
@@ -464,7 +497,7 @@ static int launch_fwd(const XattnFwdArgs& a, const FwdParams& p, cudaStream_t st
   if (grid <= 0 || grid > 0x7fffffffLL) { set_error("forward grid out of range"); return XATTN_E_INVALID; }
   {
     ProfileScope prof(kProfFwd, stream);
-    kern<<<(unsigned)grid, 512, smem, stream>>>(tq, tk, tv, p);
+    kern<<<(unsigned)grid, kFwdThreads, smem, stream>>>(tq, tk, tv, p);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("forward launch: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
