@@ -236,3 +236,12 @@ def test_long_sequence_properties(cuda_device):
     torch.testing.assert_close(y[:, rows].cpu(), ref.to(torch.bfloat16), atol=1e-2, rtol=1e-2)
     dq2, dk2, dv2 = xattn.causal_flash_attn_bwd(dy, q, k, v, y, lse, segment_idx=ids)
     assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
+    # the warp roles of the kernels hand tiles to each other through barriers: a slip there shows as
+    # a run that differs, so repeat the dense form of the shape a few times
+    yd, lsed = xattn.causal_flash_attn_fwd(q, k, v)
+    gd = xattn.causal_flash_attn_bwd(dy, q, k, v, yd, lsed)
+    for _ in range(4):
+        y2, lse2 = xattn.causal_flash_attn_fwd(q, k, v)
+        assert torch.equal(yd, y2) and torch.equal(lsed, lse2)
+        for a, b in zip(gd, xattn.causal_flash_attn_bwd(dy, q, k, v, yd, lsed)):
+            assert torch.equal(a, b)

@@ -56,13 +56,13 @@ struct FwdSmem {
   alignas(1024) uint8_t k[kKStages][kTileBytes];
   alignas(1024) uint8_t v[kVStages][kTileBytes];
   float scale_buf[2][kBlockM];       // rescale factors, double-buffered by iteration parity
-  float xmax[2][XB_FWD_PARTS][kBlockM];   // row maxima of the column parts, by iteration parity
+  float xmax[4][XB_FWD_PARTS][kBlockM];   // row maxima of the column parts, by iteration mod 4
   float final_l[XB_FWD_PARTS][kBlockM];
   float final_m[kBlockM];
   uint64_t q_full;
   uint64_t k_full[kKStages], k_empty[kKStages];
   uint64_t v_full[kVStages], v_empty[kVStages];
-  uint64_t s_full[2], s_free[2], p_full[2], p_free[2], max_x[2];
+  uint64_t s_full[2], s_free[2], p_full[2], p_free[2], max_x[4];
   uint64_t o_ready, pv_done, corr_full, final_full;
   uint32_t tmem_base;
   int abort_flag;
@@ -128,7 +128,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     for (int i = 0; i < kKStages; ++i) { mbar_init(&s.k_full[i], 1); mbar_init(&s.k_empty[i], 1); }
     for (int i = 0; i < kVStages; ++i) { mbar_init(&s.v_full[i], 1); mbar_init(&s.v_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&s.s_full[i], 1); mbar_init(&s.p_full[i], 4 * kParts); mbar_init(&s.max_x[i], 4 * kParts);
+      mbar_init(&s.s_full[i], 1); mbar_init(&s.p_full[i], 4 * kParts);
+      mbar_init(&s.max_x[2 * i], 4 * kParts); mbar_init(&s.max_x[2 * i + 1], 4 * kParts);
       mbar_init(&s.p_free[i], 1);              // the P V product has read the P buffer
       // an S buffer is free again once the softmax holds it in registers, or, where P lies over S,
       // once the P V product has read it
@@ -221,13 +222,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         mx4[e] = max3(mx4[e], sc[c + 6], sc[c + 7]);
       }
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // the row maximum over all column parts
-      s.xmax[buf][hf][r] = mx;
-      mbar_arrive_warp(&s.max_x[buf]);
-      ok = mbar_wait(ctx, &s.max_x[buf], (j >> 1) & 1, 11);
+      // The row maximum over all column parts.  Four slots: a part can be here for tile j + 4 only
+      // after every part has loaded S of tile j + 2 (the S buffer it needs is free no earlier), that
+      // is after every part has finished with the slot of tile j.  With two slots a part running
+      // ahead could overwrite a maximum another part has not read yet.
+      s.xmax[j & 3][hf][r] = mx;
+      mbar_arrive_warp(&s.max_x[j & 3]);
+      ok = mbar_wait(ctx, &s.max_x[j & 3], (j >> 2) & 1, 11);
       if (!ok) break;
 #pragma unroll
-      for (int o = 1; o < kParts; ++o) mx = fmaxf(mx, s.xmax[buf][(hf + o) % kParts][r]);
+      for (int o = 1; o < kParts; ++o) mx = fmaxf(mx, s.xmax[j & 3][(hf + o) % kParts][r]);
       float m_new = fmaxf(m, mx);
       if (!HP) {
         // keep the old reference while the maximum grew by less than 2^8: the accumulator is then
@@ -236,10 +240,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
       float factor = 1.f;
       if (m != -INFINITY && m_new != m) factor = HP ? exp2f((m - m_new) * c_log2) : ex2_approx((m - m_new) * c_log2);
-      if (hf == 0 && j > 0) {
-        s.scale_buf[buf][r] = factor;
-        mbar_arrive_warp(&s.corr_full);
-      }
       m = m_new;
       const float m_ref = (m == -INFINITY) ? 0.f : m;
       const float neg_mc = -m_ref * c_log2;
@@ -291,6 +291,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         ok = mbar_wait(ctx, &s.p_free[buf], ((j >> 1) - 1) & 1, 12);
         if (!ok) break;
         tc_fence_after();
+      }
+      // The rescale factor goes to the correction warpgroup only now: the softmax may run two tiles
+      // ahead of the P V products, and the product two tiles back having finished (the wait above;
+      // with P over S the S buffer itself could not have been refilled earlier) is what guarantees
+      // that the correction warpgroup has taken the factor this slot held before.
+      if (hf == 0 && j > 0) {
+        s.scale_buf[buf][r] = factor;
+        mbar_arrive_warp(&s.corr_full);
       }
       {
         const uint32_t t_p = kAliasP ? t_s : tmem + lane_off + cP + buf * 64 + hf * (kCols / 2);
