@@ -1,8 +1,8 @@
 """Generates tests/golden/attention_golden.npz from the REFERENCE's own oracle.
 
-Run once in a container that has the reference checkout (default /root/reference):
+Run once where a checkout of the reference is available:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 It imports the reference's tests/_reference.py (``_allowed_masks``, ``_attention_from_mask``) and
 tests/softdelta/reference.py (``softdelta_fp64_oracle``), runs them in FP64 on small seeded inputs
@@ -24,7 +24,9 @@ from golden_cases import GOLDEN_CASES, golden_inputs  # noqa: E402
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py /path/to/reference")
+    ref_root = sys.argv[1]
     sys.path.insert(0, ref_root)
     from tests._reference import _allowed_masks, _attention_from_mask  # reference code
     from tests.softdelta.reference import softdelta_fp64_oracle        # reference code
