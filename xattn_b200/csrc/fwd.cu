@@ -63,7 +63,7 @@ struct FwdSmem {
   uint64_t k_full[kKStages], k_empty[kKStages];
   uint64_t v_full[kVStages], v_empty[kVStages];
   uint64_t s_full[2], s_free[2], p_full[2], p_free[2], max_x[4];
-  uint64_t o_ready, pv_done, corr_full, final_full;
+  uint64_t o_ready, pv_done, corr_full, final_full, y_staged;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -76,7 +76,7 @@ constexpr int kFwdThreads = (4 * kFwdParts + 8) * 32;   // + correction warpgrou
 template <typename T, int HD, bool HP>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-           const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_y, const FwdParams p) {
   using Smem = FwdSmem<HD>;
   constexpr bool kAliasP = HD > 128;                    // P over S instead of in columns of its own
   constexpr int kKStages = Smem::kKStages, kVStages = Smem::kVStages, kLA = Smem::kLookahead;
@@ -108,6 +108,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const int h = kvh * G + (rem % G);
   const int b = bk / p.Hkv;
 
+  if (warp == kTmaWarp && lane == 0) {
+    // The Q tile needs nothing but the block index: its load starts before anything else, the mask
+    // plan's tile summary included (its barrier is initialised here, by the thread that uses it first).
+    tma_prefetch_desc(&tm_q);
+    mbar_init(&s.q_full, 1);
+    fence_mbar_init();
+    mbar_arrive_expect_tx(&s.q_full, ((p.D + 63) / 64) * kBoxBytes);
+    for (int bx = 0; bx < (p.D + 63) / 64; ++bx)
+      tma_load_4d(s.q + bx * kBoxBytes, &tm_q, &s.q_full, bx * 64, h, qt * kBlockM, b);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_y);
+  }
   int n_lo = 0, n_hi = 0, full_lo = 0x7fffffff, full_hi = 0;
   {
     const TileInfo ti = p.q_tiles[(size_t)b * p.nQT + qt];
@@ -124,7 +137,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   if (tid == 0) {
     // an earlier CTA gave up: do not pile on
     s.abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 2 : 0;
-    mbar_init(&s.q_full, 1);
     for (int i = 0; i < kKStages; ++i) { mbar_init(&s.k_full[i], 1); mbar_init(&s.k_empty[i], 1); }
     for (int i = 0; i < kVStages; ++i) { mbar_init(&s.v_full[i], 1); mbar_init(&s.v_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
@@ -139,6 +151,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     mbar_init(&s.pv_done, 1);
     mbar_init(&s.corr_full, 4);
     mbar_init(&s.final_full, 4 * kParts);
+    mbar_init(&s.y_staged, 4);
     fence_mbar_init();
   }
   if (warp == kTmaWarp) {
@@ -345,6 +358,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // epilogue: y = O / l, lse = ln2 * (m * c + log2 l)
     if (ok) ok = mbar_wait(ctx, &s.final_full, 0, 24);
     if (ok && iters > 0) ok = mbar_wait(ctx, &s.pv_done, (iters - 1) & 1, 26);
+    if (ok && iters == 0) ok = mbar_wait(ctx, &s.q_full, 0, 28);   // the Q load has landed: its buffer is reused below
     if (ok) {
       tc_fence_after();
       float l = 0.f;
@@ -359,8 +373,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         p.lse[((size_t)b * p.Hq + h) * p.Lq + row] =
             has ? (m * c_log2 + log2f(l)) * 0.6931471805599453f : -INFINITY;
       }
+      // y leaves through shared memory and bulk tensor stores (the Q tile's buffer is free by now:
+      // every S product has run): coalesced, clipped to the tensor by the hardware, and the CTA
+      // does not have to wait for the writes themselves.  Layout: 64-column boxes of 128-byte
+      // rows in the 128-byte swizzle (16-byte chunk c of row r sits at chunk c ^ (r & 7)).
       const uint32_t t_o = tmem + lane_off + cO;
-      T* y_row = reinterpret_cast<T*>(p.y) + (((size_t)b * p.Lq + (live ? row : 0)) * p.Hq + h) * p.V;
       float* ys_row = p.y_state ? p.y_state + (((size_t)b * p.Lq + (live ? row : 0)) * p.Hq + h) * p.V : nullptr;
       for (int c0 = 0; c0 < v_pad; c0 += 32) {
         uint32_t o[32];
@@ -371,25 +388,33 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
           for (int c = 0; c < 32; ++c) o[c] = 0u;
         }
-        if (live) {
+        uint8_t* box = s.q + (c0 >> 6) * kBoxBytes + r * 128;
 #pragma unroll
-          for (int c = 0; c < 32; c += 8) {
-            if (c0 + c < p.V) {
-              float f[8];
+        for (int c = 0; c < 32; c += 8) {
+          float f[8];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[c + e]) * inv;
-              uint4 pk;
-              pk.x = Pack2<T>::pack(f[0], f[1]);
-              pk.y = Pack2<T>::pack(f[2], f[3]);
-              pk.z = Pack2<T>::pack(f[4], f[5]);
-              pk.w = Pack2<T>::pack(f[6], f[7]);
-              *reinterpret_cast<uint4*>(y_row + c0 + c) = pk;
-              if (ys_row) {
-                *reinterpret_cast<float4*>(ys_row + c0 + c) = make_float4(f[0], f[1], f[2], f[3]);
-                *reinterpret_cast<float4*>(ys_row + c0 + c + 4) = make_float4(f[4], f[5], f[6], f[7]);
-              }
-            }
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[c + e]) * inv;
+          uint4 pk;
+          pk.x = Pack2<T>::pack(f[0], f[1]);
+          pk.y = Pack2<T>::pack(f[2], f[3]);
+          pk.z = Pack2<T>::pack(f[4], f[5]);
+          pk.w = Pack2<T>::pack(f[6], f[7]);
+          const int chunk = ((c0 & 63) + c) >> 3;
+          *reinterpret_cast<uint4*>(box + ((chunk ^ (r & 7)) << 4)) = pk;
+          if (ys_row && live && c0 + c < p.V) {
+            *reinterpret_cast<float4*>(ys_row + c0 + c) = make_float4(f[0], f[1], f[2], f[3]);
+            *reinterpret_cast<float4*>(ys_row + c0 + c + 4) = make_float4(f[4], f[5], f[6], f[7]);
           }
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive_warp(&s.y_staged);
+      if (warp == kCorrWarp && lane == 0) {
+        ok = mbar_wait(ctx, &s.y_staged, 0, 27);
+        if (ok) {
+          for (int bx = 0; bx < nbox_v; ++bx) tma_store_4d(&tm_y, s.q + bx * kBoxBytes, bx * 64, h, qt * kBlockM, b);
+          tma_store_commit();
+          tma_store_wait_read_all();
         }
       }
     }
@@ -440,12 +465,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     }
   } else if (warp == kTmaWarp && lane == 0 && iters > 0) {
     // ------------------------------ TMA producer ------------------------------
-    tma_prefetch_desc(&tm_k);
-    tma_prefetch_desc(&tm_v);
-    tma_prefetch_desc(&tm_q);
-    mbar_arrive_expect_tx(&s.q_full, nbox_qk * kBoxBytes);
-    for (int bx = 0; bx < nbox_qk; ++bx)
-      tma_load_4d(s.q + bx * kBoxBytes, &tm_q, &s.q_full, bx * 64, h, qt * kBlockM, b);
     bool ok = true;
     // K runs kLA tiles ahead of V, the order in which the two products consume them
     for (int i = 0; i < iters + kLA && ok; ++i) {
@@ -470,6 +489,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   }
 
   // ---- tail -----------------------------------------------------------------
+  if (dead && warp == kTmaWarp && lane == 0) {
+    // the Q load was issued before the abort flag was read: let it land (bounded)
+    for (int i = 0; i < (1 << 20) && !mbar_try_wait(&s.q_full, 0); ++i) { }
+  }
   tc_fence_before();
   __syncthreads();
   if (s.abort_flag == 1) {
@@ -497,6 +520,9 @@ static int launch_fwd(const XattnFwdArgs& a, const FwdParams& p, cudaStream_t st
                     a.k_strides[2], kBlockN)) return XATTN_E_INVALID;
   if (make_tile_map(&tv, a.v, a.dtype, a.batch, a.k_len, a.kv_heads, a.v_dim, a.v_strides[0], a.v_strides[1],
                     a.v_strides[2], kBlockN)) return XATTN_E_INVALID;
+  CUtensorMap ty;
+  if (make_tile_map(&ty, a.y, a.dtype, a.batch, a.q_len, a.q_heads, a.v_dim, a.q_len * a.q_heads * a.v_dim,
+                    a.q_heads * a.v_dim, a.v_dim, kBlockM)) return XATTN_E_INVALID;
   const size_t smem = sizeof(Smem) + 1024;
   auto kern = fwd_kernel<T, HD, HP>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -505,7 +531,7 @@ static int launch_fwd(const XattnFwdArgs& a, const FwdParams& p, cudaStream_t st
   if (grid <= 0 || grid > 0x7fffffffLL) { set_error("forward grid out of range"); return XATTN_E_INVALID; }
   {
     ProfileScope prof(kProfFwd, stream);
-    kern<<<(unsigned)grid, kFwdThreads, smem, stream>>>(tq, tk, tv, p);
+    kern<<<(unsigned)grid, kFwdThreads, smem, stream>>>(tq, tk, tv, ty, p);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("forward launch: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
