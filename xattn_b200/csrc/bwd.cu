@@ -179,7 +179,7 @@ struct DqSmem {
   alignas(1024) uint8_t v[2][kKvBytes];
   uint64_t do_full, q_ready;
   uint64_t k_full[kKStages], k_empty[kKStages], v_full[2], v_empty[2];
-  uint64_t s_full, s_free, dp_full, dp_free, ds_full, dq_done;
+  uint64_t s_full, s_free, dp_full, dp_free, ds_full, dq_done, dq_staged;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -190,7 +190,7 @@ struct DqSmem {
 template <typename T, int HD, int BN>
 __global__ void __launch_bounds__(384, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_k,
-              const __grid_constant__ CUtensorMap tm_v, const BwdParams p) {
+              const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_dq, const BwdParams p) {
   using Smem = DqSmem<HD, BN>;
   constexpr bool kDsOverDp = HD > 128;          // no TMEM columns left for dS
   constexpr int kKStages = Smem::kKStages;
@@ -220,6 +220,17 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
   const int h = kvh * G + (rem % G);
   const int b = bk / p.Hkv;
 
+  if (warp == 9 && lane == 0) {
+    // The dO tile needs nothing but the block index: its load starts before anything else, the
+    // mask plan's tile summary included (its barrier is initialised here, by its first user).
+    tma_prefetch_desc(&tm_do);
+    mbar_init(&s.do_full, 1);
+    fence_mbar_init();
+    mbar_arrive_expect_tx(&s.do_full, ((p.V + 63) / 64) * kDoBox);
+    for (int bx = 0; bx < (p.V + 63) / 64; ++bx)
+      tma_load_4d(s.d_o + bx * kDoBox, &tm_do, &s.do_full, bx * 64, h, qt * kBlockM, b);
+    tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_dq);
+  }
   int n_lo = 0, n_hi = 0, full_lo = 0x7fffffff, full_hi = 0;
   {
     const TileInfo ti = p.q_tiles[(size_t)b * p.nQT + qt];
@@ -234,7 +245,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
 
   if (tid == 0) {
     s.abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 2 : 0;
-    mbar_init(&s.do_full, 1);
     mbar_init(&s.q_ready, 8);
     for (int i = 0; i < kKStages; ++i) { mbar_init(&s.k_full[i], 1); mbar_init(&s.k_empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&s.v_full[i], 1); mbar_init(&s.v_empty[i], 1); }
@@ -244,6 +254,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
     mbar_init(&s.dp_free, 8);
     mbar_init(&s.ds_full, 8);
     mbar_init(&s.dq_done, 1);
+    mbar_init(&s.dq_staged, 8);
     fence_mbar_init();
   }
   if (warp == 9) { tmem_alloc(&s.tmem_base, kTmemCols); tmem_relinquish(); }
@@ -372,25 +383,36 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
       if (ok) ok = mbar_wait(ctx, &s.dq_done, (iters - 1) & 1, 52);
       if (ok) {
         tc_fence_after();
-        // this warpgroup writes columns [hf*HD/2, (hf+1)*HD/2) of dQ
+        // This warpgroup has columns [hf*HD/2, (hf+1)*HD/2) of dQ.  They leave through shared memory
+        // (the dO tile's buffer: every dP product has run) and bulk tensor stores: coalesced, clipped
+        // to the tensor by the hardware.  Layout: 64-column boxes of 128-byte rows in the 128-byte
+        // swizzle (16-byte chunk c of row r sits at chunk c ^ (r & 7)).
 #pragma unroll
         for (int c0 = 0; c0 < HD / 2; c0 += 32) {
           const int cbase = hf * (HD / 2) + c0;
           uint32_t o[32];
           tmem_ld_x32(tmem + lane_off + cDQ + cbase, o);
           tc_wait_ld();
-          if (live) {
+          uint8_t* box = s.d_o + (cbase >> 6) * kDoBox + r * 128;
 #pragma unroll
-            for (int c = 0; c < 32; c += 8) {
-              if (cbase + c < p.D) {
-                uint4 u;
-                u.x = Pack2<T>::pack(__uint_as_float(o[c + 0]) * p.scale, __uint_as_float(o[c + 1]) * p.scale);
-                u.y = Pack2<T>::pack(__uint_as_float(o[c + 2]) * p.scale, __uint_as_float(o[c + 3]) * p.scale);
-                u.z = Pack2<T>::pack(__uint_as_float(o[c + 4]) * p.scale, __uint_as_float(o[c + 5]) * p.scale);
-                u.w = Pack2<T>::pack(__uint_as_float(o[c + 6]) * p.scale, __uint_as_float(o[c + 7]) * p.scale);
-                *reinterpret_cast<uint4*>(dq_row + cbase + c) = u;
-              }
-            }
+          for (int c = 0; c < 32; c += 8) {
+            uint4 u;
+            u.x = Pack2<T>::pack(__uint_as_float(o[c + 0]) * p.scale, __uint_as_float(o[c + 1]) * p.scale);
+            u.y = Pack2<T>::pack(__uint_as_float(o[c + 2]) * p.scale, __uint_as_float(o[c + 3]) * p.scale);
+            u.z = Pack2<T>::pack(__uint_as_float(o[c + 4]) * p.scale, __uint_as_float(o[c + 5]) * p.scale);
+            u.w = Pack2<T>::pack(__uint_as_float(o[c + 6]) * p.scale, __uint_as_float(o[c + 7]) * p.scale);
+            const int chunk = ((cbase & 63) + c) >> 3;
+            *reinterpret_cast<uint4*>(box + ((chunk ^ (r & 7)) << 4)) = u;
+          }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive_warp(&s.dq_staged);
+        if (tid == 0) {
+          ok = mbar_wait(ctx, &s.dq_staged, 0, 54);
+          if (ok) {
+            for (int bx = 0; bx < nbox_qk; ++bx) tma_store_4d(&tm_dq, s.d_o + bx * kDoBox, bx * 64, h, qt * kBlockM, b);
+            tma_store_commit();
+            tma_store_wait_read_all();
           }
         }
       }
@@ -454,10 +476,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
     }
   } else if (warp == 9 && lane == 0 && iters > 0) {
     // ------------------------------ TMA producer ------------------------------
-    tma_prefetch_desc(&tm_do); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
-    mbar_arrive_expect_tx(&s.do_full, nbox_v * kDoBox);
-    for (int bx = 0; bx < nbox_v; ++bx)
-      tma_load_4d(s.d_o + bx * kDoBox, &tm_do, &s.do_full, bx * 64, h, qt * kBlockM, b);
     bool ok = true;
     for (int i = 0; i < iters && ok; ++i) {
       const int st = i & 1, ks = i % kKStages, n = n_lo + i;
@@ -474,6 +492,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
     }
   }
 
+  if ((dead || iters == 0) && warp == 9 && lane == 0) {
+    // the dO load was issued before anything was known: let it land (bounded)
+    for (int i = 0; i < (1 << 20) && !mbar_try_wait(&s.do_full, 0); ++i) { }
+  }
   tc_fence_before();
   __syncthreads();
   if (s.abort_flag == 1) {
@@ -964,6 +986,9 @@ static int launch_dq(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t str
   if (make_tile_map(&tdo, a.dy, a.dtype, a.batch, a.q_len, a.q_heads, a.v_dim, a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], kBlockM)) return XATTN_E_INVALID;
   if (make_tile_map(&tk, a.k, a.dtype, a.batch, a.k_len, a.kv_heads, a.qk_dim, a.k_strides[0], a.k_strides[1], a.k_strides[2], BN)) return XATTN_E_INVALID;
   if (make_tile_map(&tv, a.v, a.dtype, a.batch, a.k_len, a.kv_heads, a.v_dim, a.v_strides[0], a.v_strides[1], a.v_strides[2], BN)) return XATTN_E_INVALID;
+  CUtensorMap tdq;
+  if (make_tile_map(&tdq, a.dq, a.dtype, a.batch, a.q_len, a.q_heads, a.qk_dim, a.q_len * a.q_heads * a.qk_dim,
+                    a.q_heads * a.qk_dim, a.qk_dim, kBlockM)) return XATTN_E_INVALID;
   auto kern = bwd_dq_kernel<T, HD, BN>;
   const size_t smem = sizeof(DqSmem<HD, BN>) + 1024;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -972,7 +997,7 @@ static int launch_dq(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t str
   if (grid > 0x7fffffffLL) { set_error("dQ grid out of range"); return XATTN_E_INVALID; }
   {
     ProfileScope prof(kProfBwdDq, stream);
-    kern<<<(unsigned)grid, 384, smem, stream>>>(tdo, tk, tv, p);
+    kern<<<(unsigned)grid, 384, smem, stream>>>(tdo, tk, tv, tdq, p);
   }
   return XATTN_OK;
 }
