@@ -533,7 +533,7 @@ struct DkvSmem {
   // per TMEM buffer: S^T / dP^T written by their products, P^T / dS^T written by the warpgroups,
   // and the two regions read by dV / dK and free for the next products
   uint64_t s_full[2], dp_full[2], p_full[2][2], ds_full[2], s_free[2], dp_free[2];   // p_full: per chunk
-  uint64_t all_done;
+  uint64_t all_done, out_staged[2];
   uint32_t tmem_base;
   int abort_flag;
   // one bit per query tile of [m_first, m_first + kTileCache): it sees this key tile at all / every
@@ -597,7 +597,8 @@ template <typename T, int HD, int MODE, int SM>
 __global__ void __launch_bounds__(384, 1)
 bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-               const __grid_constant__ CUtensorMap tm_terms, const BwdParams p) {
+               const __grid_constant__ CUtensorMap tm_terms, const __grid_constant__ CUtensorMap tm_dk,
+               const __grid_constant__ CUtensorMap tm_dv, const BwdParams p) {
   using Smem = DkvSmem<HD, MODE, SM>;
   using Iter = DkvIter<SM>;
   constexpr int kStages = Smem::kStages;
@@ -634,6 +635,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mbar_init(&s.s_free[i], 1); mbar_init(&s.dp_free[i], 1);
     }
     mbar_init(&s.all_done, 1);
+    mbar_init(&s.out_staged[0], 4); mbar_init(&s.out_staged[1], 4);
     fence_mbar_init();
   }
   if (warp == 9) { tmem_alloc(&s.tmem_base, kTmemCols); tmem_relinquish(); }
@@ -830,6 +832,11 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       T* out = wg == 0
           ? reinterpret_cast<T*>(p.dk) + (((size_t)b * p.Lk + (live ? key : 0)) * p.Hkv + kvh) * p.D
           : reinterpret_cast<T*>(p.dv) + (((size_t)b * p.Lk + (live ? key : 0)) * p.Hkv + kvh) * p.V;
+      // With 128-row steps the gradients leave through shared memory (a stage buffer: every product
+      // has run) and bulk tensor stores: coalesced and clipped to the tensor by the hardware.
+      // Layout: 64-column boxes of 128-byte rows in the 128-byte swizzle.
+      constexpr bool kStoreByTma = SM == kBlockN;
+      uint8_t* stage_buf = wg == 0 ? s.q[0] : s.d_o[0];
       for (int c0 = 0; c0 < pad; c0 += 32) {
         uint32_t o[32];
         if (any_work) {
@@ -839,7 +846,19 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
           for (int c = 0; c < 32; ++c) o[c] = 0u;
         }
-        if (live) {
+        if (kStoreByTma) {
+          uint8_t* box = stage_buf + (c0 >> 6) * kKvBox + r * 128;
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            uint4 u;
+            u.x = Pack2<T>::pack(__uint_as_float(o[c + 0]) * mul, __uint_as_float(o[c + 1]) * mul);
+            u.y = Pack2<T>::pack(__uint_as_float(o[c + 2]) * mul, __uint_as_float(o[c + 3]) * mul);
+            u.z = Pack2<T>::pack(__uint_as_float(o[c + 4]) * mul, __uint_as_float(o[c + 5]) * mul);
+            u.w = Pack2<T>::pack(__uint_as_float(o[c + 6]) * mul, __uint_as_float(o[c + 7]) * mul);
+            const int chunk = ((c0 & 63) + c) >> 3;
+            *reinterpret_cast<uint4*>(box + ((chunk ^ (r & 7)) << 4)) = u;
+          }
+        } else if (live) {
 #pragma unroll
           for (int c = 0; c < 32; c += 8) {
             if (c0 + c < width) {
@@ -850,6 +869,20 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               u.w = Pack2<T>::pack(__uint_as_float(o[c + 6]) * mul, __uint_as_float(o[c + 7]) * mul);
               *reinterpret_cast<uint4*>(out + c0 + c) = u;
             }
+          }
+        }
+      }
+      if (kStoreByTma) {
+        fence_proxy_async_smem();
+        mbar_arrive_warp(&s.out_staged[wg]);
+        if (wt == 0) {
+          ok = mbar_wait(ctx, &s.out_staged[wg], 0, 84);
+          if (ok) {
+            const int nbox = ((wg == 0 ? p.D : p.V) + 63) / 64;
+            for (int bx = 0; bx < nbox; ++bx)
+              tma_store_4d(wg == 0 ? &tm_dk : &tm_dv, stage_buf + bx * kKvBox, bx * 64, kvh, n * kBlockN, b);
+            tma_store_commit();
+            tma_store_wait_read_all();
           }
         }
       }
@@ -1009,8 +1042,12 @@ static int launch_dkv(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t st
   if (make_tile_map(&tdo, a.dy, a.dtype, a.batch, a.q_len, a.q_heads, a.v_dim, a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], SM)) return XATTN_E_INVALID;
   if (make_tile_map(&tk, a.k, a.dtype, a.batch, a.k_len, a.kv_heads, a.qk_dim, a.k_strides[0], a.k_strides[1], a.k_strides[2], kBlockN)) return XATTN_E_INVALID;
   if (make_tile_map(&tv, a.v, a.dtype, a.batch, a.k_len, a.kv_heads, a.v_dim, a.v_strides[0], a.v_strides[1], a.v_strides[2], kBlockN)) return XATTN_E_INVALID;
-  CUtensorMap tt;
+  CUtensorMap tt, tdk, tdv;
   if (make_row_map(&tt, p.row_terms, p.B, p.Hq, p.LqPad, SM)) return XATTN_E_INVALID;
+  if (make_tile_map(&tdk, a.dk, a.dtype, a.batch, a.k_len, a.kv_heads, a.qk_dim, a.k_len * a.kv_heads * a.qk_dim,
+                    a.kv_heads * a.qk_dim, a.qk_dim, kBlockN)) return XATTN_E_INVALID;
+  if (make_tile_map(&tdv, a.dv, a.dtype, a.batch, a.k_len, a.kv_heads, a.v_dim, a.k_len * a.kv_heads * a.v_dim,
+                    a.kv_heads * a.v_dim, a.v_dim, kBlockN)) return XATTN_E_INVALID;
   auto kern = bwd_dkv_kernel<T, HD, MODE, SM>;
   const size_t smem = sizeof(DkvSmem<HD, MODE, SM>) + 1024;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -1019,7 +1056,7 @@ static int launch_dkv(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t st
   if (grid > 0x7fffffffLL) { set_error("dK/dV grid out of range"); return XATTN_E_INVALID; }
   {
     ProfileScope prof(kProfBwdDkv, stream);
-    kern<<<(unsigned)grid, 384, smem, stream>>>(tq, tdo, tk, tv, tt, p);
+    kern<<<(unsigned)grid, 384, smem, stream>>>(tq, tdo, tk, tv, tt, tdk, tdv, p);
   }
   return XATTN_OK;
 }
