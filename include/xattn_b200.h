@@ -65,6 +65,9 @@ const char* xattn_b200_last_error(void);
  *   row_hi   [B][Lq]
  *   q_tiles  [B][nQT][4]   (min lo, max hi, max lo, min hi)
  *   k_tiles  [B][nKT][2]   (first query tile, last query tile + 1)
+ *   k_order  [B * nKT]     key tiles of all batch rows (b * nKT + tile), those seen by the most
+ *                          query tiles first: the launch order of the dK / dV kernel
+ * (each section padded to a multiple of 4 words)
  * ---------------------------------------------------------------------- */
 size_t xattn_b200_plan_bytes(int64_t batch, int64_t q_len, int64_t k_len);
 

@@ -39,7 +39,7 @@ def test_plan_bytes_layout():
     lib = _lib.load()
     assert lib.xattn_b200_plan_bytes(0, 1, 1) == 0
     # rows padded to 4 words twice, 4 words per query tile, 2 per key tile padded to 4
-    assert lib.xattn_b200_plan_bytes(1, 130, 300) == 4 * (2 * 132 + 4 * 2 + 8)
+    assert lib.xattn_b200_plan_bytes(1, 130, 300) == 4 * (2 * 132 + 4 * 2 + 8 + 4)   # rows, query tiles, key tiles, key-tile order
     assert lib.xattn_b200_bwd_workspace_bytes(2, 4, 100) == 2 * 4 * 128 * (2 * 4 + 32)   # rows padded to 128
 
 

@@ -37,6 +37,7 @@ struct BwdParams {
   const int* row_hi;
   const TileInfo* q_tiles;
   const KeyTileInfo* k_tiles;
+  const int* k_order;         // key tiles of all batch rows, most work first
   const void* q;              // for direct loads in the dQ kernel
   int64_t q_sb, q_sl, q_sh;   // element strides of q
   int LqPad;                  // q_len rounded up to whole 128-row tiles: row stride of nlse2 / ndelta
@@ -618,10 +619,11 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   const int G = p.Hq / p.Hkv;
-  const int n = blockIdx.x % p.nKT;            // early key tiles (most query tiles under causal masks) first
-  const int bk = blockIdx.x / p.nKT;
-  const int kvh = bk % p.Hkv;
-  const int b = bk / p.Hkv;
+  // key tiles with the most query tiles to visit first (the plan's order), their KV heads side by side
+  const int kvh = blockIdx.x % p.Hkv;
+  const int item = p.k_order[blockIdx.x / p.Hkv];
+  const int b = item / p.nKT;
+  const int n = item - b * p.nKT;
   const KeyTileInfo kti = p.k_tiles[(size_t)b * p.nKT + n];
   const TileInfo* qt_info = p.q_tiles + (size_t)b * p.nQT;
 
@@ -1128,6 +1130,7 @@ int bwd_entry(const XattnBwdArgs* a, cudaStream_t stream) {
   p.row_lo = a->plan + pl.off_lo; p.row_hi = a->plan + pl.off_hi;
   p.q_tiles = reinterpret_cast<const TileInfo*>(a->plan + pl.off_qt);
   p.k_tiles = reinterpret_cast<const KeyTileInfo*>(a->plan + pl.off_kt);
+  p.k_order = a->plan + pl.off_ko;
   p.q = a->q; p.q_sb = a->q_strides[0]; p.q_sl = a->q_strides[1]; p.q_sh = a->q_strides[2];
   p.dq = a->dq; p.dk = a->dk; p.dv = a->dv; p.status = a->status;
   if (a->dtype == XATTN_DTYPE_BF16) return launch_bwd<__nv_bfloat16>(*a, p, stream);

@@ -34,7 +34,7 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 // table starts on a 16-byte boundary.
 struct PlanLayout {
   int64_t rows, nQT, nKT;
-  int64_t off_lo, off_hi, off_qt, off_kt, words;
+  int64_t off_lo, off_hi, off_qt, off_kt, off_ko, words;   // off_ko: key tiles of all batch rows, most work first
   __host__ __device__ PlanLayout(int64_t B, int64_t Lq, int64_t Lk) {
     rows = B * Lq;
     nQT = (Lq + kBlockM - 1) / kBlockM;
@@ -44,7 +44,8 @@ struct PlanLayout {
     off_hi = r4;
     off_qt = 2 * r4;
     off_kt = off_qt + 4 * B * nQT;
-    words = off_kt + ((2 * B * nKT + 3) & ~int64_t(3));
+    off_ko = off_kt + ((2 * B * nKT + 3) & ~int64_t(3));
+    words = off_ko + ((B * nKT + 3) & ~int64_t(3));
   }
 };
 

@@ -224,12 +224,51 @@ __global__ void __launch_bounds__(128) plan_ktiles_kernel(const TileInfo* qt_inf
   if (lane == 0) { KeyTileInfo k; k.m_first = end > 0 ? first : 0; k.m_end = end; out[w] = k; }
 }
 
+// Key tiles of all batch rows ordered by the number of query tiles that see them, most first: the
+// dK / dV kernel's CTAs differ a lot in length under packed segments, and the hardware hands CTAs
+// to SMs in index order, so the long ones have to come first for the SMs to finish together.
+// One block; a counting sort (the order among equals is whatever the atomics give: it only
+// affects scheduling).  More bins than fit shared memory: identity order.
+constexpr int kOrderMaxBins = 8192;
+__global__ void __launch_bounds__(1024) plan_korder_kernel(const KeyTileInfo* kt, int items, int nQT, int* order) {
+  __shared__ int hist[kOrderMaxBins + 1];
+  typedef cub::BlockScan<int, 1024> Scan;
+  __shared__ typename Scan::TempStorage scan_tmp;
+  const int bins = nQT + 1, tid = threadIdx.x;
+  if (bins > kOrderMaxBins) {
+    for (int i = tid; i < items; i += 1024) order[i] = i;
+    return;
+  }
+  for (int i = tid; i < bins; i += 1024) hist[i] = 0;
+  __syncthreads();
+  for (int i = tid; i < items; i += 1024) {
+    const int w = min(max(kt[i].m_end - kt[i].m_first, 0), nQT);
+    atomicAdd(&hist[nQT - w], 1);             // bin 0 = most work
+  }
+  __syncthreads();
+  int carry = 0;
+  for (int base = 0; base < bins; base += 1024) {
+    const int i = base + tid;
+    const int v = i < bins ? hist[i] : 0;
+    int excl, total;
+    Scan(scan_tmp).ExclusiveSum(v, excl, total);
+    if (i < bins) hist[i] = carry + excl;
+    carry += total;
+    __syncthreads();
+  }
+  for (int i = tid; i < items; i += 1024) {
+    const int w = min(max(kt[i].m_end - kt[i].m_first, 0), nQT);
+    order[atomicAdd(&hist[nQT - w], 1)] = i;
+  }
+}
+
 static int finish_plan(int32_t* plan, const PlanLayout& pl, int B, int Lq, cudaStream_t stream) {
   const int nQT = (int)pl.nQT, nKT = (int)pl.nKT;
   TileInfo* qt = reinterpret_cast<TileInfo*>(plan + pl.off_qt);
   KeyTileInfo* kt = reinterpret_cast<KeyTileInfo*>(plan + pl.off_kt);
   plan_qtiles_kernel<<<ceil_div(B * nQT * 32, 128), 128, 0, stream>>>(plan + pl.off_lo, plan + pl.off_hi, B, Lq, nQT, qt);
   plan_ktiles_kernel<<<ceil_div(B * nKT * 32, 128), 128, 0, stream>>>(qt, B, nQT, nKT, kt);
+  plan_korder_kernel<<<1, 1024, 0, stream>>>(kt, B * nKT, nQT, plan + pl.off_ko);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("plan launch: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
   return XATTN_OK;
