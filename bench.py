@@ -45,7 +45,7 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 
 # DRAM bytes (read + write) of one launch per batch row of S=8192, Hq=32, Hkv=8, D=128, from the ncu
 # capture summarised in profiles/ncu_full_causal_small.md
-NCU_DRAM_BYTES_PER_BATCH_ROW = {"fwd": 134.6e6, "bwd_dq": 214.1e6, "bwd_dkv": 199.8e6}
+NCU_DRAM_BYTES_PER_BATCH_ROW = {"fwd": 137.8e6, "bwd_dq": 215.1e6, "bwd_dkv": 346.6e6}
 
 WORKLOADS = {
     # name: (B, S, Hq, Hkv, D, packed segments?, description)
