@@ -118,3 +118,16 @@ def test_softdelta_torch_plan_matches_oracle_on_cpu():
         ref, _, _ = O.softdelta(q.double(), k.double(), v.double(), g.double(), None, **okw)
         assert y.dtype == torch.bfloat16 and y.shape == ref.shape
         torch.testing.assert_close(y.double(), ref, atol=2e-2, rtol=2e-2)
+
+
+def test_value_group_entry_checks_layout():
+    """The internal value-group entry wants v [B, L, Hkv, C, Dg] and g [B, Lq, H, C, 1]
+    (tests/softdelta/test_value_groups.py:1-7); other layouts are refused before any kernel runs."""
+    import torch
+    from xattn_b200.ops.softdelta_attention import _softdelta_value_groups
+    q = torch.zeros(1, 4, 2, 8)
+    k = torch.zeros(1, 4, 1, 8)
+    with pytest.raises(ValueError, match="5D"):
+        _softdelta_value_groups(q, k, torch.zeros(1, 4, 1, 16), torch.zeros(1, 4, 2))
+    with pytest.raises(ValueError, match=r"\[B, Lq, H, C, 1\]"):
+        _softdelta_value_groups(q, k, torch.zeros(1, 4, 1, 2, 8), torch.zeros(1, 4, 2, 3, 1))
