@@ -141,3 +141,32 @@ def test_padded_gqa_gradients(operation, dims, level, cuda_device):
     for g_, w_ in zip(grads, want):
         assert g_.dtype == dtype and torch.isfinite(g_).all()
         assert (g_.double().cpu() - w_).norm() <= 0.015 * w_.norm() + 1e-6
+
+
+def test_plan_orders_key_tiles_longest_first(cuda_device):
+    """The last section of the mask plan lists the key tiles of all batch rows by the number of query
+    tiles that see them, most first (the dK / dV kernel starts its CTAs in that order)."""
+    from xattn_b200 import _native
+    dev = cuda_device
+    B, L = 3, 1000
+    gen = torch.Generator().manual_seed(3)
+    ids = torch.zeros(B, L, dtype=torch.int64)
+    for b in range(B):
+        pos, seg = 0, 0
+        while pos < L:
+            n = int(torch.randint(50, 400, (1,), generator=gen))
+            ids[b, pos:pos + n] = seg
+            pos += n
+            seg += 1
+    ids = ids.to(dev)
+    plan = _native.build_plan(B, L, L, dev, q_segment_idx=ids, k_segment_idx=ids).cpu()
+    n_tiles = (L + 127) // 128
+    r4 = (B * L + 3) // 4 * 4
+    off_kt = 2 * r4 + 4 * B * n_tiles
+    off_ko = off_kt + (2 * B * n_tiles + 3) // 4 * 4
+    k_tiles = plan[off_kt:off_kt + 2 * B * n_tiles].view(B * n_tiles, 2)
+    order = plan[off_ko:off_ko + B * n_tiles]
+    assert sorted(order.tolist()) == list(range(B * n_tiles))
+    work = (k_tiles[:, 1] - k_tiles[:, 0]).clamp_min(0)[order.long()]
+    assert bool((work[1:] <= work[:-1]).all())
+    assert int(work[0]) > int(work[-1])
