@@ -50,25 +50,28 @@ def forward(
     q: Tensor, k: Tensor, v: Tensor, support: Support, scale: float,
     prev_k: Optional[Tensor], prev_v: Optional[Tensor],
     q_segment_idx: Optional[Tensor], k_segment_idx: Optional[Tensor],
-    *, high_precision: bool = False, output_state: Optional[Tensor] = None,
-) -> Tuple[Tensor, Tensor]:
+    *, high_precision: bool = False, output_state: Optional[Tensor] = None, return_plan: bool = False,
+):
+    """(y, lse), and the mask plan too when asked for (the autograd path keeps it for the backward)."""
     k_all, v_all = concat_previous(k, v, prev_k, prev_v)
     plan = make_plan(q, k_all.shape[1], support, q_segment_idx, k_segment_idx)
-    return _native.attention_fwd(q, k_all, v_all, plan, scale, high_precision=high_precision,
-                                 output_state=output_state)
+    out = _native.attention_fwd(q, k_all, v_all, plan, scale, high_precision=high_precision,
+                                output_state=output_state)
+    return (*out, plan) if return_plan else out
 
 
 def backward(
     dy: Tensor, q: Tensor, k: Tensor, v: Tensor, y: Tensor, lse: Tensor, support: Support, scale: float,
     prev_k: Optional[Tensor], prev_v: Optional[Tensor],
     q_segment_idx: Optional[Tensor], k_segment_idx: Optional[Tensor],
-    *, high_precision: bool = False,
+    *, high_precision: bool = False, plan: Optional[Tensor] = None,
 ) -> Tuple[Tensor, Tensor, Tensor, Optional[Tensor], Optional[Tensor]]:
     """(dq, dk, dv, dprev_k, dprev_v).  At level 1 the saved ``y`` / ``lse`` are ignored and the
     statistics are recomputed with the high-precision softmax
     (xattn/ops/causal_flash_attn.py:144-147)."""
     k_all, v_all = concat_previous(k, v, prev_k, prev_v)
-    plan = make_plan(q, k_all.shape[1], support, q_segment_idx, k_segment_idx)
+    if plan is None:        # the autograd path hands over the forward's plan
+        plan = make_plan(q, k_all.shape[1], support, q_segment_idx, k_segment_idx)
     if high_precision:
         y, lse = _native.attention_fwd(q, k_all, v_all, plan, scale, high_precision=True)
     dq, dk_all, dv_all = _native.attention_bwd(dy, q, k_all, v_all, y, lse, plan, scale)
@@ -86,17 +89,17 @@ class AttentionFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, prev_k, prev_v, q_segment_idx, k_segment_idx, support, scale, level):
-        y, lse = forward(q, k, v, support, scale, prev_k, prev_v, q_segment_idx, k_segment_idx,
-                         high_precision=bool(level))
-        ctx.save_for_backward(q, k, v, y, lse, prev_k, prev_v, q_segment_idx, k_segment_idx)
+        y, lse, plan = forward(q, k, v, support, scale, prev_k, prev_v, q_segment_idx, k_segment_idx,
+                               high_precision=bool(level), return_plan=True)
+        ctx.save_for_backward(q, k, v, y, lse, prev_k, prev_v, q_segment_idx, k_segment_idx, plan)
         ctx.support, ctx.scale, ctx.level = support, scale, level
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        q, k, v, y, lse, prev_k, prev_v, q_seg, k_seg = ctx.saved_tensors
+        q, k, v, y, lse, prev_k, prev_v, q_seg, k_seg, plan = ctx.saved_tensors
         dq, dk, dv, dpk, dpv = backward(dy, q, k, v, y, lse, ctx.support, ctx.scale, prev_k, prev_v,
-                                        q_seg, k_seg, high_precision=bool(ctx.level))
+                                        q_seg, k_seg, high_precision=bool(ctx.level), plan=plan)
         return dq, dk, dv, dpk, dpv, None, None, None, None, None
 
 
