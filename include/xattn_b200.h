@@ -140,6 +140,23 @@ typedef struct {
 
 int xattn_b200_fwd(const XattnFwdArgs* args, xattn_stream_t stream);
 
+/* Forward for decode shapes: q_len * (q_heads / kv_heads) <= 128 with a power-of-two group size (one
+ * new token, or a few speculative ones, against a long key cache; the reference routes these through
+ * its packed route, xattn/ops/_bos_routing_heuristics.py:52-66, and the split scheduler of
+ * csrc/attention/hopper/tile_scheduler.hpp:55-101).  The query heads of a KV group share one tile, so K
+ * and V are read once per KV head, and the key tiles of a row are divided among `splits` CTAs whose
+ * normalised FP32 partial results (with their lse) a second kernel merges in split order.  Same
+ * arguments and results as xattn_b200_fwd; HBM-bound (K and V are streamed once).
+ *   xattn_b200_fwd_split_suggest  splits that fill `sm_count` SMs with one wave of CTAs, or 0 when the
+ *                                 shape does not qualify or xattn_b200_fwd is as good (short keys)
+ *   workspace                     splits * B * q_len * Hq * (V + 1) floats, 16-byte aligned        */
+int64_t xattn_b200_fwd_split_suggest(int64_t batch, int64_t q_len, int64_t k_len, int64_t q_heads,
+                                     int64_t kv_heads, int64_t sm_count);
+size_t xattn_b200_fwd_split_workspace_bytes(int64_t batch, int64_t q_len, int64_t q_heads, int64_t v_dim,
+                                            int64_t splits);
+int xattn_b200_fwd_split(const XattnFwdArgs* args, int64_t splits, void* workspace, size_t workspace_bytes,
+                         xattn_stream_t stream);
+
 /* ------------------------------------------------------------------------
  * Backward.  Replaces causal_flash_attn_bwd / flash_swa_bwd / flash_sca_bwd and
  * their strict-past, component and varlen forms (same files as the forward

@@ -101,6 +101,9 @@ SYMBOLS = {
     "xattn_b200_build_plan": (C.c_int, [C.POINTER(PlanArgs), C.c_void_p]),
     "xattn_b200_build_varlen_plan": (C.c_int, [C.POINTER(VarlenPlanArgs), C.c_void_p]),
     "xattn_b200_fwd": (C.c_int, [C.POINTER(FwdArgs), C.c_void_p]),
+    "xattn_b200_fwd_split_suggest": (C.c_int64, [C.c_int64] * 6),
+    "xattn_b200_fwd_split_workspace_bytes": (C.c_size_t, [C.c_int64] * 5),
+    "xattn_b200_fwd_split": (C.c_int, [C.POINTER(FwdArgs), C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p]),
     "xattn_b200_bwd_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
     "xattn_b200_bwd": (C.c_int, [C.POINTER(BwdArgs), C.c_void_p]),
     "xattn_b200_bwd_static_scratch": (C.c_int, [C.POINTER(BwdArgs), C.c_void_p]),

@@ -27,6 +27,7 @@ _SYNC_CHECK = os.environ.get("XATTN_B200_SYNC_CHECK", "0") == "1"
 
 class _DeviceState:
     def __init__(self, device: torch.device):
+        self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self.event: Optional[torch.cuda.Event] = None
@@ -192,8 +193,14 @@ def attention_fwd(
     *,
     high_precision: bool = False,
     output_state: Optional[Tensor] = None,
+    splits: Optional[int] = None,
 ) -> Tuple[Tensor, Tensor]:
-    """y [B,Lq,Hq,V] (input dtype), lse [B,Hq,Lq] fp32.  ``k``/``v`` already include previous K/V."""
+    """y [B,Lq,Hq,V] (input dtype), lse [B,Hq,Lq] fp32.  ``k``/``v`` already include previous K/V.
+
+    Decode shapes (a few query rows against many keys) take the split entry, which shares a tile among
+    the query heads of a KV group and divides the keys among CTAs; ``splits`` overrides the library's
+    choice (0: never split).
+    """
     lib = _lib.load()
     require_cuda(q, "xattn_b200 forward")
     q, k, v = tma_ready(q), tma_ready(k), tma_ready(v)
@@ -219,7 +226,15 @@ def attention_fwd(
     with torch.cuda.device(q.device):
         st = _pre_launch(q.device)
         args.status = st.status.data_ptr()
-        _lib.check(lib.xattn_b200_fwd(C.byref(args), _stream_ptr()), "xattn_b200_fwd")
+        if splits is None:
+            splits = int(lib.xattn_b200_fwd_split_suggest(B, Lq, Lk, Hq, Hkv, st.sm_count))
+        if splits > 0:
+            nbytes = int(lib.xattn_b200_fwd_split_workspace_bytes(B, Lq, Hq, V, splits))
+            workspace = torch.empty(nbytes // 4, dtype=torch.float32, device=q.device)
+            _lib.check(lib.xattn_b200_fwd_split(C.byref(args), splits, workspace.data_ptr(), nbytes, _stream_ptr()),
+                       "xattn_b200_fwd_split")
+        else:
+            _lib.check(lib.xattn_b200_fwd(C.byref(args), _stream_ptr()), "xattn_b200_fwd")
         _post_launch(st)
     return y, lse
 

@@ -4,6 +4,9 @@
 namespace xb {
 const char* last_error();
 int fwd_entry(const XattnFwdArgs* a, cudaStream_t stream);
+int fwd_split_entry(const XattnFwdArgs* a, int64_t splits, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+size_t fwd_split_workspace_bytes(int64_t batch, int64_t q_len, int64_t q_heads, int64_t v_dim, int64_t splits);
+int64_t fwd_split_suggest(int64_t batch, int64_t q_len, int64_t k_len, int64_t q_heads, int64_t kv_heads, int64_t sm_count);
 int bwd_entry(const XattnBwdArgs* a, cudaStream_t stream);
 int gate_fwd_entry(const XattnGateArgs* a, cudaStream_t stream);
 int gate_bwd_entry(const XattnGateArgs* a, cudaStream_t stream);
@@ -33,6 +36,21 @@ int xattn_b200_build_varlen_plan(const XattnVarlenPlanArgs* args, xattn_stream_t
 
 int xattn_b200_fwd(const XattnFwdArgs* args, xattn_stream_t stream) {
   return xb::fwd_entry(args, static_cast<cudaStream_t>(stream));
+}
+
+int64_t xattn_b200_fwd_split_suggest(int64_t batch, int64_t q_len, int64_t k_len, int64_t q_heads,
+                                     int64_t kv_heads, int64_t sm_count) {
+  return xb::fwd_split_suggest(batch, q_len, k_len, q_heads, kv_heads, sm_count);
+}
+
+size_t xattn_b200_fwd_split_workspace_bytes(int64_t batch, int64_t q_len, int64_t q_heads, int64_t v_dim,
+                                            int64_t splits) {
+  return xb::fwd_split_workspace_bytes(batch, q_len, q_heads, v_dim, splits);
+}
+
+int xattn_b200_fwd_split(const XattnFwdArgs* args, int64_t splits, void* workspace, size_t workspace_bytes,
+                         xattn_stream_t stream) {
+  return xb::fwd_split_entry(args, splits, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 size_t xattn_b200_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len) {

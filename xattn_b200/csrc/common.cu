@@ -33,7 +33,7 @@ TensorMapEncodeFn tensor_map_encoder() {
 }
 
 int make_tile_map(CUtensorMap* out, const void* base, int dtype, int64_t B, int64_t L, int64_t H, int64_t D,
-                  int64_t sb, int64_t sl, int64_t sh, int box_rows) {
+                  int64_t sb, int64_t sl, int64_t sh, int box_rows, int box_heads) {
   TensorMapEncodeFn enc = tensor_map_encoder();
   if (!enc) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return -1; }
   if (reinterpret_cast<uintptr_t>(base) & 15) { set_error("tensor base must be 16-byte aligned"); return -1; }
@@ -48,7 +48,7 @@ int make_tile_map(CUtensorMap* out, const void* base, int dtype, int64_t B, int6
   }
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)L, (cuuint64_t)B};
   cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)sl * 2, (cuuint64_t)sb * 2};
-  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_heads, (cuuint32_t)box_rows, 1};
   cuuint32_t elem[4] = {1, 1, 1, 1};
   const CUtensorMapDataType dt = dtype == XATTN_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = enc(out, dt, 4, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,

@@ -57,10 +57,10 @@ typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint3
 TensorMapEncodeFn tensor_map_encoder();
 
 // Map over a [B, L, H, D] tensor with element strides (sb, sl, sh, 1) of 16-bit
-// elements; box = 64 elements of D x `box_rows` rows of L, 128-byte swizzle.
-// Returns 0 on success.
+// elements; box = 64 elements of D x `box_heads` heads x `box_rows` rows of L (in shared memory the
+// heads of one row lie next to each other), 128-byte swizzle.  Returns 0 on success.
 int make_tile_map(CUtensorMap* out, const void* base, int dtype, int64_t B, int64_t L, int64_t H, int64_t D,
-                  int64_t sb, int64_t sl, int64_t sh, int box_rows);
+                  int64_t sb, int64_t sl, int64_t sh, int box_rows, int box_heads = 1);
 // Tensor map over a contiguous [B][H][L][16] bf16 tensor (32-byte rows): boxes of `box_rows` rows of
 // one (batch, head), written to shared memory in the 32-byte-swizzle K-major layout.
 // Coordinates: (0, row, head, batch).

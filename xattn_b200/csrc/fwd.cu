@@ -44,6 +44,12 @@ struct FwdParams {
   float* lse;             // [B][Hq][Lq]
   float* y_state;         // optional fp32 copy of y
   int* status;
+  // decode shape only (template flag DEC): the query heads of a KV group share the tile, the key
+  // tiles are divided among `splits` CTAs per (batch, KV head), partial results go to the workspace
+  int splits;
+  int g_shift;            // log2 of the group size Hq / Hkv
+  float* part_y;          // [splits][B][Lq][Hq][V], normalised per split
+  float* part_lse;        // [splits][B][Hq][Lq], natural log; -inf where the split saw no key
 };
 
 template <int HD>
@@ -70,10 +76,14 @@ struct FwdSmem {
 
 // T: __nv_bfloat16 or __half.  HD: padded head dimension of the shared-memory tiles (64, 128 or 256).
 // HP: high-precision softmax.
+// DEC: decode shape, Lq * (Hq / Hkv) <= 128.  Tile row r holds query row r / G of head kvh * G + r % G
+// (one TMA box over G heads), so K and V are read once per KV head instead of once per query head; the
+// CTA takes one share of the key tiles and writes a normalised FP32 partial result with its lse, which
+// fwd_combine_kernel merges.  Everything between the Q load and the epilogue is the same code.
 constexpr int kFwdParts = XB_FWD_PARTS;                 // softmax warpgroups
 constexpr int kFwdThreads = (4 * kFwdParts + 8) * 32;   // + correction warpgroup + issuers / TMA
 
-template <typename T, int HD, bool HP>
+template <typename T, int HD, bool HP, bool DEC>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_y, const FwdParams p) {
@@ -100,13 +110,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
   // ---- which work item -----------------------------------------------------
   const int G = p.Hq / p.Hkv;
-  const int per_bk = p.nQT * G;
+  const int per_bk = DEC ? p.splits : p.nQT * G;
   const int bk = blockIdx.x / per_bk;
   const int rem = blockIdx.x - bk * per_bk;
-  const int qt = p.nQT - 1 - rem / G;                 // later (heavier under causal masks) tiles first
+  const int qt = DEC ? 0 : p.nQT - 1 - rem / G;       // later (heavier under causal masks) tiles first
   const int kvh = bk % p.Hkv;
-  const int h = kvh * G + (rem % G);
+  const int h = DEC ? kvh * G : kvh * G + (rem % G);  // DEC: first head of the group
   const int b = bk / p.Hkv;
+  const int split = DEC ? rem : 0;
 
   if (warp == kTmaWarp && lane == 0) {
     // The Q tile needs nothing but the block index: its load starts before anything else, the mask
@@ -130,6 +141,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       full_lo = ti.max_lo;
       full_hi = ti.min_hi;
     }
+  }
+  if (DEC) {
+    // this CTA's share of the key tiles (possibly none)
+    const int per = (n_hi - n_lo + p.splits - 1) / p.splits;
+    n_lo = min(n_lo + split * per, n_hi);
+    n_hi = min(n_lo + per, n_hi);
   }
   const int iters = n_hi - n_lo;
 
@@ -186,7 +203,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // =========================== softmax warpgroups ===========================
     const int hf = warp >> 2;                   // which part of the key-tile columns
     const int r = tid & 127;
-    const int row = qt * kBlockM + r;
+    const int row = DEC ? (r >> p.g_shift) : qt * kBlockM + r;
     int lo = 0, hi = 0;
     if (row < p.Lq) {
       lo = p.row_lo[(size_t)b * p.Lq + row];
@@ -329,7 +346,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   } else if (warp < kCorrWarp + 4) {
     // ======================= correction + epilogue warpgroup =======================
     const int r = tid & 127;
-    const int row = qt * kBlockM + r;
+    const int row = DEC ? (r >> p.g_shift) : qt * kBlockM + r;
+    const int hr = DEC ? h + (r & (G - 1)) : h;       // this row's query head
     const bool live = row < p.Lq;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
@@ -370,7 +388,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       if (has) inv = HP ? __frcp_rn(l) : __fdividef(1.f, l);
       if (live) {
         const float c_log2 = p.scale * 1.4426950408889634f;
-        p.lse[((size_t)b * p.Hq + h) * p.Lq + row] =
+        float* lse_out = DEC ? p.part_lse + (size_t)split * p.B * p.Hq * p.Lq : p.lse;
+        lse_out[((size_t)b * p.Hq + hr) * p.Lq + row] =
             has ? (m * c_log2 + log2f(l)) * 0.6931471805599453f : -INFINITY;
       }
       // y leaves through shared memory and bulk tensor stores (the Q tile's buffer is free by now:
@@ -378,7 +397,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       // does not have to wait for the writes themselves.  Layout: 64-column boxes of 128-byte
       // rows in the 128-byte swizzle (16-byte chunk c of row r sits at chunk c ^ (r & 7)).
       const uint32_t t_o = tmem + lane_off + cO;
-      float* ys_row = p.y_state ? p.y_state + (((size_t)b * p.Lq + (live ? row : 0)) * p.Hq + h) * p.V : nullptr;
+      float* ys_base = DEC ? p.part_y + (size_t)split * p.B * p.Lq * p.Hq * p.V : p.y_state;
+      float* ys_row = ys_base ? ys_base + (((size_t)b * p.Lq + (live ? row : 0)) * p.Hq + hr) * p.V : nullptr;
       for (int c0 = 0; c0 < v_pad; c0 += 32) {
         uint32_t o[32];
         if (iters > 0) {
@@ -400,7 +420,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           pk.z = Pack2<T>::pack(f[4], f[5]);
           pk.w = Pack2<T>::pack(f[6], f[7]);
           const int chunk = ((c0 & 63) + c) >> 3;
-          *reinterpret_cast<uint4*>(box + ((chunk ^ (r & 7)) << 4)) = pk;
+          if (!DEC) *reinterpret_cast<uint4*>(box + ((chunk ^ (r & 7)) << 4)) = pk;
           if (ys_row && live && c0 + c < p.V) {
             *reinterpret_cast<float4*>(ys_row + c0 + c) = make_float4(f[0], f[1], f[2], f[3]);
             *reinterpret_cast<float4*>(ys_row + c0 + c + 4) = make_float4(f[4], f[5], f[6], f[7]);
@@ -409,7 +429,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
       fence_proxy_async_smem();
       mbar_arrive_warp(&s.y_staged);
-      if (warp == kCorrWarp && lane == 0) {
+      if (!DEC && warp == kCorrWarp && lane == 0) {
         ok = mbar_wait(ctx, &s.y_staged, 0, 27);
         if (ok) {
           for (int bx = 0; bx < nbox_v; ++bx) tma_store_4d(&tm_y, s.q + bx * kBoxBytes, bx * 64, h, qt * kBlockM, b);
@@ -507,15 +527,74 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   }
 }
 
+// Merges the partial results of the decode-shape kernel: one warp per (batch, query row, head).
+// lse = log sum_s exp(lse_s), y = sum_s exp(lse_s - lse) y_s, in split order (repeatable); a row no
+// split saw a key for gives y = 0 and lse = -inf.  HBM-bound: reads splits * (V + 1) floats per row.
+template <typename T>
+__global__ void __launch_bounds__(128)
+fwd_combine_kernel(const FwdParams p) {
+  const long long units = (long long)p.B * p.Lq * p.Hq;
+  const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (unit >= units) return;
+  const int lane = threadIdx.x & 31;
+  const int h = (int)(unit % p.Hq);
+  const long long br = unit / p.Hq;
+  const int row = (int)(br % p.Lq);
+  const int b = (int)(br / p.Lq);
+  const size_t lse_idx = ((size_t)b * p.Hq + h) * p.Lq + row;
+  const size_t lse_stride = (size_t)p.B * p.Hq * p.Lq;
+  const size_t y_stride = (size_t)units * p.V;
+  float mx = -INFINITY;
+  for (int sp = lane; sp < p.splits; sp += 32) mx = fmaxf(mx, p.part_lse[sp * lse_stride + lse_idx]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+  if (mx != -INFINITY)
+    for (int sp = lane; sp < p.splits; sp += 32) sum += expf(p.part_lse[sp * lse_stride + lse_idx] - mx);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float lse = mx == -INFINITY ? -INFINITY : mx + logf(sum);
+  float2 acc[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};   // columns 2 * lane + 64 * i
+  if (mx != -INFINITY) {
+    for (int sp = 0; sp < p.splits; ++sp) {
+      const float ls = p.part_lse[sp * lse_stride + lse_idx];
+      if (ls == -INFINITY) continue;
+      const float w = expf(ls - lse);
+      const float* src = p.part_y + sp * y_stride + (size_t)unit * p.V;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int c = 2 * lane + 64 * i;
+        if (c < p.V) {
+          const float2 x = *reinterpret_cast<const float2*>(src + c);
+          acc[i].x += w * x.x;
+          acc[i].y += w * x.y;
+        }
+      }
+    }
+  }
+  if (lane == 0) p.lse[lse_idx] = lse;
+  T* y = reinterpret_cast<T*>(p.y) + (size_t)unit * p.V;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = 2 * lane + 64 * i;
+    if (c < p.V) {
+      *reinterpret_cast<uint32_t*>(y + c) = Pack2<T>::pack(acc[i].x, acc[i].y);
+      if (p.y_state) *reinterpret_cast<float2*>(p.y_state + (size_t)unit * p.V + c) = acc[i];
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
-template <typename T, int HD, bool HP>
+template <typename T, int HD, bool HP, bool DEC>
 static int launch_fwd(const XattnFwdArgs& a, const FwdParams& p, cudaStream_t stream) {
   using Smem = FwdSmem<HD>;
   CUtensorMap tq, tk, tv;
+  const int group = p.Hq / p.Hkv;
+  // decode shape: one box takes the G heads of a KV group x 128 / G query rows
   if (make_tile_map(&tq, a.q, a.dtype, a.batch, a.q_len, a.q_heads, a.qk_dim, a.q_strides[0], a.q_strides[1],
-                    a.q_strides[2], kBlockM)) return XATTN_E_INVALID;
+                    a.q_strides[2], DEC ? kBlockM / group : kBlockM, DEC ? group : 1)) return XATTN_E_INVALID;
   if (make_tile_map(&tk, a.k, a.dtype, a.batch, a.k_len, a.kv_heads, a.qk_dim, a.k_strides[0], a.k_strides[1],
                     a.k_strides[2], kBlockN)) return XATTN_E_INVALID;
   if (make_tile_map(&tv, a.v, a.dtype, a.batch, a.k_len, a.kv_heads, a.v_dim, a.v_strides[0], a.v_strides[1],
@@ -524,29 +603,43 @@ static int launch_fwd(const XattnFwdArgs& a, const FwdParams& p, cudaStream_t st
   if (make_tile_map(&ty, a.y, a.dtype, a.batch, a.q_len, a.q_heads, a.v_dim, a.q_len * a.q_heads * a.v_dim,
                     a.q_heads * a.v_dim, a.v_dim, kBlockM)) return XATTN_E_INVALID;
   const size_t smem = sizeof(Smem) + 1024;
-  auto kern = fwd_kernel<T, HD, HP>;
+  auto kern = fwd_kernel<T, HD, HP, DEC>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_error("cudaFuncSetAttribute(fwd): %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
-  const long long grid = (long long)p.nQT * p.Hq * p.B;
+  const long long grid = DEC ? (long long)p.splits * p.Hkv * p.B : (long long)p.nQT * p.Hq * p.B;
   if (grid <= 0 || grid > 0x7fffffffLL) { set_error("forward grid out of range"); return XATTN_E_INVALID; }
   {
     ProfileScope prof(kProfFwd, stream);
     kern<<<(unsigned)grid, kFwdThreads, smem, stream>>>(tq, tk, tv, ty, p);
+    if (DEC) {
+      const long long units = (long long)p.B * p.Lq * p.Hq;
+      fwd_combine_kernel<T><<<(unsigned)((units + 3) / 4), 128, 0, stream>>>(p);
+    }
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("forward launch: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
   return XATTN_OK;
 }
 
-template <typename T, bool HP>
+template <typename T, bool HP, bool DEC>
 static int dispatch_fwd_dim(const XattnFwdArgs& a, const FwdParams& p, cudaStream_t stream) {
   const int hd = (int)(a.qk_dim > a.v_dim ? a.qk_dim : a.v_dim);
-  if (hd <= 64) return launch_fwd<T, 64, HP>(a, p, stream);
-  if (hd <= 128) return launch_fwd<T, 128, HP>(a, p, stream);
-  return launch_fwd<T, 256, HP>(a, p, stream);
+  if (hd <= 64) return launch_fwd<T, 64, HP, DEC>(a, p, stream);
+  if (hd <= 128) return launch_fwd<T, 128, HP, DEC>(a, p, stream);
+  return launch_fwd<T, 256, HP, DEC>(a, p, stream);
 }
 
-int fwd_entry(const XattnFwdArgs* a, cudaStream_t stream) {
+template <bool DEC>
+static int dispatch_fwd(const XattnFwdArgs& a, const FwdParams& p, cudaStream_t stream) {
+  if (a.dtype == XATTN_DTYPE_BF16) {
+    return a.high_precision ? dispatch_fwd_dim<__nv_bfloat16, true, DEC>(a, p, stream)
+                            : dispatch_fwd_dim<__nv_bfloat16, false, DEC>(a, p, stream);
+  }
+  return a.high_precision ? dispatch_fwd_dim<__half, true, DEC>(a, p, stream)
+                          : dispatch_fwd_dim<__half, false, DEC>(a, p, stream);
+}
+
+static int check_fwd_args(const XattnFwdArgs* a, FwdParams& p) {
   if (!a) { set_error("null arguments"); return XATTN_E_INVALID; }
   if (a->dtype != XATTN_DTYPE_F16 && a->dtype != XATTN_DTYPE_BF16) { set_error("Q/K/V dtype must be fp16 or bf16"); return XATTN_E_INVALID; }
   if (a->batch <= 0 || a->q_len <= 0 || a->k_len <= 0 || a->q_heads <= 0 || a->kv_heads <= 0 ||
@@ -559,7 +652,6 @@ int fwd_entry(const XattnFwdArgs* a, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(a->y) & 15) || (a->y_state && (reinterpret_cast<uintptr_t>(a->y_state) & 15))) {
     set_error("y must be 16-byte aligned"); return XATTN_E_INVALID;
   }
-  FwdParams p;
   p.B = (int)a->batch; p.Lq = (int)a->q_len; p.Lk = (int)a->k_len; p.Hq = (int)a->q_heads; p.Hkv = (int)a->kv_heads;
   p.D = (int)a->qk_dim; p.V = (int)a->v_dim;
   p.nQT = ceil_div(p.Lq, kBlockM);
@@ -569,12 +661,63 @@ int fwd_entry(const XattnFwdArgs* a, cudaStream_t stream) {
   p.row_hi = a->plan + pl.off_hi;
   p.q_tiles = reinterpret_cast<const TileInfo*>(a->plan + pl.off_qt);
   p.y = a->y; p.lse = a->lse; p.y_state = a->y_state; p.status = a->status;
-  if (a->dtype == XATTN_DTYPE_BF16) {
-    return a->high_precision ? dispatch_fwd_dim<__nv_bfloat16, true>(*a, p, stream)
-                             : dispatch_fwd_dim<__nv_bfloat16, false>(*a, p, stream);
+  p.splits = 1; p.g_shift = 0; p.part_y = nullptr; p.part_lse = nullptr;
+  return XATTN_OK;
+}
+
+int fwd_entry(const XattnFwdArgs* a, cudaStream_t stream) {
+  FwdParams p;
+  const int rc = check_fwd_args(a, p);
+  if (rc != XATTN_OK) return rc;
+  return dispatch_fwd<false>(*a, p, stream);
+}
+
+// Decode shapes qualify when the G = Hq / Hkv heads of a group times the query rows fit one tile.
+static bool split_shape_ok(int64_t q_len, int64_t q_heads, int64_t kv_heads) {
+  if (q_len <= 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads) return false;
+  const int64_t g = q_heads / kv_heads;
+  return g <= kBlockM && (g & (g - 1)) == 0 && q_len * g <= kBlockM;
+}
+
+size_t fwd_split_workspace_bytes(int64_t batch, int64_t q_len, int64_t q_heads, int64_t v_dim, int64_t splits) {
+  if (batch <= 0 || q_len <= 0 || q_heads <= 0 || v_dim <= 0 || splits <= 0) return 0;
+  return (size_t)splits * batch * q_len * q_heads * (v_dim + 1) * sizeof(float);
+}
+
+int64_t fwd_split_suggest(int64_t batch, int64_t q_len, int64_t k_len, int64_t q_heads, int64_t kv_heads,
+                          int64_t sm_count) {
+  if (batch <= 0 || k_len <= 0 || sm_count <= 0 || !split_shape_ok(q_len, q_heads, kv_heads)) return 0;
+  const int64_t nkt = (k_len + kBlockN - 1) / kBlockN;
+  if (nkt < 4) return 0;                        // nothing to stream: the general kernel is as good
+  int64_t splits = sm_count / (batch * kv_heads);  // one wave of CTAs
+  if (splits > nkt / 2) splits = nkt / 2;          // at least two key tiles per CTA
+  if (splits < 1) splits = 1;
+  if (splits > 256) splits = 256;
+  if (splits == 1 && q_heads == kv_heads) return 0;   // neither heads to share nor keys to divide
+  return splits;
+}
+
+int fwd_split_entry(const XattnFwdArgs* a, int64_t splits, void* workspace, size_t workspace_bytes,
+                    cudaStream_t stream) {
+  FwdParams p;
+  const int rc = check_fwd_args(a, p);
+  if (rc != XATTN_OK) return rc;
+  if (!split_shape_ok(a->q_len, a->q_heads, a->kv_heads)) {
+    set_error("split forward needs q_len * (q_heads / kv_heads) <= 128 with a power-of-two group size");
+    return XATTN_E_INVALID;
   }
-  return a->high_precision ? dispatch_fwd_dim<__half, true>(*a, p, stream)
-                           : dispatch_fwd_dim<__half, false>(*a, p, stream);
+  if (splits < 1 || splits > 256) { set_error("splits must be in [1, 256]"); return XATTN_E_INVALID; }
+  const size_t need = fwd_split_workspace_bytes(a->batch, a->q_len, a->q_heads, a->v_dim, splits);
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15) || workspace_bytes < need) {
+    set_error("split forward workspace must be 16-byte aligned and hold %zu bytes", need);
+    return XATTN_E_INVALID;
+  }
+  p.splits = (int)splits;
+  int g = p.Hq / p.Hkv;
+  while (g > 1) { ++p.g_shift; g >>= 1; }
+  p.part_y = static_cast<float*>(workspace);
+  p.part_lse = p.part_y + (size_t)splits * p.B * p.Lq * p.Hq * p.V;
+  return dispatch_fwd<true>(*a, p, stream);
 }
 
 }  // namespace xb
