@@ -59,6 +59,10 @@ WORKLOADS = {
     # window-sized K/V halo from its predecessor
     "swa_c3": dict(B=1, S=32768, Hq=32, Hkv=8, D=128, segments=False, window=4096,
                    text="configs[2]: sliding-window fwd+bwd bf16 B=1 S=32768 Hq=32 Hkv=8 D=128 window=4096, sequence-sharded with KV halo exchange"),
+    # one new token per sequence against a long key cache: forward only, HBM-bound (K and V are
+    # streamed once); reported in GB/s of K + V + q + y bytes, not in the headline metric
+    "decode": dict(B=8, S=32768, Hq=32, Hkv=8, D=128, segments=False, decode=True,
+                   text="decode: causal forward bf16 GQA B=8 Lq=1 Lk=32768 Hq=32 Hkv=8 D=128 (1.07 GB of K and V per step, above L2)"),
 }
 
 
@@ -209,6 +213,8 @@ def run_ours(args, w):
 
     if "window" in w:
         return run_swa_sharded(args, w, world, rank, dev)
+    if w.get("decode"):
+        return run_decode(args, w, world, rank, dev)
     host = make_host_inputs(w, seed=1 + rank)
     pinned = [None if t is None else t.pin_memory() for t in host]
     q, k, v, dy, ids = (None if t is None else t.to(dev) for t in pinned)
@@ -370,6 +376,70 @@ def run_ours(args, w):
         dist.destroy_process_group()
 
 
+def run_decode(args, w, world, rank, dev):
+    """Forward of Lq = 1 against Lk = S keys per sequence; every rank runs its own batch."""
+    import torch.distributed as dist
+    import xattn_b200 as xattn
+    from xattn_b200 import _native
+
+    B, S, Hq, Hkv, D = w["B"], w["S"], w["Hq"], w["Hkv"], w["D"]
+    gen = torch.Generator().manual_seed(7 + rank)
+    q = torch.randn(B, 1, Hq, D, generator=gen).to(dev, torch.bfloat16)
+    k = torch.randn(B, S, Hkv, D, generator=gen).to(dev, torch.bfloat16)
+    v = torch.randn(B, S, Hkv, D, generator=gen).to(dev, torch.bfloat16)
+    # algorithmic bytes of one step: K and V read once, q read, y and lse written
+    nbytes = (k.numel() + v.numel() + 2 * q.numel()) * 2 + B * Hq * 4
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        xattn.causal_flash_attn_fwd(q, k, v)
+    _native.check_status()
+    sampler = ClockSampler(dev.index)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    _native.profile_enable(True)
+    e0.record()
+    for _ in range(args.steps):
+        xattn.causal_flash_attn_fwd(q, k, v)
+    e1.record()
+    barrier()
+    _native.profile_enable(False)
+    records = _native.profile_read()
+    clocks = sampler.stop()
+    _native.check_status()
+    times = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_step = float(times[0])
+    if rank == 0:
+        peaks, peak_src = measured_peaks()
+        fwd = [ms for kind, ms in records if kind == "fwd"]      # split kernel + merge kernel
+        kernel_ms = sum(fwd) / max(len(fwd), 1)
+        peak = float(peaks["hbm_gbs"])
+        achieved = nbytes / kernel_ms * 1e-6
+        print(json.dumps({
+            "metric": "decode attention forward, GB/s of K and V streamed, whole job", "value": world * nbytes / ms_step * 1e-6,
+            "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["text"], "l2": "K and V (1.07 GB per step) exceed the 126 MB L2",
+                       "bytes_per_step": nbytes, "parallelism": f"batch sharded over {world} GPU(s), no communication"},
+            "gpu_launches": 2 * len(fwd) + 3 * len([1 for kind, _ in records if kind == "plan"]),
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "fwd (decode shape) + merge", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": f"{peak_src} hbm_gbs (copy bandwidth)"},
+            "kernel_ms": kernel_ms,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_swa_sharded(args, w, world, rank, dev):
     """configs[2]: one sequence of S tokens split contiguously over the ranks; total work is fixed."""
     import torch.distributed as dist
@@ -489,7 +559,10 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
-    if args.impl == "reference":
+    if args.impl == "reference" and w.get("decode"):
+        print(json.dumps({"impl": "reference", "unavailable": "the decode workload is a side measurement of the "
+                          "split forward; the reference arm runs the fwd+bwd workloads"}))
+    elif args.impl == "reference":
         run_reference(args, w)
     else:
         run_ours(args, w)

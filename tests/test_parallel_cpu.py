@@ -89,9 +89,9 @@ def _worker(rank, world, port, mode, results):
         k = torch.randn(B, L, Hkv, D, dtype=torch.float64)
         v = torch.randn(B, L, Hkv, D, dtype=torch.float64)
         dy = torch.randn(B, L, Hq, D, dtype=torch.float64)
-        ids = (torch.arange(L) // 19).expand(B, -1).contiguous() if mode != "ring" else None
+        ids = (torch.arange(L) // 19).expand(B, -1).contiguous() if mode in ("swa", "sca") else None
         n = L // world
-        sl = slice(rank * n, (rank + 1) * n)
+        sl = P.zigzag_indices(L, rank, world) if mode == "zigzag" else slice(rank * n, (rank + 1) * n)
         ql, kl, vl = (t[:, sl].clone().requires_grad_() for t in (q, k, v))
         if mode == "swa":
             y = P.sequence_parallel_flash_swa(ql, kl, vl, 7, segment_idx=ids[:, sl], op=_oracle_op("window"))
@@ -100,7 +100,8 @@ def _worker(rank, world, port, mode, results):
             y = P.sequence_parallel_flash_sca(ql, kl, vl, 8, segment_idx=ids[:, sl], op=_oracle_op("chunk"))
             full = dict(visibility="chunk", span=8)
         else:
-            y = P.ring_causal_flash_attn(ql, kl, vl, kernels=_OracleBlocks)
+            y = P.ring_causal_flash_attn(ql, kl, vl, kernels=_OracleBlocks,
+                                         layout="zigzag" if mode == "zigzag" else "contiguous")
             full = dict(visibility="full")
         grads = torch.autograd.grad(y, (ql, kl, vl), dy[:, sl])
         ref_leaves = [t.clone().requires_grad_() for t in (q, k, v)]
@@ -113,7 +114,7 @@ def _worker(rank, world, port, mode, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ("swa", "sca", "ring"))
+@pytest.mark.parametrize("mode", ("swa", "sca", "ring", "zigzag"))
 @pytest.mark.parametrize("world", (2, 3))
 def test_sequence_sharding_matches_unsharded_oracle(mode, world):
     if mode == "sca" and world == 3:

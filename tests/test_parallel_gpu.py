@@ -36,6 +36,8 @@ def _worker(rank, world, port, mode, results):
         ids = (torch.arange(L, device=dev) // 1500).expand(B, -1).contiguous() if mode != "ring" else None
         n = L // world
         sl = slice(rank * n, (rank + 1) * n)
+        if mode == "zigzag":
+            sl = P.zigzag_indices(L, rank, world).to(dev)
         ql, kl, vl = (t[:, sl].clone().requires_grad_() for t in (q, k, v))
         qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
         if mode == "swa":
@@ -56,7 +58,7 @@ def _worker(rank, world, port, mode, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ("swa", "sca", "ring"))
+@pytest.mark.parametrize("mode", ("swa", "sca", "ring", "zigzag"))
 def test_sharded_matches_single_gpu(mode, cuda_device):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:

@@ -10,7 +10,10 @@ sequence-parallel run needs, and this module plugs communication into it:
 * causal attention: a ring.  At step ``t`` rank ``r`` reads the K/V block of rank ``r-t`` (diagonal
   block causal, earlier blocks unmasked, later blocks skipped), merges the partial outputs by their
   log-sum-exp, and prefetches the next block while computing.  The backward sends each block's dK / dV
-  home.
+  home.  With contiguous slices rank ``r`` has ``r + 1`` blocks of work; the ``zigzag`` layout (rank ``r``
+  holds chunks ``r`` and ``2R-1-r`` of ``2R``) gives every rank the same work at every step: an earlier
+  rank's block is seen by all local rows through its first chunk only, a later rank's block is seen
+  whole by the local second chunk only, both unmasked.
 
 Batch x heads sharding needs no code: ranks run independent batches.
 
@@ -181,10 +184,30 @@ def _merge(acc: Optional[Tuple[Tensor, Tensor]], y: Tensor, lse: Tensor) -> Tupl
     return y0 * w0 + y * w1, new
 
 
+def zigzag_indices(length: int, rank: int, world: int) -> Tensor:
+    """Positions of the full sequence that rank ``rank`` holds in the zig-zag layout: chunks ``rank`` and
+    ``2 * world - 1 - rank`` of ``2 * world`` equal chunks, in order."""
+    if length % (2 * world):
+        raise ValueError("the zig-zag layout needs a sequence length that is a multiple of 2 * world size")
+    c = length // (2 * world)
+    return torch.cat((torch.arange(rank * c, (rank + 1) * c),
+                      torch.arange((2 * world - 1 - rank) * c, (2 * world - rank) * c)))
+
+
+def _merge_rows(acc: Tuple[Tensor, Tensor], y: Tensor, lse: Tensor, start: int) -> Tuple[Tensor, Tensor]:
+    """Merge a partial result that covers the rows from ``start`` on."""
+    y0, l0 = acc
+    ya, la = _merge((y0[:, start:], l0[:, :, start:]), y, lse)
+    y0[:, start:] = ya
+    l0[:, :, start:] = la
+    return y0, l0
+
+
 class _RingCausal(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q: Tensor, k: Tensor, v: Tensor, scale: float, group, kernels):
+    def forward(ctx, q: Tensor, k: Tensor, v: Tensor, scale: float, group, kernels, zigzag: bool = False):
         rank, world = _world(group)
+        half = q.shape[1] // 2
         send_to, recv_from = (rank + 1) % world, (rank - 1) % world
         blk_k, blk_v = k.contiguous(), v.contiguous()
         acc = None
@@ -199,7 +222,14 @@ class _RingCausal(torch.autograd.Function):
                        dist.P2POp(dist.isend, blk_v, _global_rank(group, send_to), group),
                        dist.P2POp(dist.irecv, nxt_v, _global_rank(group, recv_from), group)]
                 pending = dist.batch_isend_irecv(ops)
-            if t <= rank:   # the block of rank (rank - t): on or below the diagonal
+            if zigzag and t > 0:
+                if t <= rank:   # an earlier rank's block: its first chunk lies before both local chunks
+                    y_t, lse_t = kernels.forward(q, blk_k[:, :half], blk_v[:, :half], scale, causal=False)
+                    acc = _merge(acc, y_t, lse_t)
+                else:           # a later rank's block: both of its chunks lie between the local ones
+                    y_t, lse_t = kernels.forward(q[:, half:], blk_k, blk_v, scale, causal=False)
+                    acc = _merge_rows(acc, y_t, lse_t, half)
+            elif t <= rank:     # the block of rank (rank - t): on or below the diagonal
                 y_t, lse_t = kernels.forward(q, blk_k, blk_v, scale, causal=(t == 0))
                 acc = _merge(acc, y_t, lse_t)
             for work in pending:
@@ -209,7 +239,7 @@ class _RingCausal(torch.autograd.Function):
         y32, lse = acc
         y = y32.to(q.dtype)
         ctx.save_for_backward(q, k, v, y, lse)
-        ctx.scale, ctx.group, ctx.kernels = scale, group, kernels
+        ctx.scale, ctx.group, ctx.kernels, ctx.zigzag = scale, group, kernels, zigzag
         return y
 
     @staticmethod
@@ -217,6 +247,7 @@ class _RingCausal(torch.autograd.Function):
         q, k, v, y, lse = ctx.saved_tensors
         group, kernels, scale = ctx.group, ctx.kernels, ctx.scale
         rank, world = _world(group)
+        zigzag, half = ctx.zigzag, q.shape[1] // 2
         send_to, recv_from = (rank + 1) % world, (rank - 1) % world
         dy = dy.contiguous()
         blk_k, blk_v = k.contiguous(), v.contiguous()
@@ -227,7 +258,20 @@ class _RingCausal(torch.autograd.Function):
         dv_acc = torch.zeros(v.shape, dtype=wide, device=v.device)
         dq = torch.zeros(q.shape, dtype=wide, device=q.device)
         for t in range(world):
-            if t <= rank:
+            if zigzag and t > 0:
+                if t <= rank:
+                    dq_t, dk_t, dv_t = kernels.backward(dy, q, blk_k[:, :half], blk_v[:, :half], y, lse, scale,
+                                                        causal=False)
+                    dq += dq_t.to(wide)
+                    dk_acc[:, :half] += dk_t.to(wide)
+                    dv_acc[:, :half] += dv_t.to(wide)
+                else:
+                    dq_t, dk_t, dv_t = kernels.backward(dy[:, half:], q[:, half:], blk_k, blk_v, y[:, half:],
+                                                        lse[:, :, half:], scale, causal=False)
+                    dq[:, half:] += dq_t.to(wide)
+                    dk_acc += dk_t.to(wide)
+                    dv_acc += dv_t.to(wide)
+            elif t <= rank:
                 dq_t, dk_t, dv_t = kernels.backward(dy, q, blk_k, blk_v, y, lse, scale, causal=(t == 0))
                 dq += dq_t.to(wide)
                 dk_acc += dk_t.to(wide)
@@ -242,14 +286,22 @@ class _RingCausal(torch.autograd.Function):
             for work in dist.batch_isend_irecv(ops):
                 work.wait()
             blk_k, blk_v, dk_acc, dv_acc = recv
-        return dq.to(q.dtype), dk_acc.to(k.dtype), dv_acc.to(v.dtype), None, None, None
+        return dq.to(q.dtype), dk_acc.to(k.dtype), dv_acc.to(v.dtype), None, None, None, None
 
 
 def ring_causal_flash_attn(q: Tensor, k: Tensor, v: Tensor, scale: Optional[float] = None, *, group=None,
-                           kernels=None) -> Tensor:
-    """Causal attention over a sequence split contiguously across ranks (equal slice lengths, no
-    segment metadata): ring of K/V blocks, partial outputs merged by log-sum-exp, differentiable."""
+                           kernels=None, layout: str = "contiguous") -> Tensor:
+    """Causal attention over a sequence split across ranks (equal slice lengths, no segment metadata):
+    ring of K/V blocks, partial outputs merged by log-sum-exp, differentiable.
+
+    ``layout="contiguous"``: rank r holds positions [r * n, (r + 1) * n).  ``layout="zigzag"``: rank r holds
+    the positions ``zigzag_indices(length, r, world)`` (an even slice length), which balances the causal
+    work: every rank computes half a block at every step."""
     if q.shape[1] != k.shape[1]:
         raise ValueError("ring attention needs equal query and key slice lengths")
+    if layout not in ("contiguous", "zigzag"):
+        raise ValueError("layout must be 'contiguous' or 'zigzag'")
+    if layout == "zigzag" and q.shape[1] % 2:
+        raise ValueError("the zig-zag layout needs an even slice length")
     s = float(scale) if scale is not None else q.shape[-1] ** -0.5
-    return _RingCausal.apply(q, k, v, s, group, kernels or NativeBlockKernels)
+    return _RingCausal.apply(q, k, v, s, group, kernels or NativeBlockKernels, layout == "zigzag")
