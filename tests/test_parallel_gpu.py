@@ -33,7 +33,7 @@ def _worker(rank, world, port, mode, results):
         B, L, Hq, Hkv, D = 1, 2048 * world, 8, 2, 128
         mk = lambda *s: torch.randn(s, generator=g).to(device=dev, dtype=torch.bfloat16)
         q, k, v, dy = mk(B, L, Hq, D), mk(B, L, Hkv, D), mk(B, L, Hkv, D), mk(B, L, Hq, D)
-        ids = (torch.arange(L, device=dev) // 1500).expand(B, -1).contiguous() if mode != "ring" else None
+        ids = (torch.arange(L, device=dev) // 1500).expand(B, -1).contiguous() if mode in ("swa", "sca") else None
         n = L // world
         sl = slice(rank * n, (rank + 1) * n)
         if mode == "zigzag":
@@ -47,7 +47,7 @@ def _worker(rank, world, port, mode, results):
             y = P.sequence_parallel_flash_sca(ql, kl, vl, 512, segment_idx=ids[:, sl])
             yf = xattn.flash_sca(qf, kf, vf, 512, segment_idx=ids)
         else:
-            y = P.ring_causal_flash_attn(ql, kl, vl)
+            y = P.ring_causal_flash_attn(ql, kl, vl, layout="zigzag" if mode == "zigzag" else "contiguous")
             yf = xattn.causal_flash_attn(qf, kf, vf)
         grads = torch.autograd.grad(y, (ql, kl, vl), dy[:, sl])
         ref = torch.autograd.grad(yf, (qf, kf, vf), dy)
