@@ -47,6 +47,8 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 # capture summarised in profiles/ncu_full_causal_small.md
 NCU_DRAM_BYTES_PER_BATCH_ROW = {"fwd": 137.8e6, "bwd_dq": 215.1e6, "bwd_dkv": 346.6e6}
 
+NCU_DRAM_BYTES_DECODE = 1080.4e6
+
 WORKLOADS = {
     # name: (B, S, Hq, Hkv, D, packed segments?, description)
     "causal_c2": dict(B=4, S=8192, Hq=32, Hkv=8, D=128, segments=True,
@@ -432,7 +434,9 @@ def run_decode(args, w, world, rank, dev):
             "gpu_launches": 2 * len(fwd) + 3 * len([1 for kind, _ in records if kind == "plan"]),
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "fwd (decode shape) + merge", "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_DECODE,
+                         "traffic_source": "ncu dram__bytes_read+write of one launch of each kernel on this "
+                                           "workload (profiles/ncu_full_decode.md)",
                          "peak_source": f"{peak_src} hbm_gbs (copy bandwidth)"},
             "kernel_ms": kernel_ms,
         }))
