@@ -61,6 +61,10 @@ WORKLOADS = {
     # window-sized K/V halo from its predecessor
     "swa_c3": dict(B=1, S=32768, Hq=32, Hkv=8, D=128, segments=False, window=4096,
                    text="configs[2]: sliding-window fwd+bwd bf16 B=1 S=32768 Hq=32 Hkv=8 D=128 window=4096, sequence-sharded with KV halo exchange"),
+    # causal attention over one long sequence, sequence-sharded in the zig-zag layout (strong scaling):
+    # ring of K/V blocks, every rank computes half a block per step
+    "ring_causal": dict(B=1, S=32768, Hq=32, Hkv=8, D=128, segments=False, ring=True,
+                        text="causal fwd+bwd bf16 B=1 S=32768 Hq=32 Hkv=8 D=128, one sequence sharded over the ranks (zig-zag ring of K/V blocks)"),
     # one new token per sequence against a long key cache: forward only, HBM-bound (K and V are
     # streamed once); reported in GB/s of K + V + q + y bytes, not in the headline metric
     "decode": dict(B=8, S=32768, Hq=32, Hkv=8, D=128, segments=False, decode=True,
@@ -213,7 +217,7 @@ def run_ours(args, w):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    if "window" in w:
+    if "window" in w or w.get("ring"):
         return run_swa_sharded(args, w, world, rank, dev)
     if w.get("decode"):
         return run_decode(args, w, world, rank, dev)
@@ -445,7 +449,8 @@ def run_decode(args, w, world, rank, dev):
 
 
 def run_swa_sharded(args, w, world, rank, dev):
-    """configs[2]: one sequence of S tokens split contiguously over the ranks; total work is fixed."""
+    """One sequence of S tokens split over the ranks, total work fixed: configs[2] (sliding window,
+    contiguous slices, K/V halo exchange) or the causal ring (zig-zag slices)."""
     import torch.distributed as dist
     import xattn_b200 as xattn
     from xattn_b200 import _native, parallel as P
@@ -453,22 +458,23 @@ def run_swa_sharded(args, w, world, rank, dev):
     if world == 1:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=os.environ.get("MASTER_PORT", "29533"))
         dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
-    S, D, window = w["S"], w["D"], w["window"]
-    if S % world or S // world < window:
-        raise SystemExit("sequence length must split into slices of at least one window")
+    ring = bool(w.get("ring"))
+    S, D, window = w["S"], w["D"], w.get("window", 0)
+    if S % (2 * world) or S // world < window:
+        raise SystemExit("sequence length must split into even slices of at least one window")
     n = S // world
     g = torch.Generator().manual_seed(2)
     draw = lambda *shape: torch.randn(shape, generator=g, dtype=torch.float32).to(torch.bfloat16)
     q, k, v, dy = draw(1, S, w["Hq"], D), draw(1, S, w["Hkv"], D), draw(1, S, w["Hkv"], D), draw(1, S, w["Hq"], D)
-    sl = slice(rank * n, (rank + 1) * n)
+    sl = P.zigzag_indices(S, rank, world) if ring else slice(rank * n, (rank + 1) * n)
     pinned = [t[:, sl].contiguous().pin_memory() for t in (q, k, v, dy)]
     ql, kl, vl, dyl = (t.to(dev) for t in pinned)
-    pairs = w["Hq"] * sum(min(i, window) + 1 for i in range(S))      # whole job
+    pairs = w["Hq"] * (S * (S + 1) // 2 if ring else sum(min(i, window) + 1 for i in range(S)))   # whole job
     flops_step = 14 * D * pairs
 
     def step(a, b, c, d):
         a, b, c = (t.detach().requires_grad_() for t in (a, b, c))
-        y = P.sequence_parallel_flash_swa(a, b, c, window)
+        y = P.ring_causal_flash_attn(a, b, c, layout="zigzag") if ring else P.sequence_parallel_flash_swa(a, b, c, window)
         return (y, *torch.autograd.grad(y, (a, b, c), d))
 
     def barrier():
@@ -526,18 +532,24 @@ def run_swa_sharded(args, w, world, rank, dev):
         kernels = {kd: {"launches": len(vs), "avg_ms": sum(vs) / len(vs), "share": sum(vs) / (ms * args.steps)}
                    for kd, vs in per_kind.items()}
         rank_pairs = pairs / world
-        dkv = kernels.get("bwd_dkv", {"avg_ms": float("inf")})
-        achieved = 8 * D * rank_pairs / dkv["avg_ms"] * 1e-9
+        dkv = kernels.get("bwd_dkv", {"avg_ms": float("inf"), "launches": 1})
+        # the ring launches the kernel once per block step; the work of a rank is spread over them
+        achieved = 8 * D * rank_pairs / (dkv["avg_ms"] * dkv["launches"] / args.steps) * 1e-9
         h2d = sum(t.numel() * t.element_size() for t in pinned) * world
         d2h = sum(t.numel() * t.element_size() for t in out_host) * world if out_host else 0
         print(json.dumps({
-            "metric": "sliding-window attn fwd+bwd TFLOPS (bf16 S=32K w=4096 D=128), whole job",
+            "metric": ("causal ring attn fwd+bwd TFLOPS (bf16 S=32K D=128), whole job" if ring else
+                       "sliding-window attn fwd+bwd TFLOPS (bf16 S=32K w=4096 D=128), whole job"),
             "value": flops_step / ms * 1e-9, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": w["text"], "l2": "0.27 GB of tensors per step in total",
                        "visible_pairs_per_step": pairs, "flops_per_step": flops_step,
-                       "parallelism": f"sequence split over {world} GPU(s); K/V halo of {window} tokens from the previous rank (NCCL send/recv), halo gradients sent back"},
+                       "parallelism": (f"sequence split over {world} GPU(s) in the zig-zag layout; ring of K/V blocks "
+                                       "(NCCL send/recv), partial outputs merged by lse, dK/dV travel home with their block"
+                                       if ring else
+                                       f"sequence split over {world} GPU(s); K/V halo of {window} tokens from the "
+                                       "previous rank (NCCL send/recv), halo gradients sent back")},
             "per_gpu_tflops": flops_step / ms * 1e-9 / world,
             "e2e": None if not e2e_steps else {"value": flops_step / e2e_ms * 1e-9, "unit": "TFLOP/s",
                                                "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
@@ -563,9 +575,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
-    if args.impl == "reference" and w.get("decode"):
-        print(json.dumps({"impl": "reference", "unavailable": "the decode workload is a side measurement of the "
-                          "split forward; the reference arm runs the fwd+bwd workloads"}))
+    if args.impl == "reference" and (w.get("decode") or w["S"] > 8192):
+        print(json.dumps({"impl": "reference", "unavailable": "the CPU arm runs the causal S=8192 workloads: one "
+                          "(batch row, head) slice of a 32768-token sequence needs 4.3 GB per score matrix in fp32"}))
     elif args.impl == "reference":
         run_reference(args, w)
     else:
