@@ -77,8 +77,11 @@ __device__ __forceinline__ void write_row_terms(uint4* dst, float t, float d) {
   dst[1] = make_uint4(0u, 0u, 0u, 0u);
 }
 
-// A group of 8, 16 or 32 lanes (one 16-byte chunk of the row each) takes a (batch, row, head); a warp
-// works on kPrePasses * 32 / group consecutive ones with all their loads issued before the first use.
+// A group of 8, 16 or 32 lanes (one 16-byte chunk of the row each) takes a (row, head) of one batch row;
+// a warp works on kPrePasses * 32 / group consecutive ones with all their loads (lse included) issued
+// before the first use.  Afterwards lane p of a group writes the results of pass p, so the passes'
+// epilogues run side by side.  A block covers 8 warps' worth of consecutive (row, head) pairs, which
+// divides the padded row count times the head count, so no block is ragged; blockIdx.y is the batch row.
 constexpr int kPrePasses = 4;
 
 template <typename T>
@@ -93,33 +96,31 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, 
   const int per_pass = 32 / group;
   const int lane = threadIdx.x & 31;
   const int sub = lane / group, ch = lane % group;
-  const long long total = (long long)B * LqPad * Hq;
-  const long long first = (((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * (per_pass * kPrePasses) + sub;
-  // decode (batch, row, head) once with 64-bit divisions; the other passes are a few heads further on
-  int h0, i0, b0;
-  {
-    const long long f = first < total ? first : total - 1;
-    h0 = (int)(f % Hq);
-    const long long bi = f / Hq;
-    i0 = (int)(bi % LqPad);
-    b0 = (int)(bi / LqPad);
-  }
+  const uint32_t first = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (uint32_t)(per_pass * kPrePasses) + sub;
+  const int h0 = (int)(first % (uint32_t)Hq), i0 = (int)(first / (uint32_t)Hq);
+  for (int b = blockIdx.y; b < B; b += gridDim.y) {
+  const T* dy_b = dy + b * dy_sb;
+  const T* y_b = y + b * y_sb;
+  const float* lse_b = lse + (size_t)b * Hq * Lq;
   uint4 a[kPrePasses], o[kPrePasses];
-  int hh[kPrePasses], ii[kPrePasses], bb[kPrePasses];
+  float l_mine = 0.f;                   // lane p of the group: lse of pass p
+  int h_mine = 0, i_mine = LqPad;
 #pragma unroll
   for (int ps = 0; ps < kPrePasses; ++ps) {
-    int h = h0 + ps * per_pass, i = i0, b = b0;
+    int h = h0 + ps * per_pass, i = i0;
     while (h >= Hq) { h -= Hq; ++i; }
-    while (i >= LqPad) { i -= LqPad; ++b; }
-    if (first >= total) b = B;                 // nothing left for this lane
-    hh[ps] = h; ii[ps] = i; bb[ps] = b;
     a[ps] = make_uint4(0, 0, 0, 0);
     o[ps] = make_uint4(0, 0, 0, 0);
-    if (b < B && i < Lq && ch < chunks) {
-      a[ps] = __ldg(reinterpret_cast<const uint4*>(dy + b * dy_sb + i * dy_sl + h * dy_sh + ch * 8));
-      o[ps] = __ldg(reinterpret_cast<const uint4*>(y + b * y_sb + i * y_sl + h * y_sh + ch * 8));
+    if (i < Lq && ch < chunks) {
+      a[ps] = __ldg(reinterpret_cast<const uint4*>(dy_b + i * dy_sl + h * dy_sh + ch * 8));
+      o[ps] = __ldg(reinterpret_cast<const uint4*>(y_b + i * y_sl + h * y_sh + ch * 8));
+    }
+    if (ch == ps) {
+      h_mine = h; i_mine = i;
+      if (i < Lq) l_mine = __ldg(lse_b + (size_t)h * Lq + i);
     }
   }
+  float acc_mine = 0.f;
 #pragma unroll
   for (int ps = 0; ps < kPrePasses; ++ps) {
     const uint32_t aw[4] = {a[ps].x, a[ps].y, a[ps].z, a[ps].w};
@@ -133,21 +134,22 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, 
       acc = fmaf(fa.y, fo.y, acc);
     }
     for (int off = group >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    const int h = hh[ps], i = ii[ps], b = bb[ps];
-    if (ch == 0 && b < B) {
-      const size_t idx = ((size_t)b * Hq + h) * LqPad + i;
-      if (i >= Lq) {
-        // padding up to whole tiles: rows that contribute nothing
-        ndelta[idx] = 0.f;
-        nlse2[idx] = -INFINITY;
-        write_row_terms(row_terms + 2 * idx, -INFINITY, 0.f);
-      } else {
-        const float l = lse[((size_t)b * Hq + h) * Lq + i];
-        ndelta[idx] = -acc;
-        nlse2[idx] = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
-        write_row_terms(row_terms + 2 * idx, (l == -INFINITY) ? -INFINITY : -l / scale, -acc);
-      }
+    if (ch == ps) acc_mine = acc;
+  }
+  if (ch < kPrePasses && i_mine < LqPad) {
+    const size_t idx = ((size_t)b * Hq + h_mine) * LqPad + i_mine;
+    if (i_mine >= Lq) {
+      // padding up to whole tiles: rows that contribute nothing
+      ndelta[idx] = 0.f;
+      nlse2[idx] = -INFINITY;
+      write_row_terms(row_terms + 2 * idx, -INFINITY, 0.f);
+    } else {
+      const float l = l_mine;
+      ndelta[idx] = -acc_mine;
+      nlse2[idx] = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
+      write_row_terms(row_terms + 2 * idx, (l == -INFINITY) ? -INFINITY : -l / scale, -acc_mine);
     }
+  }
   }
 }
 
@@ -1074,11 +1076,11 @@ static int launch_bwd(const XattnBwdArgs& a, BwdParams& p, cudaStream_t stream) 
   p.ndelta = ndelta; p.nlse2 = nlse2; p.row_terms = row_terms;
   {
     const int chunks = p.V >> 3;
-    const int per_warp = kPrePasses * 32 / (chunks <= 8 ? 8 : (chunks <= 16 ? 16 : 32));
-    const long long warps = ((long long)p.B * p.LqPad * p.Hq + per_warp - 1) / per_warp;
-    const long long blocks = (warps * 32 + 255) / 256;
+    const int per_block = 8 * kPrePasses * 32 / (chunks <= 8 ? 8 : (chunks <= 16 ? 16 : 32));   // divides 128
+    const long long blocks = (long long)p.LqPad * p.Hq / per_block;
+    if (blocks > 0x7fffffffLL) { set_error("backward preprocess grid out of range"); return XATTN_E_INVALID; }
     ProfileScope prof(kProfBwdPre, stream);
-    bwd_pre_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
+    bwd_pre_kernel<T><<<dim3((unsigned)blocks, (unsigned)(p.B < 65535 ? p.B : 65535)), 256, 0, stream>>>(
         reinterpret_cast<const T*>(a.dy), reinterpret_cast<const T*>(a.y), a.lse, p.B, p.Lq, p.Hq, p.V,
         a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], a.y_strides[0], a.y_strides[1], a.y_strides[2], p.LqPad,
         p.scale, ndelta, nlse2, row_terms);
