@@ -45,7 +45,7 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 
 # DRAM bytes (read + write) of one launch per batch row of S=8192, Hq=32, Hkv=8, D=128, from the ncu
 # capture summarised in profiles/ncu_full_causal_small.md
-NCU_DRAM_BYTES_PER_BATCH_ROW = {"fwd": 137.8e6, "bwd_dq": 215.1e6, "bwd_dkv": 346.6e6}
+NCU_DRAM_BYTES_PER_BATCH_ROW = {"fwd": 137.9e6, "bwd_dq": 215.1e6, "bwd_dkv": 353.3e6}
 
 NCU_DRAM_BYTES_DECODE = 1080.4e6
 
