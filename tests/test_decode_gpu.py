@@ -126,3 +126,22 @@ def test_split_entry_rejects_bad_arguments(cuda_device):
     plan = _native.build_plan(1, 2, 1024, cuda_device)
     with pytest.raises(RuntimeError, match="splits"):
         _native.attention_fwd(q, k, v, plan, 0.125, splits=1000)
+
+
+@pytest.mark.parametrize("q_length", (1, 4))
+@pytest.mark.parametrize("heads", ((8, 2), (4, 4), (16, 1)), ids=("gqa", "mha", "mqa"))
+@pytest.mark.parametrize("variant", ("causal", "window", "chunk"))
+@pytest.mark.parametrize("level", (0, 1))
+def test_softdelta_decode_shapes(q_length, heads, variant, level, cuda_device):
+    """Both reads of SoftDelta (the query read and the strict-past read of k_read) on the split forward."""
+    from tests.test_softdelta_gpu import check, make_inputs
+    dtype = torch.bfloat16
+    t = make_inputs(cuda_device, dtype, 2, 900, heads[0], heads[1], 64, 128, True, q_length=q_length, seed=13)
+    if variant == "causal":
+        check("softdelta_attention", t, dtype, level)
+    elif variant == "window":
+        check("sliding_window_softdelta_attention", t, dtype, level, dict(window_size=600),
+              dict(visibility="window", span=600))
+    else:
+        check("sliding_chunk_softdelta_attention", t, dtype, level, dict(chunk_size=512),
+              dict(visibility="chunk", span=512))

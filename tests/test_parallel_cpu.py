@@ -146,3 +146,24 @@ def test_halo_requires_long_enough_slices():
             P.sequence_parallel_flash_sca(q, q, q, 3, op=_oracle_op("chunk"))
     finally:
         dist.destroy_process_group()
+
+
+def test_zigzag_indices_partition_the_sequence():
+    from xattn_b200 import parallel as P
+    for world in (1, 2, 3, 8):
+        length = 16 * world
+        parts = [P.zigzag_indices(length, r, world) for r in range(world)]
+        assert all(p.numel() == length // world for p in parts)
+        assert torch.equal(torch.cat(parts).sort().values, torch.arange(length))
+        c = length // (2 * world)
+        for r, p in enumerate(parts):
+            # an early chunk and its mirror image: causal work per rank is the same
+            assert p[0] == r * c and p[-1] == length - r * c - 1
+            assert bool((p[1:] > p[:-1]).all())
+    with pytest.raises(ValueError, match="multiple of 2"):
+        P.zigzag_indices(10, 0, 2)
+    q = torch.zeros(1, 3, 1, 8)
+    with pytest.raises(ValueError, match="even slice"):
+        P.ring_causal_flash_attn(q, q, q, layout="zigzag")
+    with pytest.raises(ValueError, match="layout"):
+        P.ring_causal_flash_attn(q, q, q, layout="striped")
