@@ -145,3 +145,26 @@ def test_softdelta_decode_shapes(q_length, heads, variant, level, cuda_device):
     else:
         check("sliding_chunk_softdelta_attention", t, dtype, level, dict(chunk_size=512),
               dict(visibility="chunk", span=512))
+
+
+def test_decode_step_runs_as_a_cuda_graph(cuda_device):
+    """Plan, split forward and merge kernel captured once and replayed on new inputs (the launch-bound
+    serving loop): the device-status protocol makes no event queries during capture."""
+    B, Lk, Hq, Hkv, D = 2, 4096, 16, 4, 128
+    q, k, v = _decode_inputs(B, 1, Lk, Hq, Hkv, D, D, torch.bfloat16, cuda_device)
+    side = torch.cuda.Stream(cuda_device)
+    side.wait_stream(torch.cuda.current_stream(cuda_device))
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            xattn.causal_flash_attn_fwd(q, k, v)
+    torch.cuda.current_stream(cuda_device).wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y, lse = xattn.causal_flash_attn_fwd(q, k, v)
+    for seed in (1, 2):
+        q2, k2, v2 = _decode_inputs(B, 1, Lk, Hq, Hkv, D, D, torch.bfloat16, cuda_device, seed=seed)
+        q.copy_(q2); k.copy_(k2); v.copy_(v2)
+        graph.replay()
+        y_eager, lse_eager = xattn.causal_flash_attn_fwd(q2, k2, v2)
+        assert torch.equal(y, y_eager) and torch.equal(lse, lse_eager)
+    xattn.check_status()

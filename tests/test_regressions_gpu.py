@@ -170,3 +170,32 @@ def test_plan_orders_key_tiles_longest_first(cuda_device):
     work = (k_tiles[:, 1] - k_tiles[:, 0]).clamp_min(0)[order.long()]
     assert bool((work[1:] <= work[:-1]).all())
     assert int(work[0]) > int(work[-1])
+
+
+def test_training_step_runs_as_a_cuda_graph(cuda_device):
+    """Forward + backward with segment ids captured in a CUDA graph and replayed on new inputs."""
+    B, L, Hq, Hkv, D = 2, 640, 8, 2, 128
+    gen = torch.Generator().manual_seed(3)
+    mk = lambda *s: torch.randn(s, generator=gen).to(device=cuda_device, dtype=torch.bfloat16)
+    q, k, v, dy = mk(B, L, Hq, D), mk(B, L, Hkv, D), mk(B, L, Hkv, D), mk(B, L, Hq, D)
+    ids = (torch.arange(L, device=cuda_device) // 250).expand(B, -1).contiguous()
+
+    def step():
+        y, lse = xattn.causal_flash_attn_fwd(q, k, v, segment_idx=ids)
+        return (y, *xattn.causal_flash_attn_bwd(dy, q, k, v, y, lse, segment_idx=ids)[:3])
+
+    side = torch.cuda.Stream(cuda_device)
+    side.wait_stream(torch.cuda.current_stream(cuda_device))
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream(cuda_device).wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outs = step()
+    for t in (q, k, v, dy):
+        t.copy_(mk(*t.shape))
+    graph.replay()
+    eager = step()
+    for a, b in zip(outs, eager):
+        assert torch.equal(a, b)
+    xattn.check_status()

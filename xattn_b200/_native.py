@@ -57,6 +57,8 @@ def _raise_status(value: int) -> None:
 
 def _pre_launch(device: torch.device) -> _DeviceState:
     st = _state(device)
+    if torch.cuda.is_current_stream_capturing():
+        return st    # no event queries inside a CUDA graph capture; check_status() after a replay reads the word
     if st.event is not None and st.event.query():
         st.event = None
         value = int(st.host[0])
@@ -67,6 +69,8 @@ def _pre_launch(device: torch.device) -> _DeviceState:
 
 
 def _post_launch(st: _DeviceState) -> None:
+    if torch.cuda.is_current_stream_capturing():
+        return
     if _SYNC_CHECK:
         torch.cuda.current_stream().synchronize()
         value = int(st.status.item())
