@@ -13,7 +13,10 @@ Inputs are seeded synthetic N(0,1) tensors.  Rank 0 prints ONE JSON line.
 * ``e2e``       the same through the public ops with HOST buffers: every step copies q, k, v, dy
                 from pinned memory and copies y, dq, dk, dv back, inside the timed region.  Batch
                 rows are independent, so the step is pipelined over them (copies of the next and
-                of the previous row run beside the kernels of the current one).
+                of the previous row run beside the kernels of the current one; within a row dy comes
+                in last and y leaves first; device input buffers are double-buffered, so the next
+                step's inputs come in while this step's results leave; the clock stops after the
+                last step's results are on the host).
 * ``roofline``  the dominant kernel's algorithmic FLOP/s from per-launch CUDA events, against the
                 measured dense bf16 peak of MEASURED_PEAKS.json.
 * ``cpu_baseline`` the CPU oracle timed on the host cores (rank 0, N=1 only), on the reference's own
@@ -272,37 +275,60 @@ def run_ours(args, w):
     # and row b - 1 goes out while row b is computed (one copy stream per direction).
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     Bn = w["B"]
-    dev_in = [torch.empty_like(t, device=dev) for t in pinned[:4]]
+    # two sets of device input buffers: the inputs of step i + 1 come in while step i's results go out
+    dev_sets = [[torch.empty_like(t, device=dev) for t in pinned[:4]] for _ in range(2)]
+    set_free = [None, None]
+    step_no = 0
     ids_rows = None if ids is None else [ids[b:b + 1] for b in range(Bn)]
 
     def e2e_step():
-        nonlocal out_host
+        nonlocal out_host, step_no
         main = torch.cuda.current_stream(dev)
-        s_in.wait_stream(main)
-        s_out.wait_stream(main)
+        which = step_no & 1
+        step_no += 1
+        dev_in = dev_sets[which]
+        if set_free[which] is not None:
+            s_in.wait_event(set_free[which])      # the kernels of two steps ago have read this set
         arrived = []
         with torch.cuda.stream(s_in):
             for b in range(Bn):
-                for dst, src in zip(dev_in, pinned[:4]):
+                # q, k, v first: the forward can start (and y can leave) while dy is still coming in
+                for dst, src in zip(dev_in[:3], pinned[:3]):
                     dst[b:b + 1].copy_(src[b:b + 1], non_blocking=True)
-                ev = torch.cuda.Event()
-                ev.record(s_in)
-                arrived.append(ev)
-        for b in range(Bn):
-            main.wait_event(arrived[b])
-            q_, k_, v_, dy_ = (t[b:b + 1] for t in dev_in)
-            meta_b = {} if ids_rows is None else {"segment_idx": ids_rows[b]}
-            y_, lse_ = xattn.causal_flash_attn_fwd(q_, k_, v_, **meta_b)
-            outs = (y_, *xattn.causal_flash_attn_bwd(dy_, q_, k_, v_, y_, lse_, **meta_b))
-            if out_host is None:
-                out_host = [torch.empty((Bn,) + tuple(o.shape[1:]), dtype=o.dtype).pin_memory() for o in outs]
+                ev_qkv = torch.cuda.Event()
+                ev_qkv.record(s_in)
+                dev_in[3][b:b + 1].copy_(pinned[3][b:b + 1], non_blocking=True)
+                ev_dy = torch.cuda.Event()
+                ev_dy.record(s_in)
+                arrived.append((ev_qkv, ev_dy))
+
+        def send_back(b, outs, first):
+            nonlocal out_host
             done = torch.cuda.Event()
             done.record(main)
             s_out.wait_event(done)
             with torch.cuda.stream(s_out):
-                for dst, src in zip(out_host, outs):
+                for j, src in enumerate(outs):
                     src.record_stream(s_out)
-                    dst[b:b + 1].copy_(src, non_blocking=True)
+                    out_host[first + j][b:b + 1].copy_(src, non_blocking=True)
+
+        for b in range(Bn):
+            q_, k_, v_, dy_ = (t[b:b + 1] for t in dev_in)
+            meta_b = {} if ids_rows is None else {"segment_idx": ids_rows[b]}
+            main.wait_event(arrived[b][0])
+            y_, lse_ = xattn.causal_flash_attn_fwd(q_, k_, v_, **meta_b)
+            if out_host is None:
+                out_host = [torch.empty((Bn,) + tuple(t.shape[1:]), dtype=t.dtype).pin_memory()
+                            for t in (y_, q_, k_, v_)]
+            send_back(b, (y_,), 0)
+            main.wait_event(arrived[b][1])
+            grads = xattn.causal_flash_attn_bwd(dy_, q_, k_, v_, y_, lse_, **meta_b)
+            send_back(b, grads[:3], 1)
+        set_free[which] = torch.cuda.Event()
+        set_free[which].record(main)
+
+    def e2e_drain():
+        main = torch.cuda.current_stream(dev)
         main.wait_stream(s_out)
         main.wait_stream(s_in)
 
@@ -310,10 +336,12 @@ def run_ours(args, w):
     e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 10))
     for _ in range(0 if args.no_e2e else 2):
         e2e_step()
+    e2e_drain()
     barrier()
     f0.record()
     for _ in range(e2e_steps):
         e2e_step()
+    e2e_drain()                 # the last step's results are on the host before the clock stops
     f1.record()
     barrier()
     e2e_ms_total = f0.elapsed_time(f1)
