@@ -7,8 +7,7 @@
 //   Constant-key rows: dQ of a row whose visible keys are all the same vector is exactly zero
 //     (csrc/attention/precision/constant_keys.cu: key-equality runs, then zero those rows).
 //
-// One warp per (batch, token, KV head); each lane owns 8 consecutive channels per 256-channel
-// slab, so every access is a 16-byte vector (or two for FP32).
+// Every access is a 16-byte vector (or two for FP32): a lane owns 8 consecutive channels.
 #include <cub/block/block_scan.cuh>
 #include "common.cuh"
 
@@ -42,111 +41,191 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32(float x) { return 
 template <> __device__ __forceinline__ __half from_f32(float x) { return __float2half(x); }
 
 // rows = B * L; read / y: [rows][H][V], neg: [rows][Hkv][V], g: [rows][H][C] with one gate per
-// group of Dg = V / C consecutive channels (C = 1: one gate per head)
+// group of Dg = V / C consecutive channels (C = 1: one gate per head).
+//
+// A group of 8, 16 or 32 lanes (one 16-byte chunk of the V channels each) takes a unit = (row, KV head)
+// and walks the G query heads of that KV head; it keeps kGateUnits units in flight, with the loads of
+// all of them issued before the first use.  With u = row * Hkv + kv the addresses need no division:
+// neg at u * V, head r of the group at (u * G + r) * V, its gates at (u * G + r) * C.
+constexpr int kGateUnits = 4;
+constexpr int kGateThreads = 128;   // small blocks: the backward needs ~150 registers per thread
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) { const float2 t = Pack2<T>::unpack(w[k]); f[2 * k] = t.x; f[2 * k + 1] = t.y; }
+}
+
+// neg_read of the units in flight: raw 16-bit chunks, or FP32 values (level 1)
+template <typename T, bool NEG_F32> struct NegRegs;
+template <typename T> struct NegRegs<T, false> {
+  uint4 raw[kGateUnits];
+  __device__ __forceinline__ void load(int ps, const void* neg, long long off) {
+    raw[ps] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(neg) + off));
+  }
+  __device__ __forceinline__ void clear(int ps) { raw[ps] = make_uint4(0, 0, 0, 0); }
+  __device__ __forceinline__ void get(int ps, float* f) const { unpack8<T>(raw[ps], f); }
+};
+template <typename T> struct NegRegs<T, true> {
+  float val[kGateUnits][8];
+  __device__ __forceinline__ void load(int ps, const void* neg, long long off) {
+    load8_f32(reinterpret_cast<const float*>(neg) + off, val[ps]);
+  }
+  __device__ __forceinline__ void clear(int ps) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) val[ps][e] = 0.f;
+  }
+  __device__ __forceinline__ void get(int ps, float* f) const {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = val[ps][e];
+  }
+};
+
+struct GateLanes {
+  int group, per_pass, sub, ch, c;
+  bool lane_on;
+  long long first, total;
+  __device__ __forceinline__ GateLanes(long long rows, int Hkv, int V) {
+    const int chunks = V >> 3;
+    group = chunks <= 8 ? 8 : (chunks <= 16 ? 16 : 32);
+    per_pass = 32 / group;
+    const int lane = threadIdx.x & 31;
+    sub = lane / group;
+    ch = lane % group;
+    c = ch * 8;
+    lane_on = ch < chunks;
+    total = rows * Hkv;
+    first = (((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * (per_pass * kGateUnits) + sub;
+  }
+  __device__ __forceinline__ long long unit(int ps) const { return first + (long long)ps * per_pass; }
+  __device__ __forceinline__ bool on(int ps) const { return lane_on && unit(ps) < total; }
+};
+
 template <typename T, bool NEG_F32>
-__global__ void __launch_bounds__(256) gate_fwd_kernel(const T* __restrict__ read, const void* __restrict__ neg_,
+__global__ void __launch_bounds__(kGateThreads) gate_fwd_kernel(const T* __restrict__ read, const void* __restrict__ neg_,
                                                        const T* __restrict__ g, T* __restrict__ y, long long rows,
                                                        int H, int Hkv, int V, int C, int Dg) {
-  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (w >= rows * Hkv) return;
-  const long long row = w / Hkv;
-  const int kv = (int)(w - row * Hkv);
+  const GateLanes ln(rows, Hkv, V);
   const int G = H / Hkv;
-  for (int c = lane * 8; c < V; c += 256) {
-    float n[8];
-    if (NEG_F32) load8_f32(reinterpret_cast<const float*>(neg_) + (row * Hkv + kv) * V + c, n);
-    else load8<T>(reinterpret_cast<const T*>(neg_) + (row * Hkv + kv) * V + c, n);
-    for (int r = 0; r < G; ++r) {
-      const int h = kv * G + r;
-      const T* gh = g + (row * H + h) * C;
-      float x[8];
-      load8<T>(read + (row * H + h) * V + c, x);
+  NegRegs<T, NEG_F32> neg;
+#pragma unroll
+  for (int ps = 0; ps < kGateUnits; ++ps) {
+    neg.clear(ps);
+    if (ln.on(ps)) neg.load(ps, neg_, ln.unit(ps) * V + ln.c);
+  }
+  for (int r = 0; r < G; ++r) {
+    uint4 xr[kGateUnits];
+    T graw[kGateUnits];
+#pragma unroll
+    for (int ps = 0; ps < kGateUnits; ++ps) {
+      xr[ps] = make_uint4(0, 0, 0, 0);
+      graw[ps] = from_f32<T>(0.f);
+      if (ln.on(ps)) {
+        const long long hr = ln.unit(ps) * G + r;
+        xr[ps] = *reinterpret_cast<const uint4*>(read + hr * V + ln.c);   // y may be read itself: no __ldg
+        if (C == 1) graw[ps] = g[hr];
+      }
+    }
+#pragma unroll
+    for (int ps = 0; ps < kGateUnits; ++ps) {
+      if (!ln.on(ps)) continue;
+      const long long hr = ln.unit(ps) * G + r;
+      float x[8], n[8];
+      unpack8<T>(xr[ps], x);
+      neg.get(ps, n);
       if (C == 1) {
-        const float gate = sigmoid_f32(to_f32<T>(gh[0]));
+        const float gate = sigmoid_f32(to_f32<T>(graw[ps]));
 #pragma unroll
         for (int e = 0; e < 8; ++e) x[e] = x[e] - gate * n[e];
       } else {
+        const T* gh = g + hr * C;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) x[e] = x[e] - sigmoid_f32(to_f32<T>(gh[(c + e) / Dg])) * n[e];
+        for (int e = 0; e < 8; ++e) x[e] = x[e] - sigmoid_f32(to_f32<T>(gh[(ln.c + e) / Dg])) * n[e];
       }
-      store8<T>(y + (row * H + h) * V + c, x);
+      store8<T>(y + hr * V + ln.c, x);
     }
   }
 }
 
 template <typename T, bool NEG_F32>
-__global__ void __launch_bounds__(256) gate_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ y,
+__global__ void __launch_bounds__(kGateThreads) gate_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ y,
                                                        const void* __restrict__ neg_, const T* __restrict__ g,
                                                        T* __restrict__ read, T* __restrict__ dneg, T* __restrict__ dg,
                                                        long long rows, int H, int Hkv, int V, int C, int Dg) {
-  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (w >= rows * Hkv) return;
-  const long long row = w / Hkv;
-  const int kv = (int)(w - row * Hkv);
+  const GateLanes ln(rows, Hkv, V);
   const int G = H / Hkv;
-  // V <= 256: one slab per lane
-  const int c = lane * 8;
-  const bool act = c < V;
-  float n[8], dn[8];
+  NegRegs<T, NEG_F32> neg;
+  float dn[kGateUnits][8];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) { n[e] = 0.f; dn[e] = 0.f; }
-  if (act) {
-    if (NEG_F32) load8_f32(reinterpret_cast<const float*>(neg_) + (row * Hkv + kv) * V + c, n);
-    else load8<T>(reinterpret_cast<const T*>(neg_) + (row * Hkv + kv) * V + c, n);
+  for (int ps = 0; ps < kGateUnits; ++ps) {
+    neg.clear(ps);
+    if (ln.on(ps)) neg.load(ps, neg_, ln.unit(ps) * V + ln.c);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dn[ps][e] = 0.f;
   }
   for (int r = 0; r < G; ++r) {
-    const int h = kv * G + r;
-    const T* gh = g + (row * H + h) * C;
-    float d[8], yy[8];
+    uint4 dr[kGateUnits], yr[kGateUnits];
+    T graw[kGateUnits];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) { d[e] = 0.f; yy[e] = 0.f; }
-    if (act) {
-      load8<T>(dy + (row * H + h) * V + c, d);
-      load8<T>(y + (row * H + h) * V + c, yy);
+    for (int ps = 0; ps < kGateUnits; ++ps) {
+      dr[ps] = make_uint4(0, 0, 0, 0);
+      yr[ps] = make_uint4(0, 0, 0, 0);
+      graw[ps] = from_f32<T>(0.f);
+      if (ln.on(ps)) {
+        const long long hr = ln.unit(ps) * G + r;
+        dr[ps] = __ldg(reinterpret_cast<const uint4*>(dy + hr * V + ln.c));
+        yr[ps] = __ldg(reinterpret_cast<const uint4*>(y + hr * V + ln.c));
+        if (C == 1) graw[ps] = g[hr];
+      }
     }
-    if (C == 1) {
-      const float gate = sigmoid_f32(to_f32<T>(gh[0]));
-      float dot = 0.f;
-      if (act) {
+#pragma unroll
+    for (int ps = 0; ps < kGateUnits; ++ps) {
+      const bool on = ln.on(ps);
+      const long long hr = ln.unit(ps) * G + r;
+      float d[8], yy[8], n[8];
+      unpack8<T>(dr[ps], d);
+      unpack8<T>(yr[ps], yy);
+      neg.get(ps, n);
+      if (C == 1) {
+        const float gate = sigmoid_f32(to_f32<T>(graw[ps]));
+        float dot = 0.f;
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          dn[e] -= gate * d[e];
+          dn[ps][e] -= gate * d[e];
           dot += d[e] * n[e];
           yy[e] += gate * n[e];
         }
-      }
+        for (int o = ln.group >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (on && ln.ch == 0) dg[hr] = from_f32<T>(-dot * gate * (1.f - gate));
+      } else {
+        const T* gh = g + hr * C;
+        if (on) {
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      if (lane == 0) dg[row * H + h] = from_f32<T>(-dot * gate * (1.f - gate));
-    } else {
-      if (act) {
+          for (int e = 0; e < 8; ++e) {
+            const float gate = sigmoid_f32(to_f32<T>(gh[(ln.c + e) / Dg]));
+            dn[ps][e] -= gate * d[e];
+            yy[e] += gate * n[e];
+          }
+        }
+        // one gate gradient per value group: the group's share of <dy, neg_read>
+        for (int j = 0; j < C; ++j) {
+          float dot = 0.f;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float gate = sigmoid_f32(to_f32<T>(gh[(c + e) / Dg]));
-          dn[e] -= gate * d[e];
-          yy[e] += gate * n[e];
+          for (int e = 0; e < 8; ++e) dot += ((ln.c + e) / Dg == j) ? d[e] * n[e] : 0.f;
+          for (int o = ln.group >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+          if (on && ln.ch == 0) {
+            const float gate = sigmoid_f32(to_f32<T>(gh[j]));
+            dg[hr * C + j] = from_f32<T>(-dot * gate * (1.f - gate));
+          }
         }
       }
-      // one gate gradient per value group: the group's share of <dy, neg_read>
-      for (int j = 0; j < C; ++j) {
-        float dot = 0.f;
-        if (act) {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) dot += ((c + e) / Dg == j) ? d[e] * n[e] : 0.f;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        if (lane == 0) {
-          const float gate = sigmoid_f32(to_f32<T>(gh[j]));
-          dg[(row * H + h) * C + j] = from_f32<T>(-dot * gate * (1.f - gate));
-        }
-      }
+      if (on) store8<T>(read + hr * V + ln.c, yy);
     }
-    if (act) store8<T>(read + (row * H + h) * V + c, yy);
   }
-  if (act) store8<T>(dneg + (row * Hkv + kv) * V + c, dn);
+#pragma unroll
+  for (int ps = 0; ps < kGateUnits; ++ps)
+    if (ln.on(ps)) store8<T>(dneg + ln.unit(ps) * V + ln.c, dn[ps]);
 }
 
 // ---- constant-key rows ------------------------------------------------------
@@ -229,25 +308,32 @@ static int check_gate(const XattnGateArgs* a) {
   return XATTN_OK;
 }
 
+// warps needed when a warp takes kGateUnits * (32 / lanes per unit) units
+static long long gate_warps(const XattnGateArgs* a) {
+  const int chunks = (int)a->v_dim >> 3;
+  const int per_warp = kGateUnits * 32 / (chunks <= 8 ? 8 : (chunks <= 16 ? 16 : 32));
+  return (a->rows * a->kv_heads + per_warp - 1) / per_warp;
+}
+
 template <typename T>
 static void launch_gate_fwd(const XattnGateArgs* a, cudaStream_t s) {
   const int groups = a->value_groups > 1 ? (int)a->value_groups : 1;
-  const long long warps = a->rows * a->kv_heads;
-  const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+  const long long warps = gate_warps(a);
+  const unsigned blocks = (unsigned)((warps * 32 + kGateThreads - 1) / kGateThreads);
   if (a->neg_is_f32)
-    gate_fwd_kernel<T, true><<<blocks, 256, 0, s>>>((const T*)a->read, a->neg_read, (const T*)a->g, (T*)a->y, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim, groups, (int)a->v_dim / groups);
+    gate_fwd_kernel<T, true><<<blocks, kGateThreads, 0, s>>>((const T*)a->read, a->neg_read, (const T*)a->g, (T*)a->y, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim, groups, (int)a->v_dim / groups);
   else
-    gate_fwd_kernel<T, false><<<blocks, 256, 0, s>>>((const T*)a->read, a->neg_read, (const T*)a->g, (T*)a->y, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim, groups, (int)a->v_dim / groups);
+    gate_fwd_kernel<T, false><<<blocks, kGateThreads, 0, s>>>((const T*)a->read, a->neg_read, (const T*)a->g, (T*)a->y, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim, groups, (int)a->v_dim / groups);
 }
 template <typename T>
 static void launch_gate_bwd(const XattnGateArgs* a, cudaStream_t s) {
   const int groups = a->value_groups > 1 ? (int)a->value_groups : 1;
-  const long long warps = a->rows * a->kv_heads;
-  const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+  const long long warps = gate_warps(a);
+  const unsigned blocks = (unsigned)((warps * 32 + kGateThreads - 1) / kGateThreads);
   if (a->neg_is_f32)
-    gate_bwd_kernel<T, true><<<blocks, 256, 0, s>>>((const T*)a->dy, (const T*)a->y, a->neg_read, (const T*)a->g, (T*)a->read, (T*)a->dneg_read, (T*)a->dg, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim, groups, (int)a->v_dim / groups);
+    gate_bwd_kernel<T, true><<<blocks, kGateThreads, 0, s>>>((const T*)a->dy, (const T*)a->y, a->neg_read, (const T*)a->g, (T*)a->read, (T*)a->dneg_read, (T*)a->dg, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim, groups, (int)a->v_dim / groups);
   else
-    gate_bwd_kernel<T, false><<<blocks, 256, 0, s>>>((const T*)a->dy, (const T*)a->y, a->neg_read, (const T*)a->g, (T*)a->read, (T*)a->dneg_read, (T*)a->dg, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim, groups, (int)a->v_dim / groups);
+    gate_bwd_kernel<T, false><<<blocks, kGateThreads, 0, s>>>((const T*)a->dy, (const T*)a->y, a->neg_read, (const T*)a->g, (T*)a->read, (T*)a->dneg_read, (T*)a->dg, a->rows, (int)a->q_heads, (int)a->kv_heads, (int)a->v_dim, groups, (int)a->v_dim / groups);
 }
 
 int gate_fwd_entry(const XattnGateArgs* a, cudaStream_t s) {
