@@ -253,6 +253,23 @@ typedef struct {
 
 int xattn_b200_zero_constant_key_rows(const XattnConstantKeyArgs* args, xattn_stream_t stream);
 
+/* SoftDelta backward: the dK (or dV) of the query read and of the strict-past read, and optionally the
+ * gradient of the aligned keys used as k_read, summed in FP32 and rounded once
+ * (replaces _softdelta_merge_gradients, csrc/softdelta/bindings.cc:25,
+ * xattn/ops/softdelta_attention.py:506-516).  out = a + b, plus `tail` on the last tail_len rows of
+ * every batch row.  All tensors contiguous in the input dtype; `out` may be `a`. */
+typedef struct {
+  int dtype;
+  int64_t batch, k_len, kv_heads, dim;   /* a, b, out: [B][k_len][Hkv][dim], dim a multiple of 8 */
+  const void* a;
+  const void* b;
+  const void* tail;              /* [B][tail_len][Hkv][dim] or NULL            */
+  int64_t tail_len;              /* <= k_len                                   */
+  void* out;
+} XattnMergeArgs;
+
+int xattn_b200_softdelta_merge_gradients(const XattnMergeArgs* args, xattn_stream_t stream);
+
 /* Per-kernel timing for benchmarks (no counterpart in the reference, whose benchmark tool times
  * whole ops from Python, tests/_benchmark.py:22-35).  While enabled, every entry point brackets
  * its kernels with CUDA events on the launch stream.  xattn_b200_profile_read() synchronises

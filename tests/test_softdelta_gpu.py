@@ -246,3 +246,22 @@ def test_value_groups_match_oracle(dims, support, heads, segments, with_k_read, 
         floor = O.GRAD_ATOL[dtype] * e.numel() ** 0.5
         rel = ((g_.double().cpu() - e).norm() / e.norm().clamp_min(floor)).item()
         assert rel < GRAD_REL_NORM[dtype], f"{name}: relative norm error {rel}"
+
+
+@pytest.mark.parametrize("dtype", (torch.float16, torch.bfloat16), ids=("fp16", "bf16"))
+@pytest.mark.parametrize("shape,tail_len", (((2, 300, 2, 64), 0), ((3, 257, 1, 96), 100), ((1, 4099, 4, 128), 4099),
+                                            ((2, 5, 3, 8), 1)))
+def test_merge_gradients_is_an_fp32_sum_rounded_once(shape, tail_len, dtype, cuda_device):
+    """out = a + b (+ tail on the last rows of each batch row), bit for bit the FP32 sum rounded to the dtype
+    (the role of _softdelta_merge_gradients, xattn/ops/softdelta_attention.py:506-516)."""
+    from xattn_b200 import _native
+    gen = torch.Generator(device="cpu").manual_seed(17)
+    a = torch.randn(shape, generator=gen).to(device=cuda_device, dtype=dtype)
+    b = (torch.randn(shape, generator=gen) * 3).to(device=cuda_device, dtype=dtype)
+    tail = None
+    expected = a.float() + b.float()
+    if tail_len:
+        tail = torch.randn((shape[0], tail_len, *shape[2:]), generator=gen).to(device=cuda_device, dtype=dtype)
+        expected[:, shape[1] - tail_len:] += tail.float()
+    out = _native.softdelta_merge_gradients(a, b, tail)
+    assert out.dtype == dtype and torch.equal(out, expected.to(dtype))

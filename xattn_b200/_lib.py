@@ -90,6 +90,15 @@ class ConstantKeyArgs(C.Structure):
     ]
 
 
+class MergeArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int),
+        ("batch", C.c_int64), ("k_len", C.c_int64), ("kv_heads", C.c_int64), ("dim", C.c_int64),
+        ("a", C.c_void_p), ("b", C.c_void_p), ("tail", C.c_void_p), ("tail_len", C.c_int64),
+        ("out", C.c_void_p),
+    ]
+
+
 _lock = threading.Lock()
 _lib: Optional[C.CDLL] = None
 
@@ -110,6 +119,7 @@ SYMBOLS = {
     "xattn_b200_softdelta_gate_fwd": (C.c_int, [C.POINTER(GateArgs), C.c_void_p]),
     "xattn_b200_softdelta_gate_bwd": (C.c_int, [C.POINTER(GateArgs), C.c_void_p]),
     "xattn_b200_zero_constant_key_rows": (C.c_int, [C.POINTER(ConstantKeyArgs), C.c_void_p]),
+    "xattn_b200_softdelta_merge_gradients": (C.c_int, [C.POINTER(MergeArgs), C.c_void_p]),
     "xattn_b200_profile_enable": (C.c_int, [C.c_int]),
     "xattn_b200_profile_read": (C.c_int, [C.POINTER(C.c_int), C.POINTER(C.c_float), C.c_int]),
     "xattn_b200_check_status": (C.c_int, [C.c_void_p, C.c_void_p]),

@@ -304,6 +304,25 @@ def zero_constant_key_rows(dq: Tensor, k_all: Tensor, plan: Tensor) -> Tensor:
     return dq
 
 
+def softdelta_merge_gradients(a: Tensor, b: Tensor, tail: Optional[Tensor] = None) -> Tensor:
+    """a + b (+ ``tail`` on the last rows of every batch row), summed in FP32 and rounded once; [B, L, H, D]
+    tensors of the input dtype.  Returns a new tensor."""
+    lib = _lib.load()
+    a, b = a.contiguous(), b.contiguous()
+    out = torch.empty_like(a)
+    args = _lib.MergeArgs()
+    args.dtype = _DTYPES[a.dtype]
+    args.batch, args.k_len, args.kv_heads, args.dim = a.shape
+    args.a, args.b, args.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    if tail is not None:
+        tail = tail.contiguous()
+        args.tail, args.tail_len = tail.data_ptr(), tail.shape[1]
+    with torch.cuda.device(a.device):
+        _lib.check(lib.xattn_b200_softdelta_merge_gradients(C.byref(args), _stream_ptr()),
+                   "xattn_b200_softdelta_merge_gradients")
+    return out
+
+
 def _gate_args(g: Tensor, neg_read: Tensor, q_heads: int) -> "_lib.GateArgs":
     """``g`` is [B, L, H] (one gate per head) or [B, L, H, C] (one per group of V / C channels)."""
     args = _lib.GateArgs()

@@ -11,6 +11,7 @@ int bwd_entry(const XattnBwdArgs* a, cudaStream_t stream);
 int gate_fwd_entry(const XattnGateArgs* a, cudaStream_t stream);
 int gate_bwd_entry(const XattnGateArgs* a, cudaStream_t stream);
 int zero_constant_entry(const XattnConstantKeyArgs* a, cudaStream_t stream);
+int merge_gradients_entry(const XattnMergeArgs* a, cudaStream_t stream);
 int build_plan_entry(const XattnPlanArgs* a, cudaStream_t stream);
 int build_varlen_plan_entry(const XattnVarlenPlanArgs* a, cudaStream_t stream);
 }  // namespace xb
@@ -75,6 +76,10 @@ int xattn_b200_softdelta_gate_bwd(const XattnGateArgs* args, xattn_stream_t stre
 
 int xattn_b200_zero_constant_key_rows(const XattnConstantKeyArgs* args, xattn_stream_t stream) {
   return xb::zero_constant_entry(args, static_cast<cudaStream_t>(stream));
+}
+
+int xattn_b200_softdelta_merge_gradients(const XattnMergeArgs* args, xattn_stream_t stream) {
+  return xb::merge_gradients_entry(args, static_cast<cudaStream_t>(stream));
 }
 
 int xattn_b200_profile_enable(int enable) { return xb::profile_enable(enable); }

@@ -228,6 +228,45 @@ __global__ void __launch_bounds__(kGateThreads) gate_bwd_kernel(const T* __restr
     if (ln.on(ps)) store8<T>(dneg + ln.unit(ps) * V + ln.c, dn[ps]);
 }
 
+// ---- SoftDelta gradient merge -------------------------------------------------
+// out = a + b (+ tail on the last rows of each batch row), FP32 sum, one rounding.  A thread takes
+// kMergeChunks 16-byte chunks a block-width apart, all loads first; blockIdx.y is the batch row.
+constexpr int kMergeChunks = 4;
+template <typename T>
+__global__ void __launch_bounds__(256) merge_gradients_kernel(const T* __restrict__ a, const T* __restrict__ b,
+                                                              const T* __restrict__ tail, T* __restrict__ out,
+                                                              long long per_batch, long long tail_start,
+                                                              long long tail_per_batch, int B) {
+  for (int bi = blockIdx.y; bi < B; bi += gridDim.y) {
+    const long long base = (long long)bi * per_batch;
+    const long long i0 = ((long long)blockIdx.x * kMergeChunks * blockDim.x + threadIdx.x) * 8;
+    uint4 ra[kMergeChunks], rb[kMergeChunks], rt[kMergeChunks];
+#pragma unroll
+    for (int u = 0; u < kMergeChunks; ++u) {
+      const long long i = i0 + (long long)u * blockDim.x * 8;
+      ra[u] = rb[u] = rt[u] = make_uint4(0, 0, 0, 0);
+      if (i < per_batch) {
+        ra[u] = *reinterpret_cast<const uint4*>(a + base + i);       // out may be a: no read-only path
+        rb[u] = __ldg(reinterpret_cast<const uint4*>(b + base + i));
+        if (tail && i >= tail_start)
+          rt[u] = __ldg(reinterpret_cast<const uint4*>(tail + (long long)bi * tail_per_batch + (i - tail_start)));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kMergeChunks; ++u) {
+      const long long i = i0 + (long long)u * blockDim.x * 8;
+      if (i >= per_batch) continue;
+      float fa[8], fb[8], ft[8];
+      unpack8<T>(ra[u], fa);
+      unpack8<T>(rb[u], fb);
+      unpack8<T>(rt[u], ft);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) fa[e] = (fa[e] + fb[e]) + ft[e];
+      store8<T>(out + base + i, fa);
+    }
+  }
+}
+
 // ---- constant-key rows ------------------------------------------------------
 // flag[b][kvh][j] = 1 when key j differs (bitwise) from key j-1, or j == 0
 template <typename T>
@@ -353,6 +392,34 @@ int gate_bwd_entry(const XattnGateArgs* a, cudaStream_t s) {
   if (a->dtype == XATTN_DTYPE_BF16) launch_gate_bwd<__nv_bfloat16>(a, s); else launch_gate_bwd<__half>(a, s);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("gate backward launch: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
+  return XATTN_OK;
+}
+
+int merge_gradients_entry(const XattnMergeArgs* a, cudaStream_t s) {
+  if (!a || !a->a || !a->b || !a->out) { set_error("null arguments"); return XATTN_E_INVALID; }
+  if (a->dtype != XATTN_DTYPE_F16 && a->dtype != XATTN_DTYPE_BF16) { set_error("dtype must be fp16 or bf16"); return XATTN_E_INVALID; }
+  if (a->batch <= 0 || a->k_len <= 0 || a->kv_heads <= 0 || a->dim <= 0 || a->dim % 8 ||
+      (a->tail && (a->tail_len <= 0 || a->tail_len > a->k_len))) { set_error("bad merge sizes"); return XATTN_E_INVALID; }
+  const uintptr_t align = reinterpret_cast<uintptr_t>(a->a) | reinterpret_cast<uintptr_t>(a->b) |
+                          reinterpret_cast<uintptr_t>(a->out) | reinterpret_cast<uintptr_t>(a->tail);
+  if (align & 15) { set_error("merge tensors must be 16-byte aligned"); return XATTN_E_INVALID; }
+  const long long row = a->kv_heads * a->dim;
+  const long long per_batch = a->k_len * row;
+  const long long tail_per_batch = a->tail ? a->tail_len * row : 0;
+  const long long tail_start = per_batch - tail_per_batch;
+  const long long per_block = 256LL * kMergeChunks * 8;
+  const long long blocks = (per_batch + per_block - 1) / per_block;
+  if (blocks > 0x7fffffffLL) { set_error("merge grid out of range"); return XATTN_E_INVALID; }
+  const dim3 grid((unsigned)blocks, (unsigned)(a->batch < 65535 ? a->batch : 65535));
+  ProfileScope prof(kProfGate, s);
+  if (a->dtype == XATTN_DTYPE_BF16)
+    merge_gradients_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)a->a, (const __nv_bfloat16*)a->b, (const __nv_bfloat16*)a->tail,
+                                                            (__nv_bfloat16*)a->out, per_batch, tail_start, tail_per_batch, (int)a->batch);
+  else
+    merge_gradients_kernel<__half><<<grid, 256, 0, s>>>((const __half*)a->a, (const __half*)a->b, (const __half*)a->tail, (__half*)a->out,
+                                                     per_batch, tail_start, tail_per_batch, (int)a->batch);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_error("merge launch: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
   return XATTN_OK;
 }
 

@@ -163,13 +163,10 @@ def _backward(dy, q, k, v, g, k_read, prev_k, prev_v, q_ids, k_ids, y, neg_read,
     if hp:
         dq = _native.zero_constant_key_rows(dq, k_all, plan_inc)
         dkr = _native.zero_constant_key_rows(dkr, k_all, plan_strict)
-    dk_all = (dk1.float() + dk2.float())
-    dv_all = (dv1.float() + dv2.float()).to(q.dtype)
-    dk_read = dkr
-    if k_read is None:
-        dk_all[:, dk_all.shape[1] - L:] += dkr.float()
-        dk_read = None
-    dk_all = dk_all.to(q.dtype)
+    # FP32 sums rounded once; the aligned keys' own gradient folds into the last L rows of dK
+    dk_all = _native.softdelta_merge_gradients(dk1, dk2, dkr if k_read is None else None)
+    dv_all = _native.softdelta_merge_gradients(dv1, dv2)
+    dk_read = None if k_read is None else dkr
     if prev_k is None:
         return dq, dk_all, dv_all, dg, dk_read, None, None
     p = prev_k.shape[1]
