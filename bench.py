@@ -68,6 +68,13 @@ WORKLOADS = {
     # ring of K/V blocks, every rank computes half a block per step
     "ring_causal": dict(B=1, S=32768, Hq=32, Hkv=8, D=128, segments=False, ring=True,
                         text="causal fwd+bwd bf16 B=1 S=32768 Hq=32 Hkv=8 D=128, one sequence sharded over the ranks (zig-zag ring of K/V blocks)"),
+    # configs[3] and configs[4]: device-resident timing only (no host-buffer leg)
+    "sca_c4": dict(B=2, S=16384, Hq=16, Hkv=1, D=128, segments=False, other="sca", span=2048, dtype="fp16", std=0.5,
+                   text="configs[3]: sliding-chunk fwd+bwd fp16 MQA B=2 S=16384 Hq=16 Hkv=1 D=128 chunk=2048, BOS every ~U[1024,8192] tokens"),
+    "softdelta_c5": dict(B=2, S=8192, Hq=16, Hkv=16, D=128, segments=False, other="softdelta", dtype="bf16", std=1.0,
+                         text="configs[4]: SoftDelta fwd+bwd bf16 B=2 S=8192 Hq=Hkv=16 D=128, gates ~U(0,1)"),
+    "sw_softdelta_c5": dict(B=2, S=8192, Hq=16, Hkv=16, D=128, segments=False, other="softdelta", span=2048, dtype="bf16", std=1.0,
+                            text="configs[4]: sliding-window SoftDelta fwd+bwd bf16 B=2 S=8192 Hq=Hkv=16 D=128 window=2048, gates ~U(0,1)"),
     # one new token per sequence against a long key cache: forward only, HBM-bound (K and V are
     # streamed once); reported in GB/s of K + V + q + y bytes, not in the headline metric
     "decode": dict(B=8, S=32768, Hq=32, Hkv=8, D=128, segments=False, decode=True,
@@ -224,6 +231,8 @@ def run_ours(args, w):
         return run_swa_sharded(args, w, world, rank, dev)
     if w.get("decode"):
         return run_decode(args, w, world, rank, dev)
+    if w.get("other"):
+        return run_other(args, w, world, rank, dev)
     host = make_host_inputs(w, seed=1 + rank)
     pinned = [None if t is None else t.pin_memory() for t in host]
     q, k, v, dy, ids = (None if t is None else t.to(dev) for t in pinned)
@@ -476,6 +485,116 @@ def run_decode(args, w, world, rank, dev):
         dist.destroy_process_group()
 
 
+def run_other(args, w, world, rank, dev):
+    """configs[3] (sliding chunk, fp16, MQA, BOS packing) and configs[4] (SoftDelta and its sliding-window form):
+    forward + backward through the public ops with inputs resident in HBM; every rank runs its own batch."""
+    import torch.distributed as dist
+    import xattn_b200 as xattn
+    from xattn_b200 import _native
+
+    B, S, Hq, Hkv, D = w["B"], w["S"], w["Hq"], w["Hkv"], w["D"]
+    dt = torch.float16 if w["dtype"] == "fp16" else torch.bfloat16
+    gen = torch.Generator().manual_seed(3 + rank)
+    draw = lambda *shape: (torch.randn(shape, generator=gen) * w["std"]).to(dev, dt)
+    q, k, v, dy = draw(B, S, Hq, D), draw(B, S, Hkv, D), draw(B, S, Hkv, D), draw(B, S, Hq, D)
+    level = args.level
+
+    def count_pairs(**plan_kw):
+        plan = _native.build_plan(B, S, S, dev, **plan_kw)
+        n = B * S
+        r4 = (n + 3) // 4 * 4
+        return int((plan[r4:r4 + n].long() - plan[:n].long()).clamp_min(0).sum().item())
+
+    if w["other"] == "sca":
+        bos = torch.zeros(B, S, dtype=torch.bool)
+        bos[:, 0] = True
+        for b in range(B):
+            pos = 0
+            while True:
+                pos += int(torch.randint(1024, 8193, (1,), generator=gen))
+                if pos >= S:
+                    break
+                bos[b, pos] = True
+        bos = bos.to(dev)
+        ids = bos.cumsum(1)
+        pairs = Hq * count_pairs(visibility="chunk", span=w["span"], q_segment_idx=ids, k_segment_idx=ids)
+
+        def step():
+            y, lse = xattn.flash_sca_fwd(q, k, v, w["span"], bos_mask=bos, high_precision_level=level)
+            return xattn.flash_sca_bwd(dy, q, k, v, y, lse, w["span"], bos_mask=bos, high_precision_level=level)
+    else:
+        gate = torch.rand(B, S, Hq, generator=gen).to(dev, dt)
+        span = w.get("span")
+        vis = dict(visibility="window", span=span) if span else {}
+        # the query read over query heads plus the strict-past read over KV heads
+        pairs = Hq * count_pairs(**vis) + Hkv * count_pairs(strict_past=True, **vis)
+
+        def step():
+            leaves = [t.detach().requires_grad_() for t in (q, k, v, gate)]
+            if span:
+                y = xattn.sliding_window_softdelta_attention(q=leaves[0], k=leaves[1], k_read=None, v=leaves[2], g=leaves[3],
+                                                             window_size=span, high_precision_level=level)
+            else:
+                y = xattn.softdelta_attention(q=leaves[0], k=leaves[1], k_read=None, v=leaves[2], g=leaves[3],
+                                              high_precision_level=level)
+            return torch.autograd.grad(y, leaves, dy)
+
+    flops_step = 14 * D * pairs
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    _native.check_status()
+    sampler = ClockSampler(dev.index)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    _native.profile_enable(True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    _native.profile_enable(False)
+    records = _native.profile_read()
+    clocks = sampler.stop()
+    _native.check_status()
+    times = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_step = float(times[0])
+    if rank == 0:
+        peaks, peak_src = measured_peaks()
+        peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
+        per_kind = {}
+        for kind, ms in records:
+            per_kind.setdefault(kind, []).append(ms)
+        kernels = {kd: {"launches": len(vs), "ms_per_step": sum(vs) / args.steps, "share": sum(vs) / (ms_step * args.steps)}
+                   for kd, vs in per_kind.items()}
+        dkv_ms = kernels.get("bwd_dkv", {"ms_per_step": float("inf")})["ms_per_step"]
+        achieved = 8 * D * pairs / dkv_ms * 1e-9
+        print(json.dumps({
+            "metric": "attn fwd+bwd TFLOPS, whole job", "value": world * flops_step / ms_step * 1e-9, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": w["text"], "high_precision_level": level, "l2": "tensors of one step exceed the 126 MB L2",
+                       "visible_pairs_per_step": pairs, "flops_per_step": flops_step,
+                       "parallelism": f"batch sharded over {world} GPU(s), no communication"},
+            "gpu_launches": len(records) + 3 * len(per_kind.get("plan", [])), "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": "bwd_dkv (all its launches of a step)", "achieved": achieved,
+                         "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": f"{peak_src} bf16_tflops_sustained"},
+            "kernels": kernels,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_swa_sharded(args, w, world, rank, dev):
     """One sequence of S tokens split over the ranks, total work fixed: configs[2] (sliding window,
     contiguous slices, K/V halo exchange) or the causal ring (zig-zag slices)."""
@@ -599,11 +718,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--workload", default="causal_c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--level", type=int, default=0, choices=(0, 1),
+                    help="high_precision_level of the sca_c4 / softdelta_c5 / sw_softdelta_c5 workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
-    if args.impl == "reference" and (w.get("decode") or w["S"] > 8192):
+    if args.impl == "reference" and (w.get("decode") or w.get("other") or w["S"] > 8192):
         print(json.dumps({"impl": "reference", "unavailable": "the CPU arm runs the causal S=8192 workloads: one "
                           "(batch row, head) slice of a 32768-token sequence needs 4.3 GB per score matrix in fp32"}))
     elif args.impl == "reference":
