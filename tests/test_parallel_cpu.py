@@ -127,7 +127,7 @@ def test_sequence_sharding_matches_unsharded_oracle(mode, world):
         for p in procs:
             p.start()
         for p in procs:
-            p.join(timeout=120)
+            p.join(timeout=300)
         for p in procs:
             assert p.exitcode == 0, f"rank exited with {p.exitcode}"
         assert len(results) == world
