@@ -49,3 +49,26 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "absent.so"))
     with pytest.raises(ImportError, match="no CPU fallback"):
         _lib.load()
+
+
+def test_header_is_plain_c_and_structs_match_ctypes(tmp_path):
+    """include/xattn_b200.h compiles as C11 on its own, and the ctypes mirrors have the C sizes."""
+    import shutil
+    import subprocess
+    import ctypes as C
+    from xattn_b200 import _lib
+    if shutil.which("gcc") is None:
+        pytest.skip("gcc not available")
+    names = {"XattnPlanArgs": _lib.PlanArgs, "XattnVarlenPlanArgs": _lib.VarlenPlanArgs, "XattnFwdArgs": _lib.FwdArgs,
+             "XattnBwdArgs": _lib.BwdArgs, "XattnGateArgs": _lib.GateArgs, "XattnConstantKeyArgs": _lib.ConstantKeyArgs,
+             "XattnMergeArgs": _lib.MergeArgs}
+    src = tmp_path / "sizes.c"
+    body = "\n".join(f'  printf("{n} %zu\\n", sizeof({n}));' for n in names)
+    src.write_text('#include <stdio.h>\n#include "xattn_b200.h"\nint main(void) {\n' + body + "\n  return 0;\n}\n")
+    exe = tmp_path / "sizes"
+    include = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include")
+    subprocess.run(["gcc", "-std=c11", "-Wall", "-Werror", "-I", include, str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    sizes = dict(zip(out[::2], map(int, out[1::2])))
+    for name, mirror in names.items():
+        assert sizes[name] == C.sizeof(mirror), name
