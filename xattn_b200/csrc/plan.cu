@@ -104,11 +104,8 @@ struct RowArgs {
   int* row_lo; int* row_hi;
 };
 
-__global__ void __launch_bounds__(256) plan_rows_kernel(const RowArgs a) {
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (long long)a.B * a.Lq) return;
-  const int b = (int)(idx / a.Lq);
-  const int i = (int)(idx - (long long)b * a.Lq);
+// visible-key interval of query row i of batch row b (idx = b * Lq + i)
+__device__ __forceinline__ void row_interval(const RowArgs& a, int b, int i, long long idx, int& out_lo, int& out_hi) {
   long long k_start = 0, k_end = a.Lk;
   if (a.q_seg) {
     const int64_t id = a.q_seg[(size_t)b * a.q_seg_stride + i];
@@ -131,8 +128,70 @@ __global__ void __launch_bounds__(256) plan_rows_kernel(const RowArgs a) {
   if (lo < k_start) lo = k_start;
   if (hi > k_end) hi = k_end;
   if (hi <= lo) { lo = 0; hi = 0; }
-  a.row_lo[idx] = (int)lo;
-  a.row_hi[idx] = (int)hi;
+  out_lo = (int)lo;
+  out_hi = (int)hi;
+}
+
+__global__ void __launch_bounds__(256) plan_rows_kernel(const RowArgs a) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)a.B * a.Lq) return;
+  const int b = (int)(idx / a.Lq);
+  const int i = (int)(idx - (long long)b * a.Lq);
+  int lo, hi;
+  row_interval(a, b, i, idx, lo, hi);
+  a.row_lo[idx] = lo;
+  a.row_hi[idx] = hi;
+}
+
+// The whole plan of a batch row in one block when the queries fit one tile (decode shapes, where the
+// four launches of the general path cost as much as the attention itself): row intervals, the one
+// query-tile summary, the key tiles it touches, and the identity as key-tile order (every key tile is
+// seen by at most one query tile, so there is nothing to sort).  128 threads; blockIdx.x = batch row.
+__global__ void __launch_bounds__(128) plan_one_tile_kernel(const RowArgs a, int nKT, TileInfo* q_tiles,
+                                                            KeyTileInfo* k_tiles, int* k_order) {
+  __shared__ int red[4][4];
+  __shared__ int any_empty_s[4];
+  const int b = blockIdx.x, i = threadIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int min_lo = INT_MAX, max_hi = 0, max_lo = 0, min_hi = INT_MAX;
+  bool any_empty = false;
+  if (i < a.Lq) {
+    const long long idx = (long long)b * a.Lq + i;
+    int lo, hi;
+    row_interval(a, b, i, idx, lo, hi);
+    a.row_lo[idx] = lo;
+    a.row_hi[idx] = hi;
+    if (hi > lo) { min_lo = lo; max_hi = hi; max_lo = lo; min_hi = hi; } else { any_empty = true; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    min_lo = min(min_lo, __shfl_xor_sync(0xffffffffu, min_lo, o));
+    max_hi = max(max_hi, __shfl_xor_sync(0xffffffffu, max_hi, o));
+    max_lo = max(max_lo, __shfl_xor_sync(0xffffffffu, max_lo, o));
+    min_hi = min(min_hi, __shfl_xor_sync(0xffffffffu, min_hi, o));
+  }
+  any_empty = __any_sync(0xffffffffu, any_empty);
+  if (lane == 0) {
+    red[warp][0] = min_lo; red[warp][1] = max_hi; red[warp][2] = max_lo; red[warp][3] = min_hi;
+    any_empty_s[warp] = any_empty ? 1 : 0;
+  }
+  __syncthreads();
+  min_lo = min(min(red[0][0], red[1][0]), min(red[2][0], red[3][0]));
+  max_hi = max(max(red[0][1], red[1][1]), max(red[2][1], red[3][1]));
+  max_lo = max(max(red[0][2], red[1][2]), max(red[2][2], red[3][2]));
+  min_hi = min(min(red[0][3], red[1][3]), min(red[2][3], red[3][3]));
+  any_empty = (any_empty_s[0] | any_empty_s[1] | any_empty_s[2] | any_empty_s[3]) != 0;
+  TileInfo t;
+  if (max_hi == 0) { t.min_lo = 0; t.max_hi = 0; t.max_lo = INT_MAX; t.min_hi = 0; }
+  else { t.min_lo = min_lo; t.max_hi = max_hi; t.max_lo = any_empty ? INT_MAX : max_lo; t.min_hi = min_hi; }
+  if (threadIdx.x == 0) q_tiles[b] = t;
+  for (int kt = threadIdx.x; kt < nKT; kt += blockDim.x) {
+    const int k0 = kt * kBlockN, k1 = k0 + kBlockN;
+    const bool seen = t.max_hi > t.min_lo && t.min_lo < k1 && t.max_hi > k0;
+    KeyTileInfo k;
+    k.m_first = 0;
+    k.m_end = seen ? 1 : 0;
+    k_tiles[(size_t)b * nKT + kt] = k;
+    k_order[(size_t)b * nKT + kt] = b * nKT + kt;
+  }
 }
 
 struct VarlenRowArgs {
@@ -297,6 +356,13 @@ int build_plan_entry(const XattnPlanArgs* a, cudaStream_t stream) {
     // its own slot before overwriting it
     run_bounds_kernel<<<B, 256, 0, stream>>>(a->q_segment, a->q_segment_stride, Lq, r.row_lo, r.row_hi);
     r.q_run_start = r.row_lo; r.q_run_end = r.row_hi;
+  }
+  if (Lq <= kBlockM && !r.reset) {
+    plan_one_tile_kernel<<<B, 128, 0, stream>>>(r, (int)pl.nKT, reinterpret_cast<TileInfo*>(a->plan + pl.off_qt),
+                                               reinterpret_cast<KeyTileInfo*>(a->plan + pl.off_kt), a->plan + pl.off_ko);
+    cudaError_t e1 = cudaGetLastError();
+    if (e1 != cudaSuccess) { set_error("plan launch: %s", cudaGetErrorString(e1)); return XATTN_E_CUDA; }
+    return XATTN_OK;
   }
   plan_rows_kernel<<<ceil_div(B * Lq, 256), 256, 0, stream>>>(r);
   cudaError_t e = cudaGetLastError();
