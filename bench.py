@@ -370,8 +370,8 @@ def run_ours(args, w):
         per_kind = {}
         for kind, ms in records:
             per_kind.setdefault(kind, []).append(ms)
-        launches = len(records)  # plan scopes hold three small kernels each
-        launches += 2 * len(per_kind.get("plan", []))
+        launches = len(records)  # one record per scope; a plan scope holds four small kernels
+        launches += 3 * len(per_kind.get("plan", []))
         # algorithmic FLOPs per launch: forward 4*D*P; in the backward the dQ kernel's S / dP
         # products repeat the dK/dV kernel's, so only its dQ product is new work
         algo = {"fwd": 4 * D * pairs, "bwd_dq": 2 * D * pairs, "bwd_dkv": 8 * D * pairs}
@@ -472,7 +472,8 @@ def run_decode(args, w, world, rank, dev):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": w["text"], "l2": "K and V (1.07 GB per step) exceed the 126 MB L2",
                        "bytes_per_step": nbytes, "parallelism": f"batch sharded over {world} GPU(s), no communication"},
-            "gpu_launches": 2 * len(fwd) + 3 * len([1 for kind, _ in records if kind == "plan"]),
+            # a forward scope holds the split kernel and the merge kernel, a one-tile plan is one kernel
+            "gpu_launches": 2 * len(fwd) + len([1 for kind, _ in records if kind == "plan"]),
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "fwd (decode shape) + merge", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_DECODE,
@@ -585,7 +586,9 @@ def run_other(args, w, world, rank, dev):
             "config": {"workload": w["text"], "high_precision_level": level, "l2": "tensors of one step exceed the 126 MB L2",
                        "visible_pairs_per_step": pairs, "flops_per_step": flops_step,
                        "parallelism": f"batch sharded over {world} GPU(s), no communication"},
-            "gpu_launches": len(records) + 3 * len(per_kind.get("plan", [])), "clocks": clocks,
+            # a plan scope holds four kernels, a level-1 repair scope three, every other scope one
+            "gpu_launches": len(records) + 3 * len(per_kind.get("plan", [])) + 2 * len(per_kind.get("repair", [])),
+            "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "bwd_dkv (all its launches of a step)", "achieved": achieved,
                          "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
                          "peak_source": f"{peak_src} bf16_tflops_sustained"},
@@ -701,7 +704,7 @@ def run_swa_sharded(args, w, world, rank, dev):
             "e2e": None if not e2e_steps else {"value": flops_step / e2e_ms * 1e-9, "unit": "TFLOP/s",
                                                "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                                                "d2h_bytes_per_step": d2h, "steps": e2e_steps},
-            "gpu_launches": len(records) + 2 * len(per_kind.get("plan", [])),
+            "gpu_launches": len(records) + 3 * len(per_kind.get("plan", [])),
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "bwd_dkv", "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
