@@ -199,3 +199,28 @@ def test_training_step_runs_as_a_cuda_graph(cuda_device):
     for a, b in zip(outs, eager):
         assert torch.equal(a, b)
     xattn.check_status()
+
+
+@pytest.mark.parametrize("operation", ("causal_flash_attn", "flash_swa", "flash_sca"))
+def test_level1_autograd_equals_standalone_backward(operation, cuda_device):
+    """The autograd path reuses the level-1 forward's statistics, the standalone backward recomputes them:
+    both give the same bits."""
+    B, L, Hq, Hkv, D = 2, 389, 4, 2, 64
+    gen = torch.Generator().manual_seed(9)
+    mk = lambda *s: torch.randn(s, generator=gen).to(device=cuda_device, dtype=torch.bfloat16)
+    q, k, v, dy = mk(B, L, Hq, D), mk(B, L, Hkv, D), mk(B, L, Hkv, D), mk(B, L, Hq, D)
+    ids = (torch.arange(L, device=cuda_device) // 150).expand(B, -1).contiguous()
+    extra = {"causal_flash_attn": {}, "flash_swa": {"window_size": 100}, "flash_sca": {"chunk_size": 64}}[operation]
+    leaves = [t.clone().requires_grad_() for t in (q, k, v)]
+    y = getattr(xattn, operation)(*leaves, **extra, segment_idx=ids, high_precision_level=1)
+    grads = torch.autograd.grad(y, leaves, dy)
+    y2, lse = getattr(xattn, operation + "_fwd")(q, k, v, **extra, segment_idx=ids, high_precision_level=1)
+    assert torch.equal(y, y2)
+    alone = getattr(xattn, operation + "_bwd")(dy, q, k, v, y2, lse, **extra, segment_idx=ids, high_precision_level=1)
+    for a, b in zip(grads, alone[:3]):
+        assert torch.equal(a, b)
+    # the standalone backward does not trust what it is given: level-0 statistics give the same result
+    y0, lse0 = getattr(xattn, operation + "_fwd")(q, k, v, **extra, segment_idx=ids, high_precision_level=0)
+    other = getattr(xattn, operation + "_bwd")(dy, q, k, v, y0, lse0, **extra, segment_idx=ids, high_precision_level=1)
+    for a, b in zip(grads, other[:3]):
+        assert torch.equal(a, b)

@@ -64,15 +64,17 @@ def backward(
     dy: Tensor, q: Tensor, k: Tensor, v: Tensor, y: Tensor, lse: Tensor, support: Support, scale: float,
     prev_k: Optional[Tensor], prev_v: Optional[Tensor],
     q_segment_idx: Optional[Tensor], k_segment_idx: Optional[Tensor],
-    *, high_precision: bool = False, plan: Optional[Tensor] = None,
+    *, high_precision: bool = False, plan: Optional[Tensor] = None, recompute: bool = True,
 ) -> Tuple[Tensor, Tensor, Tensor, Optional[Tensor], Optional[Tensor]]:
-    """(dq, dk, dv, dprev_k, dprev_v).  At level 1 the saved ``y`` / ``lse`` are ignored and the
+    """(dq, dk, dv, dprev_k, dprev_v).  At level 1 the given ``y`` / ``lse`` are ignored and the
     statistics are recomputed with the high-precision softmax
-    (xattn/ops/causal_flash_attn.py:144-147)."""
+    (xattn/ops/causal_flash_attn.py:144-147), unless the caller vouches that they already come from
+    that forward on these inputs (``recompute=False``: the autograd path, where the recomputation
+    would reproduce the saved tensors bit for bit)."""
     k_all, v_all = concat_previous(k, v, prev_k, prev_v)
     if plan is None:        # the autograd path hands over the forward's plan
         plan = make_plan(q, k_all.shape[1], support, q_segment_idx, k_segment_idx)
-    if high_precision:
+    if high_precision and recompute:
         y, lse = _native.attention_fwd(q, k_all, v_all, plan, scale, high_precision=True)
     dq, dk_all, dv_all = _native.attention_bwd(dy, q, k_all, v_all, y, lse, plan, scale)
     if high_precision:
@@ -99,7 +101,7 @@ class AttentionFunction(torch.autograd.Function):
     def backward(ctx, dy):
         q, k, v, y, lse, prev_k, prev_v, q_seg, k_seg, plan = ctx.saved_tensors
         dq, dk, dv, dpk, dpv = backward(dy, q, k, v, y, lse, ctx.support, ctx.scale, prev_k, prev_v,
-                                        q_seg, k_seg, high_precision=bool(ctx.level), plan=plan)
+                                        q_seg, k_seg, high_precision=bool(ctx.level), plan=plan, recompute=False)
         return dq, dk, dv, dpk, dpv, None, None, None, None, None
 
 
