@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define XATTN_B200_ABI_VERSION 1
+#define XATTN_B200_ABI_VERSION 2
 
 enum {
   XATTN_OK = 0,
@@ -82,6 +82,12 @@ typedef struct {
   int64_t q_segment_stride;      /* elements between batch rows                */
   int64_t k_segment_stride;
   int32_t* plan;                 /* xattn_b200_plan_bytes() bytes              */
+  int32_t* status;               /* optional status word.  Key ids must never decrease along a row
+                                    (the contract of csrc/attention/partition/segment_index.h:362-363:
+                                    the keys of one id are found by binary search).  When given, the
+                                    plan kernels also compare neighbouring key ids (one more pass
+                                    over k_segment) and store (batch row << 8) | 3 on a decrease;
+                                    NULL skips the check                        */
 } XattnPlanArgs;
 
 /* Builds the plan for dense [B, L, H, D] inputs.
@@ -136,6 +142,11 @@ typedef struct {
   float* lse;                    /* [B][Hq][q_len]                             */
   float* y_state;                /* optional FP32 copy of y, same shape, or NULL */
   int32_t* status;               /* one word, zero on entry                    */
+  int32_t* anchor;               /* optional, high_precision only: [B][Hq][q_len], the visible key with
+                                    the row's largest logit (the first of equals; -1 for a row without
+                                    keys) — the anchor of the reference's row statistics
+                                    (csrc/attention/precision/row_statistics_sm90.cuh:144-186), which
+                                    the high-precision backward centres dP on          */
 } XattnFwdArgs;
 
 int xattn_b200_fwd(const XattnFwdArgs* args, xattn_stream_t stream);
@@ -191,9 +202,26 @@ typedef struct {
   void* dv;                      /* [B][k_len][Hkv][V] contiguous              */
   float* workspace;              /* xattn_b200_bwd_workspace_bytes() bytes     */
   int32_t* status;
+  int high_precision;            /* 1: the anchored backward (below); y is not read then */
+  const int32_t* anchor;         /* high_precision: [B][Hq][q_len] from the forward */
+  const float* grad_unscale;     /* optional device scalar multiplied into dq, dk and dv before they are
+                                    rounded (undoes a power-of-two prescale of dy, the reference's
+                                    xattn/ops/_precision_backend.py:203-225), or NULL  */
 } XattnBwdArgs;
 
+/* With high_precision = 1 the backward restates the reference's precision pipeline
+ * (xattn/ops/_precision_backend.py:29-170) on this library's kernels: `lse` and `anchor` must come
+ * from the high-precision forward on the same inputs; dP is centred on each row's anchor key
+ * (dP_ia = dO_i . V_a, computed directly), a statistics pass computes
+ * Delta_i = sum_j P_ij (dP_ij - dP_ia) (csrc/attention/precision/row_statistics_sm90.cuh:39-188), and both
+ * mainloops use dS_ij = P_ij ((dP_ij - dP_ia) - Delta_i) with P = root * root,
+ * root = exp2((s_ij c - lse2) / 2), so that a probability below the FP32 normal range still meets a
+ * huge dP correctly, and with the centred value exactly zero on the anchor.  The workspace needs
+ * xattn_b200_bwd_workspace_bytes_hp() bytes.  Not reproduced: the split hi / lo operands and the
+ * FP64 row sums with zero-sum and probability repair (csrc/attention/precision/zero_sum_repair.cu,
+ * probability_repair.cu); the operands of the dV / dK / dQ products are rounded once. */
 size_t xattn_b200_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);
+size_t xattn_b200_bwd_workspace_bytes_hp(int64_t batch, int64_t q_heads, int64_t q_len);
 int xattn_b200_bwd(const XattnBwdArgs* args, xattn_stream_t stream);
 
 /* The same backward for callers that may not allocate device memory (no counterpart in the
@@ -275,7 +303,7 @@ int xattn_b200_softdelta_merge_gradients(const XattnMergeArgs* args, xattn_strea
  * its kernels with CUDA events on the launch stream.  xattn_b200_profile_read() synchronises
  * those events, writes (kind, milliseconds) pairs and clears the log; it returns the number of
  * records written.  Kinds: 1 plan, 2 forward, 3 backward preprocess, 4 backward dQ,
- * 5 backward dK/dV, 6 SoftDelta gate, 7 constant-key repair. */
+ * 5 backward dK/dV, 6 SoftDelta gate, 7 constant-key repair, 8 high-precision row statistics. */
 int xattn_b200_profile_enable(int enable);
 int xattn_b200_profile_read(int* kinds, float* ms, int capacity);
 

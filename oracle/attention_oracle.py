@@ -62,38 +62,46 @@ def allowed_masks(
     q_segment_idx: Optional[Tensor] = None,
     k_segment_idx: Optional[Tensor] = None,
     reset_position_per_segment: bool = False,
+    rows: Optional[Tensor] = None,
 ) -> Tuple[Tensor, Tensor]:
     """(inclusive, strict-past) boolean masks [B, Lq, Lk].
 
     Restates tests/_reference.py:35-131 with array operations in place of the
     per-element loops.  Per-segment reset positions need each id to label one
     contiguous run per row (the reference asserts that, :29).
+
+    ``rows`` (1-D indices of query rows) restricts the result to those rows, [B, len(rows), Lk]: the
+    same rule evaluated for a sample of a sequence too long for the full matrix (the reference's
+    long-sequence checks sample rows the same way, tests/_numerics.py:293-320).
     """
     if visibility not in ("full", "window", "chunk"):
         raise AssertionError(visibility)
+    pick = torch.arange(q_length) if rows is None else rows.long()
+    n_rows = pick.numel()
+    k_index = torch.arange(k_length).expand(batch, k_length)
+    aligned_q_pos = (pick + (k_length - q_length)).expand(batch, n_rows)
     if q_segment_idx is None:
-        same = torch.ones(batch, q_length, k_length, dtype=torch.bool)
-        q_pos = (torch.arange(q_length) + (k_length - q_length)).expand(batch, q_length)
-        k_pos = torch.arange(k_length).expand(batch, k_length)
-        k_pos = k_pos[:, None, :].expand(batch, q_length, k_length)
+        same = torch.ones(batch, n_rows, k_length, dtype=torch.bool)
+        q_pos = aligned_q_pos
+        k_pos = k_index[:, None, :].expand(batch, n_rows, k_length)
     else:
         assert k_segment_idx is not None
         q_ids = q_segment_idx.detach().cpu().long()
         k_ids = k_segment_idx.detach().cpu().long()
-        same = q_ids[:, :, None] == k_ids[:, None, :]
+        same = q_ids[:, pick, None] == k_ids[:, None, :]
         if reset_position_per_segment:
             q_start, q_end = _run_bounds(q_ids)
             k_start, _ = _run_bounds(k_ids)
             matching = same.sum(dim=-1)  # length of the key run with the query's id (0 if none)
-            q_pos = (torch.arange(q_length)[None, :] - q_start) + matching - (q_end - q_start)
+            q_pos = (pick[None, :] - q_start[:, pick]) + matching - (q_end - q_start)[:, pick]
             k_local = torch.arange(k_length)[None, :] - k_start
-            k_pos = k_local[:, None, :].expand(batch, q_length, k_length)
+            k_pos = k_local[:, None, :].expand(batch, n_rows, k_length)
         else:
-            q_pos = (torch.arange(q_length) + (k_length - q_length)).expand(batch, q_length)
-            k_pos = torch.arange(k_length).expand(batch, k_length)[:, None, :].expand(batch, q_length, k_length)
+            q_pos = aligned_q_pos
+            k_pos = k_index[:, None, :].expand(batch, n_rows, k_length)
     qp = q_pos[:, :, None]
     if visibility == "full":
-        left = torch.ones(batch, q_length, k_length, dtype=torch.bool)
+        left = torch.ones(batch, n_rows, k_length, dtype=torch.bool)
     elif visibility == "window":
         assert span is not None
         left = k_pos >= qp - span
@@ -108,17 +116,20 @@ def allowed_masks(
 def attention_from_mask(q: Tensor, k: Tensor, v: Tensor, allowed: Tensor, scale: float) -> Tensor:
     """Masked softmax read, tests/_reference.py:134-155.  q [B,Lq,Hq,D], k [B,Lk,Hkv,D],
     v [B,Lk,Hkv,V], allowed [B,Lq,Lk] -> [B,Lq,Hq,V] in the dtype of the inputs."""
-    group = q.shape[2] // k.shape[2]
-    if group != 1:
-        k = k.repeat_interleave(group, dim=2)
-        v = v.repeat_interleave(group, dim=2)
-    scores = torch.einsum("bqhd,bkhd->bhqk", q, k) * scale
-    keep = allowed[:, None]
+    batch, q_len, heads, _ = q.shape
+    kv_heads = k.shape[2]
+    group = heads // kv_heads
+    # the query heads of a KV group share its keys and values (repeat_interleave in the reference;
+    # grouped here so that long sequences do not materialise repeated K and V)
+    qg = q.reshape(batch, q_len, kv_heads, group, q.shape[-1])
+    scores = torch.einsum("bqhgd,bkhd->bhgqk", qg, k) * scale
+    keep = allowed[:, None, None]
     scores = scores.masked_fill(~keep, float("-inf"))
-    any_key = allowed.any(dim=-1, keepdim=True)[:, None]
+    any_key = allowed.any(dim=-1, keepdim=True)[:, None, None]
     scores = torch.where(any_key, scores, torch.zeros_like(scores))
     prob = torch.softmax(scores, dim=-1).masked_fill(~keep, 0.0)
-    return torch.einsum("bhqk,bkhv->bqhv", prob, v)
+    out = torch.einsum("bhgqk,bkhv->bqhgv", prob, v)
+    return out.reshape(batch, q_len, heads, v.shape[-1])
 
 
 def lse_from_mask(q: Tensor, k: Tensor, allowed: Tensor, scale: float) -> Tensor:

@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared_symbols():
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     loaded = _lib.load()
-    assert loaded.xattn_b200_abi_version() == 1
+    assert loaded.xattn_b200_abi_version() == _lib.ABI_VERSION == 2
     assert set(_lib.SYMBOLS) == set(declared_symbols())
 
 
@@ -41,6 +41,7 @@ def test_plan_bytes_layout():
     # rows padded to 4 words twice, 4 words per query tile, 2 per key tile padded to 4
     assert lib.xattn_b200_plan_bytes(1, 130, 300) == 4 * (2 * 132 + 4 * 2 + 8 + 4)   # rows, query tiles, key tiles, key-tile order
     assert lib.xattn_b200_bwd_workspace_bytes(2, 4, 100) == 2 * 4 * 128 * (2 * 4 + 32)   # rows padded to 128
+    assert lib.xattn_b200_bwd_workspace_bytes_hp(2, 4, 100) == 2 * 4 * 128 * (3 * 4 + 32)
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

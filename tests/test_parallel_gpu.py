@@ -22,10 +22,13 @@ def _worker(rank, world, port, mode, results):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
                       XATTN_B200_SYNC_CHECK="1")
+    import datetime
     import torch.distributed as dist
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    # a short timeout: a rank blocked in a send / recv whose peer died returns on its own
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
     try:
         import xattn_b200 as xattn
         from xattn_b200 import parallel as P
@@ -72,6 +75,13 @@ def test_sharded_matches_single_gpu(mode, cuda_device):
             p.start()
         for p in procs:
             p.join(timeout=300)
+        # no rank may outlive the test and keep a GPU of a shared machine busy
+        stragglers = [p for p in procs if p.is_alive()]
+        for p in stragglers:
+            p.kill()
+        for p in stragglers:
+            p.join()
+        assert not stragglers, f"{len(stragglers)} rank(s) had to be killed after the timeout"
         for p in procs:
             assert p.exitcode == 0, f"rank exited with {p.exitcode}"
         # relative norm error of y, dq, dk, dv on each rank's slice: the sharded runs differ from the single-GPU

@@ -16,6 +16,7 @@ LIB_PATH = os.environ.get("XATTN_B200_LIBRARY") or os.path.join(_HERE, "libxattn
 
 XATTN_DTYPE_F16, XATTN_DTYPE_BF16 = 0, 1
 VIS_FULL, VIS_WINDOW, VIS_CHUNK, VIS_ALL = 0, 1, 2, 3
+ABI_VERSION = 2          # XATTN_B200_ABI_VERSION of include/xattn_b200.h
 
 
 class PlanArgs(C.Structure):
@@ -25,7 +26,7 @@ class PlanArgs(C.Structure):
         ("strict_past", C.c_int), ("reset_positions", C.c_int),
         ("q_segment", C.c_void_p), ("k_segment", C.c_void_p),
         ("q_segment_stride", C.c_int64), ("k_segment_stride", C.c_int64),
-        ("plan", C.c_void_p),
+        ("plan", C.c_void_p), ("status", C.c_void_p),
     ]
 
 
@@ -50,7 +51,7 @@ class FwdArgs(C.Structure):
         ("scale", C.c_float), ("high_precision", C.c_int),
         ("plan", C.c_void_p),
         ("y", C.c_void_p), ("lse", C.c_void_p), ("y_state", C.c_void_p),
-        ("status", C.c_void_p),
+        ("status", C.c_void_p), ("anchor", C.c_void_p),
     ]
 
 
@@ -67,6 +68,7 @@ class BwdArgs(C.Structure):
         ("plan", C.c_void_p),
         ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
         ("workspace", C.c_void_p), ("status", C.c_void_p),
+        ("high_precision", C.c_int), ("anchor", C.c_void_p), ("grad_unscale", C.c_void_p),
     ]
 
 
@@ -114,6 +116,7 @@ SYMBOLS = {
     "xattn_b200_fwd_split_workspace_bytes": (C.c_size_t, [C.c_int64] * 5),
     "xattn_b200_fwd_split": (C.c_int, [C.POINTER(FwdArgs), C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p]),
     "xattn_b200_bwd_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
+    "xattn_b200_bwd_workspace_bytes_hp": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
     "xattn_b200_bwd": (C.c_int, [C.POINTER(BwdArgs), C.c_void_p]),
     "xattn_b200_bwd_static_scratch": (C.c_int, [C.POINTER(BwdArgs), C.c_void_p]),
     "xattn_b200_softdelta_gate_fwd": (C.c_int, [C.POINTER(GateArgs), C.c_void_p]),
@@ -142,7 +145,7 @@ def load() -> C.CDLL:
             fn = getattr(lib, name)
             fn.restype = restype
             fn.argtypes = argtypes
-        if lib.xattn_b200_abi_version() != 1:
+        if lib.xattn_b200_abi_version() != ABI_VERSION:
             raise ImportError("libxattn_b200.so has an unexpected ABI version; rebuild it")
         _lib = lib
         return lib

@@ -49,6 +49,12 @@ def _stream_ptr() -> C.c_void_p:
 
 
 def _raise_status(value: int) -> None:
+    if value & 0xff == 3:
+        raise RuntimeError(
+            f"segment ids of the keys decrease along batch row {value >> 8}: k_segment_idx / segment_idx must "
+            "be nondecreasing along each row (the keys of one id are located by binary search); results "
+            "of that call are invalid"
+        )
     raise RuntimeError(
         f"xattn_b200 kernel reported device status {value & 0xff} at wait site {value >> 8}; "
         "results of that launch are invalid"
@@ -157,7 +163,15 @@ def build_plan(
         args.k_segment_stride = ks.stride(0) if batch > 1 else k_len
     args.plan = plan.data_ptr()
     with torch.cuda.device(device):
+        st = None
+        # The sorted-ids check reads every key id once more: skipped for decode shapes, where that pass
+        # would cost more than the plan itself.
+        if q_segment_idx is not None and not (q_len <= 128 and k_len > 4096):
+            st = _pre_launch(device)
+            args.status = st.status.data_ptr()
         _lib.check(lib.xattn_b200_build_plan(C.byref(args), _stream_ptr()), "xattn_b200_build_plan")
+        if st is not None:
+            _post_launch(st)
     return plan
 
 
@@ -198,8 +212,11 @@ def attention_fwd(
     high_precision: bool = False,
     output_state: Optional[Tensor] = None,
     splits: Optional[int] = None,
-) -> Tuple[Tensor, Tensor]:
+    return_anchor: bool = False,
+):
     """y [B,Lq,Hq,V] (input dtype), lse [B,Hq,Lq] fp32.  ``k``/``v`` already include previous K/V.
+    With ``return_anchor`` (high precision only) a third result: int32 [B,Hq,Lq], the visible key
+    holding each row's largest logit, which the high-precision backward centres dP on.
 
     Decode shapes (a few query rows against many keys) take the split entry, which shares a tile among
     the query heads of a KV group and divides the keys among CTAs; ``splits`` overrides the library's
@@ -227,6 +244,13 @@ def attention_fwd(
         if output_state.shape != y.shape or output_state.dtype != torch.float32 or not output_state.is_contiguous():
             raise ValueError("output_state must be a contiguous FP32 tensor shaped like y")
         args.y_state = output_state.data_ptr()
+    anchor = None
+    if return_anchor:
+        if not high_precision:
+            raise ValueError("anchor keys are a result of the high-precision forward only")
+        anchor = torch.empty((B, Hq, Lq), dtype=torch.int32, device=q.device)
+        args.anchor = anchor.data_ptr()
+        splits = 0          # the split forward of decode shapes does not track anchors
     with torch.cuda.device(q.device):
         st = _pre_launch(q.device)
         args.status = st.status.data_ptr()
@@ -240,7 +264,7 @@ def attention_fwd(
         else:
             _lib.check(lib.xattn_b200_fwd(C.byref(args), _stream_ptr()), "xattn_b200_fwd")
         _post_launch(st)
-    return y, lse
+    return (y, lse, anchor) if return_anchor else (y, lse)
 
 
 def attention_bwd(
@@ -252,8 +276,17 @@ def attention_bwd(
     lse: Tensor,
     plan: Tensor,
     scale: float,
+    *,
+    anchor: Optional[Tensor] = None,
+    grad_unscale: Optional[Tensor] = None,
 ) -> Tuple[Tensor, Tensor, Tensor]:
-    """(dq, dk, dv) shaped like q, k, v (k / v including previous K/V), in the input dtype."""
+    """(dq, dk, dv) shaped like q, k, v (k / v including previous K/V), in the input dtype.
+
+    With ``anchor`` (and ``lse``) from the high-precision forward on the same inputs this is the
+    high-precision backward: dP centred on each row's anchor key, the row statistic recomputed from
+    centred terms, P formed as a square of its root (xattn/ops/_precision_backend.py:29-170).
+    ``grad_unscale``: optional FP32 device scalar multiplied into the three gradients before they are
+    rounded (undoes a power-of-two prescale of ``dy``)."""
     lib = _lib.load()
     require_cuda(q, "xattn_b200 backward")
     q, k, v, y, dy = tma_ready(q), tma_ready(k), tma_ready(v), tma_ready(y), tma_ready(dy)
@@ -263,7 +296,8 @@ def attention_bwd(
     dq = torch.empty((B, Lq, Hq, D), dtype=q.dtype, device=q.device)
     dk = torch.empty((B, Lk, Hkv, D), dtype=q.dtype, device=q.device)
     dv = torch.empty((B, Lk, Hkv, V), dtype=q.dtype, device=q.device)
-    ws = torch.empty(int(lib.xattn_b200_bwd_workspace_bytes(B, Hq, Lq)) // 4, dtype=torch.float32, device=q.device)
+    nbytes = lib.xattn_b200_bwd_workspace_bytes_hp if anchor is not None else lib.xattn_b200_bwd_workspace_bytes
+    ws = torch.empty(int(nbytes(B, Hq, Lq)) // 4, dtype=torch.float32, device=q.device)
     args = _lib.BwdArgs()
     args.dtype = _DTYPES[q.dtype]
     args.batch, args.q_len, args.k_len = B, Lq, Lk
@@ -276,6 +310,15 @@ def attention_bwd(
     args.plan = plan.data_ptr()
     args.dq, args.dk, args.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     args.workspace = ws.data_ptr()
+    if anchor is not None:
+        if anchor.shape != (B, Hq, Lq) or anchor.dtype != torch.int32 or not anchor.is_contiguous():
+            raise ValueError("anchor must be a contiguous int32 tensor [B, Hq, Lq]")
+        args.high_precision = 1
+        args.anchor = anchor.data_ptr()
+    if grad_unscale is not None:
+        if grad_unscale.dtype != torch.float32 or grad_unscale.numel() != 1 or grad_unscale.device != q.device:
+            raise ValueError("grad_unscale must be one FP32 number on the inputs' device")
+        args.grad_unscale = grad_unscale.data_ptr()
     with torch.cuda.device(q.device):
         st = _pre_launch(q.device)
         args.status = st.status.data_ptr()
@@ -362,7 +405,8 @@ def softdelta_gate_bwd(dy: Tensor, y: Tensor, neg_read: Tensor, g: Tensor) -> Tu
     return read, dneg, dg
 
 
-PROFILE_KINDS = {1: "plan", 2: "fwd", 3: "bwd_pre", 4: "bwd_dq", 5: "bwd_dkv", 6: "gate", 7: "repair"}
+PROFILE_KINDS = {1: "plan", 2: "fwd", 3: "bwd_pre", 4: "bwd_dq", 5: "bwd_dkv", 6: "gate", 7: "repair",
+                 8: "bwd_stats"}
 
 
 def profile_enable(enable: bool) -> None:

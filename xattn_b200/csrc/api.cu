@@ -62,6 +62,13 @@ size_t xattn_b200_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_
   return (size_t)batch * q_heads * padded * (2 * sizeof(float) + 32);
 }
 
+size_t xattn_b200_bwd_workspace_bytes_hp(int64_t batch, int64_t q_heads, int64_t q_len) {
+  if (batch <= 0 || q_heads <= 0 || q_len <= 0) return 0;
+  // the low-precision layout plus one FP32 word per row: -dP at the anchor key
+  const size_t padded = ((size_t)q_len + 127) / 128 * 128;
+  return (size_t)batch * q_heads * padded * (3 * sizeof(float) + 32);
+}
+
 int xattn_b200_bwd(const XattnBwdArgs* args, xattn_stream_t stream) {
   return xb::bwd_entry(args, static_cast<cudaStream_t>(stream));
 }

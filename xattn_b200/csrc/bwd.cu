@@ -43,7 +43,13 @@ struct BwdParams {
   int LqPad;                  // q_len rounded up to whole 128-row tiles: row stride of nlse2 / ndelta
   const float* nlse2;         // [B][Hq][LqPad]  -lse * log2e; -inf for rows without keys and padding
   const float* ndelta;        // [B][Hq][LqPad]  -rowsum(dy * y); 0 in the padding
-  const void* row_terms;      // [B][Hq][LqPad][16] bf16: the same two numbers as extra GEMM columns
+  const void* row_terms;      // [B][Hq][LqPad][16] bf16: the same numbers as extra GEMM columns
+  // high-precision backward only
+  const int* anchor;          // [B][Hq][Lq]  key with the row's largest logit (-1: no visible key)
+  const float* ndpa;          // [B][Hq][LqPad]  -dP at the anchor key
+  float* ndelta_out;          // the statistics kernel writes ndelta and row_terms
+  void* row_terms_out;
+  const float* grad_unscale;  // optional device scalar multiplied into dq, dk and dv on the way out
   void* dq;                   // [B][Lq][Hq][D]
   void* dk;                   // [B][Lk][Hkv][D]
   void* dv;                   // [B][Lk][Hkv][V]
@@ -58,11 +64,13 @@ struct BwdParams {
 // costs more load bandwidth than the tensor products leave.  So they ride along in the products
 // instead.  One extra k-step of 16 columns is appended to Q and dO (this 32-byte row per query)
 // and to K and V (constant rows of ones and zeros):
-//   S^T + (-lse / scale)  =  [K | 1 1 1 0 ..] [Q | t0 t1 t2 0 ..]^T     t0 + t1 + t2 = -lse / scale
-//   dP^T + (-delta)       =  [V | 0 0 0 1 1 1 0 ..] [dO | 0 0 0 d0 d1 d2 0 ..]^T
-// with each number split into three bf16 terms (24 significant bits) and FP32 accumulation.
-// Rows without keys and padding rows get a huge negative first term, so that P = 0 for them.
-__device__ __forceinline__ void write_row_terms(uint4* dst, float t, float d) {
+//   S^T + (-lse / scale)  =  [K | 1 1 1 0 ..] [Q | t0 t1 t2 0 ..]^T          t0 + t1 + t2 = -lse / scale
+//   dP^T + d + e          =  [V | 0 0 0 1 1 1 1 1 0 ..] [dO | 0 0 0 d0 d1 d2 e0 e1 0 ..]^T
+// with each number split into bf16 terms (24 significant bits for t and d, 16 for e) and FP32
+// accumulation.  Low precision: d = -delta, e = 0.  High precision: d = -dP at the row's anchor
+// key, e = -Delta (the centred row statistic).  All eight terms sit in the first 16 bytes of the
+// row.  Rows without keys and padding rows get a huge negative first term, so that P = 0 for them.
+__device__ __forceinline__ void write_row_terms(uint4* dst, float t, float d, float e) {
   if (!(t > -1e30f)) t = -1.2676506e30f;          // -2^100, exact in bf16
   const __nv_bfloat16 t0 = __float2bfloat16_rn(t);
   const float tr = t - __bfloat162float(t0);
@@ -72,8 +80,11 @@ __device__ __forceinline__ void write_row_terms(uint4* dst, float t, float d) {
   const float dr = d - __bfloat162float(d0);
   const __nv_bfloat16 d1 = __float2bfloat16_rn(dr);
   const __nv_bfloat16 d2 = __float2bfloat16_rn(dr - __bfloat162float(d1));
+  const __nv_bfloat16 e0 = __float2bfloat16_rn(e);
+  const __nv_bfloat16 e1 = __float2bfloat16_rn(e - __bfloat162float(e0));
   auto bits = [](__nv_bfloat16 x) -> uint32_t { return (uint32_t)__bfloat16_as_ushort(x); };
-  dst[0] = make_uint4(bits(t0) | (bits(t1) << 16), bits(t2) | (bits(d0) << 16), bits(d1) | (bits(d2) << 16), 0u);
+  dst[0] = make_uint4(bits(t0) | (bits(t1) << 16), bits(t2) | (bits(d0) << 16), bits(d1) | (bits(d2) << 16),
+                      bits(e0) | (bits(e1) << 16));
   dst[1] = make_uint4(0u, 0u, 0u, 0u);
 }
 
@@ -146,15 +157,69 @@ __global__ void __launch_bounds__(kPreThreads) bwd_pre_kernel(const T* __restric
       // padding up to whole tiles: rows that contribute nothing
       ndelta[idx] = 0.f;
       nlse2[idx] = -INFINITY;
-      write_row_terms(row_terms + 2 * idx, -INFINITY, 0.f);
+      write_row_terms(row_terms + 2 * idx, -INFINITY, 0.f, 0.f);
     } else {
       const float l = l_mine;
       ndelta[idx] = -acc_mine;
       nlse2[idx] = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
-      write_row_terms(row_terms + 2 * idx, (l == -INFINITY) ? -INFINITY : -l / scale, -acc_mine);
+      write_row_terms(row_terms + 2 * idx, (l == -INFINITY) ? -INFINITY : -l / scale, -acc_mine, 0.f);
     }
   }
   }
+  }
+}
+
+
+// High-precision preprocess.  The low-precision delta = rowsum(dy * y) inherits the rounding of y to
+// 16 bits, which is fatal when one key holds nearly all of a row's probability and dO V^T is huge
+// (tests/test_high_precision.py:278-310 of the reference).  The reference's remedy is to centre dP on
+// the row's anchor key, the one with the largest logit (csrc/attention/precision/row_statistics_sm90.cuh:144-186):
+// dS_ij = P_ij ((dP_ij - dP_ia) - Delta_i) with Delta_i = sum_j P_ij (dP_ij - dP_ia), which is exact
+// on the anchor and needs no cancellation of large numbers.  This kernel computes dP_ia = dO_i . V_a
+// with one 16-lane group per (row, head); Delta follows in the statistics pass of the dQ kernel.
+template <typename T>
+__global__ void __launch_bounds__(128) bwd_pre_hp_kernel(const T* __restrict__ dy, const T* __restrict__ v,
+                                                         const float* __restrict__ lse, const int* __restrict__ anchor,
+                                                         int B, int Lq, int Lk, int Hq, int Hkv, int V,
+                                                         int64_t dy_sb, int64_t dy_sl, int64_t dy_sh, int64_t v_sb,
+                                                         int64_t v_sl, int64_t v_sh, int LqPad,
+                                                         float* __restrict__ ndpa, float* __restrict__ nlse2) {
+  const int sub = threadIdx.x & 15;
+  const long long units = (long long)B * Hq * LqPad;
+  const long long unit = (long long)blockIdx.x * 8 + (threadIdx.x >> 4);
+  const bool in_range = unit < units;
+  const int i = in_range ? (int)(unit % LqPad) : 0;
+  const long long bh = in_range ? unit / LqPad : 0;
+  const int h = (int)(bh % Hq), b = (int)(bh / Hq);
+  const bool live = in_range && i < Lq;
+  int a = -1;
+  float l = -INFINITY;
+  if (live) {
+    a = anchor[((size_t)b * Hq + h) * Lq + i];
+    l = lse[((size_t)b * Hq + h) * Lq + i];
+  }
+  float acc = 0.f;
+  if (live && a >= 0 && a < Lk) {
+    const T* dy_row = dy + b * dy_sb + i * dy_sl + h * dy_sh;
+    const T* v_row = v + b * v_sb + (int64_t)a * v_sl + (h / (Hq / Hkv)) * v_sh;
+    for (int c = sub * 8; c < V; c += 128) {
+      const uint4 x = __ldg(reinterpret_cast<const uint4*>(dy_row + c));
+      const uint4 w = __ldg(reinterpret_cast<const uint4*>(v_row + c));
+      const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 fa = Pack2<T>::unpack(xw[k]);
+        const float2 fb = Pack2<T>::unpack(ww[k]);
+        acc = fmaf(fa.x, fb.x, acc);
+        acc = fmaf(fa.y, fb.y, acc);
+      }
+    }
+  }
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (in_range && sub == 0) {
+    ndpa[unit] = -acc;
+    nlse2[unit] = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
   }
 }
 
@@ -190,17 +255,30 @@ struct DqSmem {
   uint64_t s_full, s_free, dp_full, dp_free, ds_full, dq_done, dq_staged;
   uint32_t tmem_base;
   int abort_flag;
+  float red[kBlockM];          // statistics pass: the second column half's partial sums
 };
+
+// MODE of the dQ kernel.  kDqPlain: the low-precision backward.  kDqStats / kDqHigh: the two passes of the
+// high-precision backward (restating csrc/attention/precision/row_statistics_sm90.cuh:39-188 and the
+// high-precision branch of hopper/mainloop_bwd_sm90_tma_gmma_ws.hpp:1811-1868 on this kernel's
+// structure).  Both compute P as the square of root = exp2((S c - lse2) / 2), so that a probability
+// below the smallest normal FP32 number still multiplies a huge dP correctly (root * (root * x)), and
+// centre dP on the row's anchor key, where the centred value is exactly zero.
+//   kDqStats  no dQ product: Delta_i = sum_j P_ij (dP_ij - dP_ia), written with the row's extra GEMM
+//             columns for the dK / dV kernel
+//   kDqHigh   dS_ij = P_ij ((dP_ij - dP_ia) - Delta_i), dQ += dS K
+enum { kDqPlain = 0, kDqStats = 1, kDqHigh = 2 };
 
 // warps 0-3 / 4-7: element-wise warpgroups (thread = query row; first / second half of the key-tile columns)
 // warps 8, 11, 10: issuers of S, dP and dQ (an issuing thread stalls while its products run, so each
 // product has its own and none holds another back), warp 9: TMA producer + TMEM owner
-template <typename T, int HD, int BN>
+template <typename T, int HD, int BN, int MODE>
 __global__ void __launch_bounds__(384, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_dq, const BwdParams p) {
   using Smem = DqSmem<HD, BN>;
-  constexpr bool kDsOverDp = HD > 128;          // no TMEM columns left for dS
+  constexpr bool kHigh = MODE != kDqPlain, kStats = MODE == kDqStats;
+  constexpr bool kDsOverDp = HD > 128 && !kStats;   // no TMEM columns left for dS
   constexpr int kKStages = Smem::kKStages;
   constexpr int kDoBox = kBlockM * 64 * 2;     // 64-column box of the 128-row dO tile
   constexpr int kKvBox = BN * 64 * 2;          // 64-column box of a BN-row K / V tile
@@ -212,8 +290,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
   // TMEM columns.  dS, packed: 16 columns per 32-column chunk of dP, side by side from cDS, or
   // (HD = 256) over the first 16 columns of the chunk itself.
   constexpr uint32_t cQ = 0, cDS = 64;
-  constexpr uint32_t cS = 128, cDP = kDsOverDp ? 192 : 256;
-  constexpr uint32_t cDQ = kDsOverDp ? 256 : 384;
+  constexpr uint32_t cS = 128, cDP = HD > 128 ? 192 : 256;
+  constexpr uint32_t cDQ = HD > 128 ? 256 : 384;
 
   extern __shared__ uint8_t smem_raw[];
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -290,8 +368,19 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
     const bool live = row < p.Lq;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     T* dq_row = reinterpret_cast<T*>(p.dq) + (((size_t)b * p.Lq + (live ? row : 0)) * p.Hq + h) * p.D;
+    // statistics pass: what a row hands to the dK / dV kernel
+    auto write_stats = [&](float delta) {
+      const size_t idx = ((size_t)b * p.Hq + h) * p.LqPad + row;
+      float nl2 = -INFINITY, npa = 0.f;
+      if (live) { nl2 = p.nlse2[idx]; npa = p.ndpa[idx]; }
+      p.ndelta_out[idx] = -delta;
+      write_row_terms(reinterpret_cast<uint4*>(p.row_terms_out) + 2 * idx,
+                      nl2 == -INFINITY ? -INFINITY : nl2 / (p.scale * 1.4426950408889634f), npa, -delta);
+    };
     if (iters == 0) {
-      if (live) {
+      if (kStats) {
+        if (hf == 0) write_stats(0.f);
+      } else if (live) {
         for (int c = hf * (HD / 2); c < (hf + 1) * (HD / 2) && c < p.D; c += 8)
           *reinterpret_cast<uint4*>(dq_row + c) = make_uint4(0, 0, 0, 0);
       }
@@ -318,17 +407,24 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
       tc_wait_st();
       tc_fence_before();
       mbar_arrive_warp(&s.q_ready);
-      int lo = 0, hi = 0;
-      float nlse2 = -INFINITY, ndelta = 0.f;
+      int lo = 0, hi = 0, anchor = -1;
+      float nlse2 = -INFINITY, ndelta = 0.f, ndpa = 0.f;
       if (live) {
         lo = p.row_lo[(size_t)b * p.Lq + row];
         hi = p.row_hi[(size_t)b * p.Lq + row];
         nlse2 = p.nlse2[((size_t)b * p.Hq + h) * p.LqPad + row];
-        ndelta = p.ndelta[((size_t)b * p.Hq + h) * p.LqPad + row];
+        if (!kStats) ndelta = p.ndelta[((size_t)b * p.Hq + h) * p.LqPad + row];
+        if (kHigh) {
+          ndpa = p.ndpa[((size_t)b * p.Hq + h) * p.LqPad + row];
+          anchor = p.anchor[((size_t)b * p.Hq + h) * p.Lq + row];
+        }
       }
-      const float c_log2 = p.scale * 1.4426950408889634f;
+      // high precision: the exponent is halved, P = root * root
+      const float c_log2 = p.scale * 1.4426950408889634f * (kHigh ? 0.5f : 1.f);
+      if (kHigh) nlse2 *= 0.5f;
       const float2 cc = make_float2(c_log2, c_log2), nl = make_float2(nlse2, nlse2);
-      const float2 nd = make_float2(ndelta, ndelta);
+      const float2 nd = make_float2(ndelta, ndelta), npa = make_float2(ndpa, ndpa);
+      float2 stat_a = make_float2(0.f, 0.f), stat_b = make_float2(0.f, 0.f);
       bool ok = true;
       for (int i = 0; i < iters && ok; ++i) {
         const int col0 = (n_lo + i) * BN + hf * CH;
@@ -348,7 +444,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
         for (int c = 0; c < CH; c += 2) {
           // a share of the exponentials on the FMA pipe: the special-function unit bounds this loop
           const float2 x = fma2(make_float2(pv[c], pv[c + 1]), cc, nl);
-          const float2 pr = ((c >> 1) & 3) < kFmaPairs ? ex2_pair_fma(x) : ex2_pair_sfu(x);
+          const float2 pr = (!kHigh && ((c >> 1) & 3) < kFmaPairs) ? ex2_pair_fma(x) : ex2_pair_sfu(x);
           pv[c] = pr.x; pv[c + 1] = pr.y;
         }
         if (!tile_full) {
@@ -360,6 +456,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
         if (!ok) break;
         tc_fence_after();
         uint32_t pk[CH / 2];
+        const int ac = anchor - col0;         // the anchor's column in this thread's share, if any
 #pragma unroll
         for (int c0 = 0; c0 < CH; c0 += 32) {
           float dpv[32];
@@ -368,10 +465,29 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
           tc_wait_ld();
 #pragma unroll
           for (int c = 0; c < 32; c += 2) {
-            const float2 ds = mul2(make_float2(pv[c0 + c], pv[c0 + c + 1]), add2(make_float2(dpv[c], dpv[c + 1]), nd));
-            pk[(c0 + c) >> 1] = Pack2<T>::pack(ds.x, ds.y);
+            const float2 pr = make_float2(pv[c0 + c], pv[c0 + c + 1]);
+            if (kHigh) {
+              float2 cent = add2(make_float2(dpv[c], dpv[c + 1]), npa);
+              cent.x = (c0 + c == ac) ? 0.f : cent.x;
+              cent.y = (c0 + c + 1 == ac) ? 0.f : cent.y;
+              if (kStats) {
+                if (c & 2) stat_b = fma2(pr, mul2(pr, cent), stat_b);
+                else stat_a = fma2(pr, mul2(pr, cent), stat_a);
+              } else {
+                const float2 ds = mul2(pr, mul2(pr, add2(cent, nd)));
+                pk[(c0 + c) >> 1] = Pack2<T>::pack(ds.x, ds.y);
+              }
+            } else {
+              const float2 ds = mul2(pr, add2(make_float2(dpv[c], dpv[c + 1]), nd));
+              pk[(c0 + c) >> 1] = Pack2<T>::pack(ds.x, ds.y);
+            }
           }
           if (kDsOverDp) tmem_st_x16(t_dp, pk + (c0 >> 1));
+        }
+        if (kStats) {
+          tc_fence_before();
+          mbar_arrive_warp(&s.dp_free);        // dP has been read: the next one may be issued
+          continue;
         }
         if (!kDsOverDp) {
           tc_fence_before();
@@ -388,8 +504,19 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
         tc_fence_before();
         mbar_arrive_warp(&s.ds_full);
       }
-      if (ok) ok = mbar_wait(ctx, &s.dq_done, (iters - 1) & 1, 52);
-      if (ok) {
+      if (kStats) {
+        // Delta = first half's sum + second half's sum, in that order
+        const float part = (stat_a.x + stat_a.y) + (stat_b.x + stat_b.y);
+        if (hf == 1) s.red[r] = part;
+        mbar_arrive_warp(&s.dq_staged);
+        if (ok && hf == 0) {
+          ok = mbar_wait(ctx, &s.dq_staged, 0, 55);
+          if (ok) write_stats(live ? part + s.red[r] : 0.f);
+        }
+      }
+      if (ok && !kStats) ok = mbar_wait(ctx, &s.dq_done, (iters - 1) & 1, 52);
+      if (ok && !kStats) {
+        const float out_scale = p.scale * (p.grad_unscale ? __ldg(p.grad_unscale) : 1.f);
         tc_fence_after();
         // This warpgroup has columns [hf*HD/2, (hf+1)*HD/2) of dQ.  They leave through shared memory
         // (the dO tile's buffer: every dP product has run) and bulk tensor stores: coalesced, clipped
@@ -405,10 +532,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
 #pragma unroll
           for (int c = 0; c < 32; c += 8) {
             uint4 u;
-            u.x = Pack2<T>::pack(__uint_as_float(o[c + 0]) * p.scale, __uint_as_float(o[c + 1]) * p.scale);
-            u.y = Pack2<T>::pack(__uint_as_float(o[c + 2]) * p.scale, __uint_as_float(o[c + 3]) * p.scale);
-            u.z = Pack2<T>::pack(__uint_as_float(o[c + 4]) * p.scale, __uint_as_float(o[c + 5]) * p.scale);
-            u.w = Pack2<T>::pack(__uint_as_float(o[c + 6]) * p.scale, __uint_as_float(o[c + 7]) * p.scale);
+            u.x = Pack2<T>::pack(__uint_as_float(o[c + 0]) * out_scale, __uint_as_float(o[c + 1]) * out_scale);
+            u.y = Pack2<T>::pack(__uint_as_float(o[c + 2]) * out_scale, __uint_as_float(o[c + 3]) * out_scale);
+            u.z = Pack2<T>::pack(__uint_as_float(o[c + 4]) * out_scale, __uint_as_float(o[c + 5]) * out_scale);
+            u.w = Pack2<T>::pack(__uint_as_float(o[c + 6]) * out_scale, __uint_as_float(o[c + 7]) * out_scale);
             const int chunk = ((cbase & 63) + c) >> 3;
             *reinterpret_cast<uint4*>(box + ((chunk ^ (r & 7)) << 4)) = u;
           }
@@ -441,6 +568,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
                 idesc_s, js > 0);
       }
       umma_commit(&s.s_full);
+      if (kStats) umma_commit(&s.k_empty[ks]);   // no dQ product holds the K tile any longer
     }
   } else if (warp == 11 && lane == 0 && iters > 0) {
     // ------------------------------ dP issuer ------------------------------
@@ -461,7 +589,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
       umma_commit(&s.dp_full);
       umma_commit(&s.v_empty[vs]);
     }
-  } else if (warp == 10 && lane == 0 && iters > 0) {
+  } else if (warp == 10 && lane == 0 && iters > 0 && !kStats) {
     // ------------------------------ dQ issuer ------------------------------
     const uint32_t idesc_dq = make_idesc(kBlockM, d_pad, kFormat, 0, 1);
     bool ok = true;
@@ -601,7 +729,7 @@ struct DkvIter {
 // With two S^T / dP^T buffers (SM <= 64) sub-tiles alternate between them.  With one (SM = 128, the
 // widest products: a tcgen05.mma costs about the same for 64 columns as for 128) the
 // S^T -> P^T -> dV and dP^T -> dS^T -> dK chains of a step overlap each other and the next step's S^T.
-template <typename T, int HD, int MODE, int SM>
+template <typename T, int HD, int MODE, int SM, bool HP>
 __global__ void __launch_bounds__(384, 1)
 bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -649,11 +777,11 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   }
   if (warp == 9) { tmem_alloc(&s.tmem_base, kTmemCols); tmem_relinquish(); }
   if (tid < kBlockN) {
-    // key-side rows of the extra k-step: bf16 ones in columns 0-2 (S^T) or 3-5 (dP^T), the same
+    // key-side rows of the extra k-step: bf16 ones in columns 0-2 (S^T) or 3-7 (dP^T), the same
     // in both 16-byte halves of the row so that the swizzle cannot matter (the query-side rows
     // are zero in their second half)
     const uint4 os = make_uint4(0x3f803f80u, 0x00003f80u, 0u, 0u);
-    const uint4 od = make_uint4(0u, 0x3f800000u, 0x3f803f80u, 0u);
+    const uint4 od = make_uint4(0u, 0x3f800000u, 0x3f803f80u, 0x3f803f80u);
     uint4* ps = reinterpret_cast<uint4*>(s.ones_s + tid * 32);
     uint4* pd = reinterpret_cast<uint4*>(s.ones_dp + tid * 32);
     ps[0] = os; ps[1] = os; pd[0] = od; pd[1] = od;
@@ -700,7 +828,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int r = wt;                         // key row inside the tile
     const int key = n * kBlockN + r;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-    const float c_log2 = p.scale * 1.4426950408889634f;
+    // high precision: root = exp2(x / 2), P = root * root (see the dQ kernel's modes)
+    const float c_log2 = p.scale * 1.4426950408889634f * (HP ? 0.5f : 1.f);
     const float2 cc = make_float2(c_log2, c_log2);
     bool ok = true;
     // Bit of the bitmap word: every row of query tile mm sees all of this key tile, no masking.
@@ -722,6 +851,18 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       return (size_t)b * p.Lq + (qrow < p.Lq ? qrow : p.Lq - 1);
     };
     int my_lo[kPerLane], my_hi[kPerLane];
+    // High precision: on a query's anchor key the centred dP is exactly zero, so dS there is
+    // P (0 - Delta).  Lane c fetches anchor and -Delta of its columns like the bounds above; a warp
+    // looks at a column only when that column's anchor is one of the warp's own 32 keys.
+    int my_anchor[kPerLane];
+    float my_nd[kPerLane];
+    auto fetch_anchor = [&](const Iter& item, int j) {
+      const int qrow = item.row0() + wg * kHalf + j * kChunk + (lane & (kChunk - 1));
+      const int qr = qrow < p.Lq ? qrow : p.Lq - 1;
+      const size_t bh = (size_t)b * p.Hq + kvh * G + item.g;
+      my_anchor[j] = qrow < p.Lq ? p.anchor[bh * p.Lq + qr] : -1;
+      my_nd[j] = p.ndelta[bh * p.LqPad + qr];
+    };
     Iter it = it0;
     uint32_t fw = 0;
     int fbit = 0;
@@ -730,6 +871,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       for (int j = 0; j < kPerLane; ++j) {
         const size_t bi = bound_index(it, j);
         my_lo[j] = p.row_lo[bi]; my_hi[j] = p.row_hi[bi];
+        if (HP) fetch_anchor(it, j);
       }
       fw = full_word(it.m, fbit);
     }
@@ -755,11 +897,23 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
       }
+      uint32_t hit[kPerLane];
+      int anchor_now[kPerLane];
+      float nd_now[kPerLane];
+      if (HP) {
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j) {
+          const int rel = my_anchor[j] - (key - lane);
+          hit[j] = __ballot_sync(0xffffffffu, rel >= 0 && rel < 32) & (kChunk == 32 ? 0xffffffffu : ((1u << kChunk) - 1u));
+          anchor_now[j] = my_anchor[j]; nd_now[j] = my_nd[j];
+        }
+      }
       if (n1.valid()) {
 #pragma unroll
         for (int j = 0; j < kPerLane; ++j) {
           const size_t bi = bound_index(n1, j);
           my_lo[j] = p.row_lo[bi]; my_hi[j] = p.row_hi[bi];
+          if (HP) fetch_anchor(n1, j);
         }
         fw = full_word(n1.m, fbit);
       }
@@ -782,7 +936,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int c = j * kChunk; c < (j + 1) * kChunk; c += 2) {
           // a share of the exponentials on the FMA pipe: the special-function unit bounds this loop
           const float2 x = mul2(make_float2(pv[c], pv[c + 1]), cc);
-          const float2 e = ((c >> 1) & 3) < XB_DKV_FMA_PAIRS ? ex2_pair_fma(x) : ex2_pair_sfu(x);
+          const float2 e = (!HP && ((c >> 1) & 3) < XB_DKV_FMA_PAIRS) ? ex2_pair_fma(x) : ex2_pair_sfu(x);
           pv[c] = e.x; pv[c + 1] = e.y;
         }
         if (!tile_full) {
@@ -793,7 +947,11 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (kWantDv) {
           uint32_t pp[kChunk / 2];
 #pragma unroll
-          for (int c = 0; c < kChunk; c += 2) pp[c >> 1] = Pack2<T>::pack(pv[j * kChunk + c], pv[j * kChunk + c + 1]);
+          for (int c = 0; c < kChunk; c += 2) {
+            float2 pr = make_float2(pv[j * kChunk + c], pv[j * kChunk + c + 1]);
+            if (HP) pr = mul2(pr, pr);
+            pp[c >> 1] = Pack2<T>::pack(pr.x, pr.y);
+          }
           if (kChunk == 32) tmem_st_x16(t_s + j * kChunk, pp); else tmem_st_x8(t_s + j * kChunk, pp);
           tc_wait_st();
         }
@@ -812,11 +970,23 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (kChunk == 32) tmem_ld_x32(t_dp + j * kChunk, reinterpret_cast<uint32_t*>(dpv));
           else tmem_ld_x16(t_dp + j * kChunk, reinterpret_cast<uint32_t*>(dpv));
           tc_wait_ld();
+          if (HP && hit[j]) {
+#pragma unroll
+            for (int c = 0; c < kChunk; ++c) {
+              if ((hit[j] >> c) & 1u) {                      // the same for the whole warp
+                const int a = __shfl_sync(0xffffffffu, anchor_now[j], c);
+                const float ndl = __shfl_sync(0xffffffffu, nd_now[j], c);
+                if (key == a) dpv[c] = ndl;
+              }
+            }
+          }
           uint32_t pd[kChunk / 2];
 #pragma unroll
           for (int c = 0; c < kChunk; c += 2) {
             const int g2 = j * kChunk + c;
-            const float2 d = mul2(make_float2(pv[g2], pv[g2 + 1]), make_float2(dpv[c], dpv[c + 1]));
+            const float2 pr = make_float2(pv[g2], pv[g2 + 1]);
+            float2 d = mul2(pr, make_float2(dpv[c], dpv[c + 1]));
+            if (HP) d = mul2(pr, d);
             pd[c >> 1] = Pack2<T>::pack(d.x, d.y);
           }
           if (kChunk == 32) tmem_st_x16(t_dp + j * kChunk, pd); else tmem_st_x8(t_dp + j * kChunk, pd);
@@ -836,7 +1006,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const bool live = key < p.Lk;
       const int width = wg == 0 ? p.D : p.V;
       const int pad = wg == 0 ? d_pad : v_pad;
-      const float mul = wg == 0 ? p.scale : 1.f;
+      const float mul = (wg == 0 ? p.scale : 1.f) * (p.grad_unscale ? __ldg(p.grad_unscale) : 1.f);
       const uint32_t col = wg == 0 ? cDK : cDV;
       T* out = wg == 0
           ? reinterpret_cast<T*>(p.dk) + (((size_t)b * p.Lk + (live ? key : 0)) * p.Hkv + kvh) * p.D
@@ -1022,7 +1192,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
-template <typename T, int HD, int BN>
+template <typename T, int HD, int BN, int MODE>
 static int launch_dq(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t stream) {
   CUtensorMap tdo, tk, tv;
   if (make_tile_map(&tdo, a.dy, a.dtype, a.batch, a.q_len, a.q_heads, a.v_dim, a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], kBlockM)) return XATTN_E_INVALID;
@@ -1031,20 +1201,20 @@ static int launch_dq(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t str
   CUtensorMap tdq;
   if (make_tile_map(&tdq, a.dq, a.dtype, a.batch, a.q_len, a.q_heads, a.qk_dim, a.q_len * a.q_heads * a.qk_dim,
                     a.q_heads * a.qk_dim, a.qk_dim, kBlockM)) return XATTN_E_INVALID;
-  auto kern = bwd_dq_kernel<T, HD, BN>;
+  auto kern = bwd_dq_kernel<T, HD, BN, MODE>;
   const size_t smem = sizeof(DqSmem<HD, BN>) + 1024;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_error("cudaFuncSetAttribute(dq): %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
   const long long grid = (long long)p.nQT * p.Hq * p.B;
   if (grid > 0x7fffffffLL) { set_error("dQ grid out of range"); return XATTN_E_INVALID; }
   {
-    ProfileScope prof(kProfBwdDq, stream);
+    ProfileScope prof(MODE == kDqStats ? kProfBwdStats : kProfBwdDq, stream);
     kern<<<(unsigned)grid, 384, smem, stream>>>(tdo, tk, tv, tdq, p);
   }
   return XATTN_OK;
 }
 
-template <typename T, int HD, int MODE, int SM>
+template <typename T, int HD, int MODE, int SM, bool HP>
 static int launch_dkv(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t stream) {
   CUtensorMap tq, tdo, tk, tv;
   if (make_tile_map(&tq, a.q, a.dtype, a.batch, a.q_len, a.q_heads, a.qk_dim, a.q_strides[0], a.q_strides[1], a.q_strides[2], SM)) return XATTN_E_INVALID;
@@ -1057,7 +1227,7 @@ static int launch_dkv(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t st
                     a.kv_heads * a.qk_dim, a.qk_dim, kBlockN)) return XATTN_E_INVALID;
   if (make_tile_map(&tdv, a.dv, a.dtype, a.batch, a.k_len, a.kv_heads, a.v_dim, a.k_len * a.kv_heads * a.v_dim,
                     a.kv_heads * a.v_dim, a.v_dim, kBlockN)) return XATTN_E_INVALID;
-  auto kern = bwd_dkv_kernel<T, HD, MODE, SM>;
+  auto kern = bwd_dkv_kernel<T, HD, MODE, SM, HP>;
   const size_t smem = sizeof(DkvSmem<HD, MODE, SM>) + 1024;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { set_error("cudaFuncSetAttribute(dkv): %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
@@ -1070,16 +1240,27 @@ static int launch_dkv(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t st
   return XATTN_OK;
 }
 
-template <typename T>
+template <typename T, bool HP>
 static int launch_bwd(const XattnBwdArgs& a, BwdParams& p, cudaStream_t stream) {
   // 1. preprocess
-  // workspace: -delta, -lse2 (FP32 each), then the 32-byte rows of extra GEMM columns
+  // workspace: -delta, -lse2 (FP32 each), the 32-byte rows of extra GEMM columns, and (high precision)
+  // -dP at the anchor key
   const size_t rows = (size_t)p.B * p.Hq * p.LqPad;
   float* ndelta = a.workspace;
   float* nlse2 = a.workspace + rows;
   uint4* row_terms = reinterpret_cast<uint4*>(a.workspace + 2 * rows);
+  float* ndpa = a.workspace + 10 * rows;
   p.ndelta = ndelta; p.nlse2 = nlse2; p.row_terms = row_terms;
-  {
+  p.ndpa = HP ? ndpa : nullptr; p.ndelta_out = ndelta; p.row_terms_out = row_terms;
+  if (HP) {
+    const long long blocks = ((long long)rows + 7) / 8;
+    if (blocks > 0x7fffffffLL) { set_error("backward preprocess grid out of range"); return XATTN_E_INVALID; }
+    ProfileScope prof(kProfBwdPre, stream);
+    bwd_pre_hp_kernel<T><<<(unsigned)blocks, 128, 0, stream>>>(
+        reinterpret_cast<const T*>(a.dy), reinterpret_cast<const T*>(a.v), a.lse, a.anchor, p.B, p.Lq, p.Lk, p.Hq,
+        p.Hkv, p.V, a.dy_strides[0], a.dy_strides[1], a.dy_strides[2], a.v_strides[0], a.v_strides[1],
+        a.v_strides[2], p.LqPad, ndpa, nlse2);
+  } else {
     const int chunks = p.V >> 3;
     const int per_block = kPreIters * (kPreThreads / 32) * kPrePasses * 32 / (chunks <= 8 ? 8 : (chunks <= 16 ? 16 : 32));
     const long long blocks = ((long long)p.LqPad * p.Hq + per_block - 1) / per_block;
@@ -1091,18 +1272,22 @@ static int launch_bwd(const XattnBwdArgs& a, BwdParams& p, cudaStream_t stream) 
         p.scale, ndelta, nlse2, row_terms);
   }
   const int hd = p.D > p.V ? p.D : p.V;
+  constexpr int kDq = HP ? kDqHigh : kDqPlain;
   int rc;
-  // 2. dQ   3. dK / dV
+  // (high precision: the statistics pass)   2. dQ   3. dK / dV
   if (hd <= 64) {
-    if ((rc = launch_dq<T, 64, 128>(a, p, stream))) return rc;
-    if ((rc = launch_dkv<T, 64, kDkvBoth, 128>(a, p, stream))) return rc;
+    if (HP && (rc = launch_dq<T, 64, 128, kDqStats>(a, p, stream))) return rc;
+    if ((rc = launch_dq<T, 64, 128, kDq>(a, p, stream))) return rc;
+    if ((rc = launch_dkv<T, 64, kDkvBoth, 128, HP>(a, p, stream))) return rc;
   } else if (hd <= 128) {
-    if ((rc = launch_dq<T, 128, 128>(a, p, stream))) return rc;
-    if ((rc = launch_dkv<T, 128, kDkvBoth, 128>(a, p, stream))) return rc;
+    if (HP && (rc = launch_dq<T, 128, 128, kDqStats>(a, p, stream))) return rc;
+    if ((rc = launch_dq<T, 128, 128, kDq>(a, p, stream))) return rc;
+    if ((rc = launch_dkv<T, 128, kDkvBoth, 128, HP>(a, p, stream))) return rc;
   } else {
-    if ((rc = launch_dq<T, 256, 64>(a, p, stream))) return rc;
-    if ((rc = launch_dkv<T, 256, kDvOnly, 64>(a, p, stream))) return rc;
-    if ((rc = launch_dkv<T, 256, kDkOnly, 32>(a, p, stream))) return rc;
+    if (HP && (rc = launch_dq<T, 256, 64, kDqStats>(a, p, stream))) return rc;
+    if ((rc = launch_dq<T, 256, 64, kDq>(a, p, stream))) return rc;
+    if ((rc = launch_dkv<T, 256, kDvOnly, 64, HP>(a, p, stream))) return rc;
+    if ((rc = launch_dkv<T, 256, kDkOnly, 32, HP>(a, p, stream))) return rc;
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("backward launch: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
@@ -1120,6 +1305,7 @@ int bwd_entry(const XattnBwdArgs* a, cudaStream_t stream) {
   if (!(a->scale > 0.f) || !isfinite(a->scale)) { set_error("scale must be finite and positive"); return XATTN_E_INVALID; }
   if (!a->q || !a->k || !a->v || !a->y || !a->dy || !a->lse || !a->plan || !a->dq || !a->dk || !a->dv ||
       !a->workspace || !a->status) { set_error("null tensor pointer"); return XATTN_E_INVALID; }
+  if (a->high_precision && !a->anchor) { set_error("the high-precision backward needs the forward's anchor keys"); return XATTN_E_INVALID; }
   for (const void* ptr : {a->q, a->y, a->dy, (const void*)a->dq, (const void*)a->dk, (const void*)a->dv,
                           (const void*)a->workspace}) {
     if (reinterpret_cast<uintptr_t>(ptr) & 15) { set_error("tensors must be 16-byte aligned"); return XATTN_E_INVALID; }
@@ -1140,8 +1326,11 @@ int bwd_entry(const XattnBwdArgs* a, cudaStream_t stream) {
   p.k_order = a->plan + pl.off_ko;
   p.q = a->q; p.q_sb = a->q_strides[0]; p.q_sl = a->q_strides[1]; p.q_sh = a->q_strides[2];
   p.dq = a->dq; p.dk = a->dk; p.dv = a->dv; p.status = a->status;
-  if (a->dtype == XATTN_DTYPE_BF16) return launch_bwd<__nv_bfloat16>(*a, p, stream);
-  return launch_bwd<__half>(*a, p, stream);
+  p.anchor = a->anchor; p.grad_unscale = a->grad_unscale;
+  if (a->dtype == XATTN_DTYPE_BF16) {
+    return a->high_precision ? launch_bwd<__nv_bfloat16, true>(*a, p, stream) : launch_bwd<__nv_bfloat16, false>(*a, p, stream);
+  }
+  return a->high_precision ? launch_bwd<__half, true>(*a, p, stream) : launch_bwd<__half, false>(*a, p, stream);
 }
 
 }  // namespace xb

@@ -17,8 +17,14 @@
 //    later reads, so nothing has to be cleared between calls and a previous call's contents are
 //    never observed; but two calls whose kernels overlap on the GPU (different streams, or threads
 //    without ordering) would overwrite each other's rows — callers serialise them;
+//  * the high-precision backward (high_precision = 1) needs 44 bytes per row instead of 40, so its
+//    limit is 10/11 of kStaticRows;
 //  * the first call on a device resolves the array's device address (cudaGetSymbolAddress, with
-//    that device current).  Make that first call outside any stream capture.
+//    that device current).  Where the CUDA runtime loads modules lazily that call is also the one
+//    that loads this module and reserves the array on the device: it can take milliseconds, and it
+//    fails with an out-of-memory error if another owner already holds all device memory.  Make that
+//    first call at start-up, before the arena owner takes the rest of the device and outside any
+//    stream capture.
 #include <mutex>
 #include "common.cuh"
 
@@ -62,11 +68,19 @@ int static_workspace(float** out) {
 int bwd_static_entry(const XattnBwdArgs* a, cudaStream_t stream) {
   if (!a) { set_error("null arguments"); return XATTN_E_INVALID; }
   if (a->batch <= 0 || a->q_heads <= 0 || a->q_len <= 0) { set_error("bad batch / head / length"); return XATTN_E_INVALID; }
+  // each factor is bounded before anything is multiplied, so the products below cannot overflow
+  if (a->batch > kStaticRows || a->q_heads > kStaticRows || a->q_len > kStaticRows) {
+    set_error("batch, q_heads or q_len alone exceeds the static workspace of %lld rows; "
+              "use xattn_b200_bwd with a caller-provided workspace", kStaticRows);
+    return XATTN_E_INVALID;
+  }
   const long long padded = (a->q_len + 127) / 128 * 128;      // the kernels keep whole 128-row tiles
-  const long long rows = (long long)a->batch * a->q_heads * padded;
-  if (rows > kStaticRows || rows / a->batch / a->q_heads != padded) {
-    set_error("batch * q_heads * q_len (rounded up to 128) = %lld exceeds the static workspace of %lld rows; "
-              "use xattn_b200_bwd with a caller-provided workspace", rows, kStaticRows);
+  const long long bh = (long long)a->batch * a->q_heads;       // <= 2^40
+  const long long floats_per_row = a->high_precision ? 11 : 10;
+  const long long max_rows = 10 * kStaticRows / floats_per_row;
+  if (bh > max_rows || bh * padded > max_rows) {
+    set_error("batch * q_heads * q_len (rounded up to 128) exceeds the static workspace of %lld rows; "
+              "use xattn_b200_bwd with a caller-provided workspace", max_rows);
     return XATTN_E_INVALID;
   }
   float* ws = nullptr;

@@ -72,7 +72,7 @@ void set_error(const char* fmt, ...);
 // Optional per-kernel timing: when enabled, a ProfileScope brackets the launches made
 // inside it with CUDA events on the launch stream.
 enum ProfileKind : int {
-  kProfPlan = 1, kProfFwd = 2, kProfBwdPre = 3, kProfBwdDq = 4, kProfBwdDkv = 5, kProfGate = 6, kProfRepair = 7,
+  kProfPlan = 1, kProfFwd = 2, kProfBwdPre = 3, kProfBwdDq = 4, kProfBwdDkv = 5, kProfGate = 6, kProfRepair = 7, kProfBwdStats = 8,
 };
 struct ProfileScope {
   ProfileScope(int kind, cudaStream_t stream);

@@ -43,6 +43,7 @@ struct FwdParams {
   void* y;                // [B][Lq][Hq][V]
   float* lse;             // [B][Hq][Lq]
   float* y_state;         // optional fp32 copy of y
+  int* anchor;            // optional (HP): [B][Hq][Lq] key index of the row's largest logit
   int* status;
   // decode shape only (template flag DEC): the query heads of a KV group share the tile, the key
   // tiles are divided among `splits` CTAs per (batch, KV head), partial results go to the workspace
@@ -65,6 +66,8 @@ struct FwdSmem {
   float xmax[4][XB_FWD_PARTS][kBlockM];   // row maxima of the column parts, by iteration mod 4
   float final_l[XB_FWD_PARTS][kBlockM];
   float final_m[kBlockM];
+  float best_s[XB_FWD_PARTS][kBlockM];   // HP: largest logit of each column part and its key index
+  int best_i[XB_FWD_PARTS][kBlockM];
   uint64_t q_full;
   uint64_t k_full[kKStages], k_empty[kKStages];
   uint64_t v_full[kVStages], v_empty[kVStages];
@@ -212,6 +215,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const float c_log2 = p.scale * 1.4426950408889634f;
     float m = -INFINITY, l = 0.f;
+    float best = -INFINITY;                     // HP: this part's largest logit so far and where it was
+    int best_idx = -1;
     bool ok = true;
     for (int j = 0; j < iters && ok; ++j) {
       const int buf = j & 1;
@@ -252,6 +257,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         mx4[e] = max3(mx4[e], sc[c + 6], sc[c + 7]);
       }
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      if (HP && mx > best) {
+        // the anchor key of the high-precision backward: the first key holding the row's maximum
+        best = mx;
+#pragma unroll
+        for (int c = kCols - 1; c >= 0; --c) best_idx = (sc[c] == mx) ? col0 + c : best_idx;
+      }
       // The row maximum over all column parts.  Four slots: a part can be here for tile j + 4 only
       // after every part has loaded S of tile j + 2 (the S buffer it needs is free no earlier), that
       // is after every part has finished with the slot of tile j.  With two slots a part running
@@ -342,6 +353,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // hand the row statistics to the epilogue
     s.final_l[hf][r] = l;
     if (hf == 0) s.final_m[r] = m;
+    if (HP) { s.best_s[hf][r] = best; s.best_i[hf][r] = best_idx; }
     mbar_arrive_warp(&s.final_full);
   } else if (warp < kCorrWarp + 4) {
     // ======================= correction + epilogue warpgroup =======================
@@ -391,6 +403,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         float* lse_out = DEC ? p.part_lse + (size_t)split * p.B * p.Hq * p.Lq : p.lse;
         lse_out[((size_t)b * p.Hq + hr) * p.Lq + row] =
             has ? (m * c_log2 + log2f(l)) * 0.6931471805599453f : -INFINITY;
+        if (HP && !DEC && p.anchor) {
+          float bs = -INFINITY;
+          int bi = -1;
+          if (iters > 0) {
+#pragma unroll
+            for (int o = 0; o < kParts; ++o) {
+              const float v = s.best_s[o][r];
+              const int i = s.best_i[o][r];
+              if (i >= 0 && (v > bs || (v == bs && i < bi))) { bs = v; bi = i; }
+            }
+          }
+          p.anchor[((size_t)b * p.Hq + hr) * p.Lq + row] = bi;
+        }
       }
       // y leaves through shared memory and bulk tensor stores (the Q tile's buffer is free by now:
       // every S product has run): coalesced, clipped to the tensor by the hardware, and the CTA
@@ -661,6 +686,7 @@ static int check_fwd_args(const XattnFwdArgs* a, FwdParams& p) {
   p.row_hi = a->plan + pl.off_hi;
   p.q_tiles = reinterpret_cast<const TileInfo*>(a->plan + pl.off_qt);
   p.y = a->y; p.lse = a->lse; p.y_state = a->y_state; p.status = a->status;
+  p.anchor = a->high_precision ? a->anchor : nullptr;
   p.splits = 1; p.g_shift = 0; p.part_y = nullptr; p.part_lse = nullptr;
   return XATTN_OK;
 }

@@ -102,7 +102,23 @@ struct RowArgs {
   int64_t q_seg_stride, k_seg_stride;
   const int* q_run_start; const int* q_run_end;   // reset only
   int* row_lo; int* row_hi;
+  int* status;                                    // optional: where a broken id contract is reported
 };
+
+// The binary searches above are only right when the key ids of a row never decrease (the reference's
+// kernels assume the same, csrc/attention/partition/segment_index.h:362-363, and say nothing when it
+// does not hold).  Each thread compares a share of the neighbouring key ids; a decrease stores
+// (batch row << 8) | kStatusUnsortedSegments in the caller's status word.
+__device__ __forceinline__ void check_key_ids(const RowArgs& a, long long first, long long stride) {
+  if (!a.k_seg || !a.status) return;
+  const long long total = (long long)a.B * a.Lk;
+  for (long long j = first; j < total; j += stride) {
+    const int b = (int)(j / a.Lk);
+    const int jj = (int)(j - (long long)b * a.Lk);
+    const int64_t* ks = a.k_seg + (size_t)b * a.k_seg_stride;
+    if (jj > 0 && ks[jj] < ks[jj - 1]) atomicCAS(a.status, 0, ((b & 0x7fffff) << 8) | kStatusUnsortedSegments);
+  }
+}
 
 // visible-key interval of query row i of batch row b (idx = b * Lq + i)
 __device__ __forceinline__ void row_interval(const RowArgs& a, int b, int i, long long idx, int& out_lo, int& out_hi) {
@@ -134,6 +150,7 @@ __device__ __forceinline__ void row_interval(const RowArgs& a, int b, int i, lon
 
 __global__ void __launch_bounds__(256) plan_rows_kernel(const RowArgs a) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  check_key_ids(a, idx, (long long)gridDim.x * blockDim.x);
   if (idx >= (long long)a.B * a.Lq) return;
   const int b = (int)(idx / a.Lq);
   const int i = (int)(idx - (long long)b * a.Lq);
@@ -152,6 +169,7 @@ __global__ void __launch_bounds__(128) plan_one_tile_kernel(const RowArgs a, int
   __shared__ int red[4][4];
   __shared__ int any_empty_s[4];
   const int b = blockIdx.x, i = threadIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  check_key_ids(a, (long long)blockIdx.x * blockDim.x + threadIdx.x, (long long)gridDim.x * blockDim.x);
   int min_lo = INT_MAX, max_hi = 0, max_lo = 0, min_hi = INT_MAX;
   bool any_empty = false;
   if (i < a.Lq) {
@@ -351,6 +369,7 @@ int build_plan_entry(const XattnPlanArgs* a, cudaStream_t stream) {
   r.q_seg_stride = a->q_segment_stride; r.k_seg_stride = a->k_segment_stride;
   r.row_lo = a->plan + pl.off_lo; r.row_hi = a->plan + pl.off_hi;
   r.q_run_start = r.q_run_end = nullptr;
+  r.status = a->status;
   if (r.reset) {
     // run starts / ends are staged in the row_lo / row_hi slots; plan_rows_kernel reads
     // its own slot before overwriting it

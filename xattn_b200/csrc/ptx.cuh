@@ -21,6 +21,7 @@ enum : int {
   kStatusOk = 0,
   kStatusWaitTimeout = 1,   // an mbarrier wait ran out of time
   kStatusBadArgs = 2,
+  kStatusUnsortedSegments = 3,   // key segment ids decrease somewhere along a row (plan kernels)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

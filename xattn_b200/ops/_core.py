@@ -52,33 +52,59 @@ def forward(
     q_segment_idx: Optional[Tensor], k_segment_idx: Optional[Tensor],
     *, high_precision: bool = False, output_state: Optional[Tensor] = None, return_plan: bool = False,
 ):
-    """(y, lse), and the mask plan too when asked for (the autograd path keeps it for the backward)."""
+    """(y, lse), and with ``return_plan`` (the autograd path, which keeps them for the backward) the mask
+    plan and, at level 1, the rows' anchor keys too (``None`` at level 0)."""
     k_all, v_all = concat_previous(k, v, prev_k, prev_v)
     plan = make_plan(q, k_all.shape[1], support, q_segment_idx, k_segment_idx)
     out = _native.attention_fwd(q, k_all, v_all, plan, scale, high_precision=high_precision,
-                                output_state=output_state)
-    return (*out, plan) if return_plan else out
+                                output_state=output_state, return_anchor=return_plan and high_precision)
+    if not return_plan:
+        return out
+    return (*out, plan) if high_precision else (*out, None, plan)
+
+
+def prescale_fp16(dy: Tensor, v_all: Tensor):
+    """Level 1, FP16 only: ``dy`` times a power of two that keeps dS = P (dP - delta), bounded by
+    2 max|dO_i| max|V_j|, near 2^13 and so out of the FP16 subnormals, and the FP32 device scalar that
+    undoes it on the gradients (gradients are linear in ``dy``, so both steps are exact).  Restates
+    xattn/ops/_precision_backend.py:203-225; stays on the device, no synchronisation."""
+    if dy.dtype != torch.float16 or not dy.numel() or not v_all.numel():
+        return dy, None
+    g = torch.linalg.vector_norm(dy, dim=-1, dtype=torch.float32).amax()
+    w = torch.linalg.vector_norm(v_all, dim=-1, dtype=torch.float32).amax()
+    bound = 2 * g * w
+    e = torch.floor(torch.log2(2.0 ** 13 / bound))
+    e = torch.minimum(e, torch.floor(torch.log2(30000.0 / dy.abs().amax().float())))   # dy stays finite
+    e = torch.where(bound > 32768.0, e, e.clamp_min(0))
+    e = torch.where(torch.isfinite(e), e, torch.zeros_like(e)).clamp(-60, 60).to(torch.int32)
+    factor = ((e + 127) << 23).view(torch.float32)
+    return (dy.float() * factor).to(dy.dtype), ((127 - e) << 23).view(torch.float32).reshape(1)
 
 
 def backward(
     dy: Tensor, q: Tensor, k: Tensor, v: Tensor, y: Tensor, lse: Tensor, support: Support, scale: float,
     prev_k: Optional[Tensor], prev_v: Optional[Tensor],
     q_segment_idx: Optional[Tensor], k_segment_idx: Optional[Tensor],
-    *, high_precision: bool = False, plan: Optional[Tensor] = None, recompute: bool = True,
+    *, high_precision: bool = False, plan: Optional[Tensor] = None, anchor: Optional[Tensor] = None,
 ) -> Tuple[Tensor, Tensor, Tensor, Optional[Tensor], Optional[Tensor]]:
-    """(dq, dk, dv, dprev_k, dprev_v).  At level 1 the given ``y`` / ``lse`` are ignored and the
-    statistics are recomputed with the high-precision softmax
-    (xattn/ops/causal_flash_attn.py:144-147), unless the caller vouches that they already come from
-    that forward on these inputs (``recompute=False``: the autograd path, where the recomputation
-    would reproduce the saved tensors bit for bit)."""
+    """(dq, dk, dv, dprev_k, dprev_v).  Level 1 is the anchored backward of ``_native.attention_bwd``
+    followed by the exact zeroing of dQ rows whose visible keys are one repeated vector.  It needs the
+    statistics of the high-precision forward: the given ``y`` / ``lse`` are ignored and the forward is
+    run again (xattn/ops/causal_flash_attn.py:144-147), unless the caller hands over that forward's
+    own ``lse`` and ``anchor`` (the autograd path)."""
     k_all, v_all = concat_previous(k, v, prev_k, prev_v)
     if plan is None:        # the autograd path hands over the forward's plan
         plan = make_plan(q, k_all.shape[1], support, q_segment_idx, k_segment_idx)
-    if high_precision and recompute:
-        y, lse = _native.attention_fwd(q, k_all, v_all, plan, scale, high_precision=True)
-    dq, dk_all, dv_all = _native.attention_bwd(dy, q, k_all, v_all, y, lse, plan, scale)
     if high_precision:
+        if anchor is None:
+            y, lse, anchor = _native.attention_fwd(q, k_all, v_all, plan, scale, high_precision=True,
+                                                   return_anchor=True)
+        dy, unscale = prescale_fp16(dy, v_all)
+        dq, dk_all, dv_all = _native.attention_bwd(dy, q, k_all, v_all, y, lse, plan, scale, anchor=anchor,
+                                                   grad_unscale=unscale)
         dq = _native.zero_constant_key_rows(dq, k_all, plan)
+    else:
+        dq, dk_all, dv_all = _native.attention_bwd(dy, q, k_all, v_all, y, lse, plan, scale)
     if prev_k is None:
         return dq, dk_all, dv_all, None, None
     p = prev_k.shape[1]
@@ -91,17 +117,17 @@ class AttentionFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, prev_k, prev_v, q_segment_idx, k_segment_idx, support, scale, level):
-        y, lse, plan = forward(q, k, v, support, scale, prev_k, prev_v, q_segment_idx, k_segment_idx,
-                               high_precision=bool(level), return_plan=True)
-        ctx.save_for_backward(q, k, v, y, lse, prev_k, prev_v, q_segment_idx, k_segment_idx, plan)
+        y, lse, anchor, plan = forward(q, k, v, support, scale, prev_k, prev_v, q_segment_idx, k_segment_idx,
+                                       high_precision=bool(level), return_plan=True)
+        ctx.save_for_backward(q, k, v, y, lse, prev_k, prev_v, q_segment_idx, k_segment_idx, plan, anchor)
         ctx.support, ctx.scale, ctx.level = support, scale, level
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        q, k, v, y, lse, prev_k, prev_v, q_seg, k_seg, plan = ctx.saved_tensors
+        q, k, v, y, lse, prev_k, prev_v, q_seg, k_seg, plan, anchor = ctx.saved_tensors
         dq, dk, dv, dpk, dpv = backward(dy, q, k, v, y, lse, ctx.support, ctx.scale, prev_k, prev_v,
-                                        q_seg, k_seg, high_precision=bool(ctx.level), plan=plan, recompute=False)
+                                        q_seg, k_seg, high_precision=bool(ctx.level), plan=plan, anchor=anchor)
         return dq, dk, dv, dpk, dpv, None, None, None, None, None
 
 

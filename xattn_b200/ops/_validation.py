@@ -163,6 +163,13 @@ def resolve_segments(
     ``segment_idx`` labels all keys and its suffix labels Q; a BOS mask becomes ids by a running
     count of its set bits (xattn/ops/_bos_metadata.py:84-90); explicit Q / K ids pass through.
     No device value is read.
+
+    Contract: the key ids of a row must never decrease (the keys carrying one id are one contiguous run,
+    which the plan kernels locate by binary search; the reference's kernels assume the same,
+    csrc/attention/partition/segment_index.h:362-363).  BOS masks satisfy it by construction.  The plan
+    kernels compare neighbouring key ids on the device and a violation surfaces as a ``RuntimeError``
+    naming the batch row, at the call itself with ``XATTN_B200_SYNC_CHECK=1``, else at the next call or
+    ``check_status()``.
     """
     batch, q_length = q.shape[0], q.shape[1]
     if bos_mask is not None:

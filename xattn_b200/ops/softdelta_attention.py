@@ -155,11 +155,21 @@ def _backward(dy, q, k, v, g, k_read, prev_k, prev_v, q_ids, k_ids, y, neg_read,
     lse_neg, lse_read = lse[:, :Hkv], lse[:, Hkv:]
     neg = neg_read if neg_read.dtype == q.dtype else neg_read.to(q.dtype)
     if hp:
-        # level 1 recomputes the statistics of both reads with the high-precision softmax
-        read, lse_read = _native.attention_fwd(q, k_all, v_all, plan_inc, scale, high_precision=True)
-        neg, lse_neg = _native.attention_fwd(kr, k_all, v_all, plan_strict, scale, high_precision=True)
-    dq, dk1, dv1 = _native.attention_bwd(dy, q, k_all, v_all, read, lse_read, plan_inc, scale)
-    dkr, dk2, dv2 = _native.attention_bwd(dneg, kr, k_all, v_all, neg, lse_neg, plan_strict, scale)
+        # level 1 recomputes the statistics of both reads with the high-precision softmax, takes their
+        # anchor keys along and runs the anchored backward on each read
+        read, lse_read, a_read = _native.attention_fwd(q, k_all, v_all, plan_inc, scale, high_precision=True,
+                                                       return_anchor=True)
+        neg, lse_neg, a_neg = _native.attention_fwd(kr, k_all, v_all, plan_strict, scale, high_precision=True,
+                                                    return_anchor=True)
+        dy1, un1 = _core.prescale_fp16(dy, v_all)
+        dy2, un2 = _core.prescale_fp16(dneg, v_all)
+        dq, dk1, dv1 = _native.attention_bwd(dy1, q, k_all, v_all, read, lse_read, plan_inc, scale,
+                                             anchor=a_read, grad_unscale=un1)
+        dkr, dk2, dv2 = _native.attention_bwd(dy2, kr, k_all, v_all, neg, lse_neg, plan_strict, scale,
+                                              anchor=a_neg, grad_unscale=un2)
+    else:
+        dq, dk1, dv1 = _native.attention_bwd(dy, q, k_all, v_all, read, lse_read, plan_inc, scale)
+        dkr, dk2, dv2 = _native.attention_bwd(dneg, kr, k_all, v_all, neg, lse_neg, plan_strict, scale)
     if hp:
         dq = _native.zero_constant_key_rows(dq, k_all, plan_inc)
         dkr = _native.zero_constant_key_rows(dkr, k_all, plan_strict)
