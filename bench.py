@@ -46,11 +46,30 @@ if ROOT not in sys.path:
 METRIC = "attn fwd+bwd TFLOPS (bf16 causal S=8K D=128), whole job"
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 
-# DRAM bytes (read + write) of one launch per batch row of S=8192, Hq=32, Hkv=8, D=128, from the ncu
-# capture summarised in profiles/ncu_full_causal_small.md
-NCU_DRAM_BYTES_PER_BATCH_ROW = {"fwd": 137.9e6, "bwd_dq": 215.1e6, "bwd_dkv": 353.3e6}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch on ONE batch row of the
+# workload (S=8192, Hq=32, Hkv=8, D=128), from ncu captures of one launch each: the dense causal
+# row and a row packed with segments ~U[512,4096] (the headline packing).  Traffic grows in
+# proportion to the batch rows (they share no data), so a launch over B rows moves B times this.
+NCU_DRAM_BYTES_PER_BATCH_ROW = {
+    "dense": {"fwd": 137.9e6, "bwd_dq": 215.1e6, "bwd_dkv": 353.3e6},
+    "packed": {"fwd": 137.5e6, "bwd_dq": 211.6e6, "bwd_dkv": 300.6e6},
+}
 
 NCU_DRAM_BYTES_DECODE = 1080.4e6
+
+
+def tensor_roofline(achieved, peaks, peak_src, timed_seconds):
+    """Fractions of the measured dense bf16 peaks.  The burst figure is the denominator for a timed
+    region shorter than a second (the clocks have not settled under the power cap yet), the
+    sustained one for longer regions; both are printed."""
+    burst = float(peaks.get("bf16_tflops", peaks.get("bf16_tflops_sustained")))
+    sustained = float(peaks.get("bf16_tflops_sustained", burst))
+    use_burst = timed_seconds < 1.0
+    peak = burst if use_burst else sustained
+    return {"achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+            "frac_of_burst": achieved / burst, "frac_of_sustained": achieved / sustained,
+            "peak_source": f"{peak_src} {'bf16_tflops (burst' if use_burst else 'bf16_tflops_sustained (sustained'}"
+                           f": the timed region lasted {timed_seconds:.3f} s)"}
 
 WORKLOADS = {
     # name: (B, S, Hq, Hkv, D, packed segments?, description)
@@ -58,6 +77,8 @@ WORKLOADS = {
                       text="configs[1]: causal fwd+bwd bf16 GQA B=4 S=8192 Hq=32 Hkv=8 D=128, packed segments ~U[512,4096], level 0"),
     "causal_small": dict(B=1, S=8192, Hq=32, Hkv=8, D=128, segments=False,
                          text="profiling case: dense causal B=1 S=8192 Hq=32 Hkv=8 D=128 (0.24 GB of tensors, above L2)"),
+    "causal_c2_row": dict(B=1, S=8192, Hq=32, Hkv=8, D=128, segments=True,
+                          text="profiling case: one batch row of configs[1] (causal, packed segments ~U[512,4096]; 0.17 GB of tensors, above L2)"),
     "causal_c2_dense": dict(B=4, S=8192, Hq=32, Hkv=8, D=128, segments=False,
                             text="configs[1] shape with one segment per sequence (dense causal)"),
     # sequence-sharded across the ranks (strong scaling): each rank holds S / N tokens and receives a
@@ -158,58 +179,78 @@ class ClockSampler(threading.Thread):
         }
 
 
-def cpu_oracle_step(q, k, v, dy, ids):
-    """One forward + backward of the CPU oracle in fp32 on the given slice; returns seconds."""
-    from oracle import attention_oracle as O
+def cpu_reference():
+    """(module, kind): the reference's own CPU oracle compiled into oracle/_ref (kind "reference") when it
+    has been built (oracle/build_ref.py), else the restatement in oracle/ (kind "port")."""
+    from oracle import build_ref
+    ref = build_ref.load("_reference")
+    if ref is not None:
+        return ref, "reference"
+    from oracle import attention_oracle
+    return attention_oracle, "port"
+
+
+def cpu_mask(impl, kind, length, ids):
+    """[1, L, L] causal mask with segment isolation, built once outside the timed steps."""
+    if kind == "reference":
+        return impl._allowed_masks(length, length, 1, torch.device("cpu"), "full", None, ids, ids, False)[0]
+    return impl.allowed_masks(length, length, 1, "full", None, ids, ids, False)[0]
+
+
+def cpu_step(impl, kind, q, k, v, dy, mask):
+    """One masked-softmax read forward + autograd backward in fp32 on the host; returns seconds."""
+    read = impl._attention_from_mask if kind == "reference" else impl.attention_from_mask
+    leaves = [t.detach().clone().requires_grad_() for t in (q, k, v)]
     t0 = time.perf_counter()
-    O.forward_backward(q, k, v, dy, visibility="full", q_segment_idx=ids, k_segment_idx=ids)
+    y = read(*leaves, mask, q.shape[-1] ** -0.5)
+    torch.autograd.grad(y, leaves, dy)
     return time.perf_counter() - t0
 
 
 def cpu_baseline_config0(threads):
     """The reference's CPU-sized configuration (configs[0]): B=2, S=1024, Hq=Hkv=8, D=64, fp32."""
-    from oracle import attention_oracle as O
+    impl, kind = cpu_reference()
     torch.set_num_threads(threads)
     g = torch.Generator().manual_seed(0)
     B, S, H, D = 2, 1024, 8, 64
     q, k, v, dy = (torch.randn(B, S, H, D, generator=g) for _ in range(4))
-    times = [cpu_oracle_step(q, k, v, dy, None) for _ in range(3)]
+    mask = cpu_mask(impl, kind, S, None).expand(B, -1, -1)
+    times = [cpu_step(impl, kind, q, k, v, dy, mask) for _ in range(3)]
     pairs = B * H * S * (S + 1) // 2
     flops = 14 * D * pairs
     t = statistics.median(times)
-    return {"value": flops / t * 1e-12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+    return {"value": flops / t * 1e-12, "unit": "TFLOP/s", "cores": threads, "kind": kind,
             "sample": "configs[0] in full (B=2 S=1024 Hq=Hkv=8 D=64 fp32 fwd+bwd), median of 3, "
                       f"{t:.3f} s per step"}
 
 
 def run_reference(args, w):
-    """CPU arm: the oracle (a port of the reference's tests/_reference.py path) on the host cores."""
+    """CPU arm: the reference's own oracle (tests/_reference.py compiled into oracle/_ref; the restatement
+    in oracle/ where that has not been built) on the host cores, with all the threads torch can use."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from oracle import attention_oracle as O
+    impl, kind = cpu_reference()
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     q, k, v, dy, ids = make_host_inputs(w, seed=1)
     # bounded sample: batch row 0, query head 0 (with its KV head), full sequence
     qs, ks, vs, dys = (t[:1, :, :1].float() for t in (q, k, v, dy))
     ids_s = None if ids is None else ids[:1]
-    lo, hi = O.row_intervals(w["S"], w["S"], 1, "full", None, ids_s, ids_s)
-    flops = 14 * w["D"] * O.visible_pairs(lo, hi)
+    mask = cpu_mask(impl, kind, w["S"], ids_s)
+    flops = 14 * w["D"] * int(mask.sum())
     for _ in range(min(args.warmup, 1)):
-        cpu_oracle_step(qs, ks, vs, dys, ids_s)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        cpu_oracle_step(qs, ks, vs, dys, ids_s)
-    dt = (time.perf_counter() - t0) / args.steps
+        cpu_step(impl, kind, qs, ks, vs, dys, mask)
+    dt = sum(cpu_step(impl, kind, qs, ks, vs, dys, mask) for _ in range(args.steps)) / args.steps
     value = flops / dt * 1e-12
-    sample = "one step = batch row 0, query head 0 of the workload (1/128 of a full step), fp32 torch on the host"
+    sample = ("one step = batch row 0, query head 0 of the workload (1/128 of a full step): the masked softmax read "
+              "and its autograd backward in fp32 torch on the host, mask built once beforehand")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": w["text"], "sample": sample},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -367,6 +408,21 @@ def run_ours(args, w):
     ms_step, e2e_ms_step = float(times[0]), float(times[1])
     total_flops = float(work[0])
 
+    # With more than one GPU the sequence-sharded workloads run in the same process group, after the
+    # headline measurement: configs[2] with its K/V halo exchange, and the causal ring.
+    sharded = None
+    if world > 1 and not args.no_sharded:
+        del q, k, v, dy, dev_sets, out_host
+        torch.cuda.empty_cache()
+        sharded = {}
+        for name in ("swa_c3", "ring_causal"):
+            res = measure_sharded(args, WORKLOADS[name], world, rank, dev, with_e2e=False, steps=max(3, min(args.steps, 10)))
+            if rank == 0:
+                sharded[name] = {key: res[key] for key in (
+                    "metric", "value", "unit", "ms_per_step", "scaling", "per_gpu_tflops", "single_gpu_ms",
+                    "efficiency_vs_1gpu", "kernel_ms_per_step", "non_kernel_ms_per_step", "kernels")}
+                sharded[name]["workload"] = res["config"]["workload"]
+
     if rank == 0:
         peaks, peak_src = measured_peaks()
         per_kind = {}
@@ -389,6 +445,8 @@ def run_ours(args, w):
         dominant = max((kd for kd in kernels if kd in algo), key=lambda kd: kernels[kd]["avg_ms"] * kernels[kd]["launches"])
         peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
         achieved = kernels[dominant]["algorithmic_tflops"]
+        packing = "packed" if w["segments"] else "dense"
+        row_traffic = NCU_DRAM_BYTES_PER_BATCH_ROW[packing].get(dominant)
         line = {
             "metric": METRIC, "value": total_flops / ms_step * 1e-9, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
@@ -396,7 +454,9 @@ def run_ours(args, w):
             "config": {"workload": w["text"] if level == 0 else w["text"].replace("level 0", "level 1"),
                        "high_precision_level": level, "l2": "inputs (0.67 GB per step) exceed the 126 MB L2",
                        "visible_pairs_per_step": pairs, "flops_per_step": flops_step,
-                       "parallelism": f"batch x heads sharded over {world} GPU(s), no communication"},
+                       "parallelism": f"batch x heads sharded over {world} GPU(s): embarrassingly parallel, no "
+                                      "communication (every rank runs its own batch); the sequence-sharded "
+                                      "workloads with their exchanges are under 'sharded' when more than one GPU runs"},
             "per_gpu_tflops": total_flops / ms_step * 1e-9 / world,
             "frac_of_measured_bf16_peak": {
                 "burst": total_flops / ms_step * 1e-9 / world / float(peaks.get("bf16_tflops", peak)),
@@ -406,15 +466,17 @@ def run_ours(args, w):
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
             "gpu_launches": launches,
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak,
-                         "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": NCU_DRAM_BYTES_PER_BATCH_ROW.get(dominant, 0) * w["B"] or None,
-                         "traffic_source": "ncu dram__bytes_read+write of one launch at B=1 S=8192 dense "
-                                           "(profiles/ncu_full_causal_small.md), times the batch size",
-                         "peak_source": f"{peak_src} bf16_tflops_sustained (kernel timed inside a long step)",
+            "roofline": {"bound": "tensor", "kernel": dominant,
+                         **tensor_roofline(achieved, peaks, peak_src, ms_total * 1e-3),
+                         "traffic": row_traffic * w["B"] if row_traffic else None,
+                         "traffic_source": (f"ncu dram__bytes_read.sum + dram__bytes_write.sum of one {dominant} launch on "
+                                            f"one {packing} batch row of this workload, times the {w['B']} batch rows"
+                                            if row_traffic else None),
                          "executed_tflops": kernels[dominant]["executed_tflops"]},
             "kernels": kernels,
         }
+        if sharded is not None:
+            line["sharded"] = sharded
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_config0(os.cpu_count() or 1)
         print(json.dumps(line))
@@ -480,8 +542,8 @@ def run_decode(args, w, world, rank, dev):
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "fwd (decode shape) + merge", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_DECODE,
-                         "traffic_source": "ncu dram__bytes_read+write of one launch of each kernel on this "
-                                           "workload (profiles/ncu_full_decode.md)",
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of each "
+                                           "kernel on this workload",
                          "peak_source": f"{peak_src} hbm_gbs (copy bandwidth)"},
             "kernel_ms": kernel_ms,
         }))
@@ -592,25 +654,23 @@ def run_other(args, w, world, rank, dev):
             # a plan scope holds four kernels, a level-1 repair scope three, every other scope one
             "gpu_launches": len(records) + 3 * len(per_kind.get("plan", [])) + 2 * len(per_kind.get("repair", [])),
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "bwd_dkv (all its launches of a step)", "achieved": achieved,
-                         "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
-                         "peak_source": f"{peak_src} bf16_tflops_sustained"},
+            "roofline": {"bound": "tensor", "kernel": "bwd_dkv (all its launches of a step)",
+                         **tensor_roofline(achieved, peaks, peak_src, ms_step * args.steps * 1e-3), "traffic": None},
             "kernels": kernels,
         }))
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_swa_sharded(args, w, world, rank, dev):
-    """One sequence of S tokens split over the ranks, total work fixed: configs[2] (sliding window,
-    contiguous slices, K/V halo exchange) or the causal ring (zig-zag slices)."""
+def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
+    """One sequence of S tokens split over the ranks of the current process group, total work fixed:
+    configs[2] (sliding window, contiguous slices, K/V halo exchange) or the causal ring (zig-zag
+    slices).  Returns the result dictionary on rank 0 (None elsewhere).  Rank 0 also times the same
+    sequence unsharded on its own GPU while the others wait, for the strong-scaling efficiency."""
     import torch.distributed as dist
     import xattn_b200 as xattn
     from xattn_b200 import _native, parallel as P
 
-    if world == 1:
-        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=os.environ.get("MASTER_PORT", "29533"))
-        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
     ring = bool(w.get("ring"))
     S, D, window = w["S"], w["D"], w.get("window", 0)
     if S % (2 * world) or S // world < window:
@@ -644,16 +704,16 @@ def run_swa_sharded(args, w, world, rank, dev):
     sampler.start()
     _native.profile_enable(True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step(ql, kl, vl, dyl)
     e1.record()
     barrier()
     _native.profile_enable(False)
     records = _native.profile_read()
-    ms = e0.elapsed_time(e1) / args.steps
+    ms = e0.elapsed_time(e1) / steps
     out_host = None
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 10))
+    e2e_steps = max(3, min(steps, 10)) if with_e2e else 0
 
     def e2e_step():
         nonlocal out_host
@@ -663,7 +723,7 @@ def run_swa_sharded(args, w, world, rank, dev):
         for dst, src in zip(out_host, outs):
             dst.copy_(src, non_blocking=True)
 
-    for _ in range(0 if args.no_e2e else 2):
+    for _ in range(2 if with_e2e else 0):
         e2e_step()
     barrier()
     f0.record()
@@ -673,47 +733,85 @@ def run_swa_sharded(args, w, world, rank, dev):
     barrier()
     e2e_ms = f0.elapsed_time(f1) / max(e2e_steps, 1)
     clocks = sampler.stop()
+    # the same sequence unsharded on one GPU (rank 0 alone), device-timed
+    single_ms = None
+    if world > 1 and rank == 0:
+        qf, kf, vf, dyf = (t.to(dev) for t in (q, k, v, dy))
+
+        def single():
+            a, b, c = (t.detach().requires_grad_() for t in (qf, kf, vf))
+            y = xattn.causal_flash_attn(a, b, c) if ring else xattn.flash_swa(a, b, c, window)
+            return torch.autograd.grad(y, (a, b, c), dyf)
+
+        for _ in range(3):
+            single()
+        torch.cuda.synchronize()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(max(3, min(steps, 5))):
+            single()
+        s1.record()
+        torch.cuda.synchronize()
+        single_ms = s0.elapsed_time(s1) / max(3, min(steps, 5))
+        _native.check_status()
+        del qf, kf, vf, dyf
+    barrier()
     times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(times[0]), float(times[1])
+    if rank != 0:
+        return None
+    peaks, peak_src = measured_peaks()
+    per_kind = {}
+    for kind, t in records:
+        per_kind.setdefault(kind, []).append(t)
+    kernels = {kd: {"launches": len(vs), "avg_ms": sum(vs) / len(vs), "ms_per_step": sum(vs) / steps,
+                    "share": sum(vs) / (ms * steps)} for kd, vs in per_kind.items()}
+    kernel_ms = sum(kv["ms_per_step"] for kv in kernels.values())
+    rank_pairs = pairs / world
+    dkv = kernels.get("bwd_dkv", {"avg_ms": float("inf"), "launches": 1})
+    # the ring launches the kernel once per block step; the work of a rank is spread over them
+    achieved = 8 * D * rank_pairs / (dkv["avg_ms"] * dkv["launches"] / steps) * 1e-9
+    h2d = sum(t.numel() * t.element_size() for t in pinned) * world
+    d2h = sum(t.numel() * t.element_size() for t in out_host) * world if out_host else 0
+    return {
+        "metric": ("causal ring attn fwd+bwd TFLOPS (bf16 S=32K D=128), whole job" if ring else
+                   "sliding-window attn fwd+bwd TFLOPS (bf16 S=32K w=4096 D=128), whole job"),
+        "value": flops_step / ms * 1e-9, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": w["text"], "l2": "0.27 GB of tensors per step in total",
+                   "visible_pairs_per_step": pairs, "flops_per_step": flops_step,
+                   "parallelism": (f"sequence split over {world} GPU(s) in the zig-zag layout; ring of K/V blocks "
+                                   "(NCCL send/recv), partial outputs merged by lse, dK/dV travel home with their block"
+                                   if ring else
+                                   f"sequence split over {world} GPU(s); K/V halo of {window} tokens from the "
+                                   "previous rank (NCCL send/recv), halo gradients sent back")},
+        "per_gpu_tflops": flops_step / ms * 1e-9 / world,
+        # strong scaling: time of the unsharded sequence on one GPU over N times the sharded time
+        "single_gpu_ms": single_ms,
+        "efficiency_vs_1gpu": None if single_ms is None else single_ms / (world * ms),
+        # rank 0's kernels against its step: the rest is exchange, copies and launch gaps
+        "kernel_ms_per_step": kernel_ms, "non_kernel_ms_per_step": ms - kernel_ms,
+        "e2e": None if not e2e_steps else {"value": flops_step / e2e_ms * 1e-9, "unit": "TFLOP/s",
+                                           "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                                           "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+        "gpu_launches": len(records) + 3 * len(per_kind.get("plan", [])),
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "bwd_dkv",
+                     **tensor_roofline(achieved, peaks, peak_src, ms * steps * 1e-3), "traffic": None},
+        "kernels": kernels,
+    }
+
+
+def run_swa_sharded(args, w, world, rank, dev):
+    import torch.distributed as dist
+    if world == 1:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=os.environ.get("MASTER_PORT", "29533"))
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    line = measure_sharded(args, w, world, rank, dev, with_e2e=not args.no_e2e, steps=args.steps)
     if rank == 0:
-        peaks, peak_src = measured_peaks()
-        peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
-        per_kind = {}
-        for kind, t in records:
-            per_kind.setdefault(kind, []).append(t)
-        kernels = {kd: {"launches": len(vs), "avg_ms": sum(vs) / len(vs), "share": sum(vs) / (ms * args.steps)}
-                   for kd, vs in per_kind.items()}
-        rank_pairs = pairs / world
-        dkv = kernels.get("bwd_dkv", {"avg_ms": float("inf"), "launches": 1})
-        # the ring launches the kernel once per block step; the work of a rank is spread over them
-        achieved = 8 * D * rank_pairs / (dkv["avg_ms"] * dkv["launches"] / args.steps) * 1e-9
-        h2d = sum(t.numel() * t.element_size() for t in pinned) * world
-        d2h = sum(t.numel() * t.element_size() for t in out_host) * world if out_host else 0
-        print(json.dumps({
-            "metric": ("causal ring attn fwd+bwd TFLOPS (bf16 S=32K D=128), whole job" if ring else
-                       "sliding-window attn fwd+bwd TFLOPS (bf16 S=32K w=4096 D=128), whole job"),
-            "value": flops_step / ms * 1e-9, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": w["text"], "l2": "0.27 GB of tensors per step in total",
-                       "visible_pairs_per_step": pairs, "flops_per_step": flops_step,
-                       "parallelism": (f"sequence split over {world} GPU(s) in the zig-zag layout; ring of K/V blocks "
-                                       "(NCCL send/recv), partial outputs merged by lse, dK/dV travel home with their block"
-                                       if ring else
-                                       f"sequence split over {world} GPU(s); K/V halo of {window} tokens from the "
-                                       "previous rank (NCCL send/recv), halo gradients sent back")},
-            "per_gpu_tflops": flops_step / ms * 1e-9 / world,
-            "e2e": None if not e2e_steps else {"value": flops_step / e2e_ms * 1e-9, "unit": "TFLOP/s",
-                                               "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
-                                               "d2h_bytes_per_step": d2h, "steps": e2e_steps},
-            "gpu_launches": len(records) + 3 * len(per_kind.get("plan", [])),
-            "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "bwd_dkv", "achieved": achieved, "peak": peak,
-                         "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
-                         "peak_source": f"{peak_src} bf16_tflops_sustained"},
-            "kernels": kernels,
-        }))
+        print(json.dumps(line))
     dist.destroy_process_group()
 
 
@@ -728,6 +826,8 @@ def main():
                     help="high_precision_level (default 0; the causal, sca_c4 and softdelta workloads take 1 too)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-sharded", action="store_true",
+                    help="with more than one GPU: skip the sequence-sharded workloads after the headline measurement")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference" and (w.get("decode") or w.get("other") or w["S"] > 8192):

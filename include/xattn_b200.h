@@ -307,6 +307,13 @@ int xattn_b200_softdelta_merge_gradients(const XattnMergeArgs* args, xattn_strea
 int xattn_b200_profile_enable(int enable);
 int xattn_b200_profile_read(int* kinds, float* ms, int capacity);
 
+/* Self-test of the bounded device-side wait (no counterpart in the reference, whose kernels wait
+ * without a limit): launches one small CTA that waits on a barrier nothing completes, for at most
+ * `budget_us` microseconds (1 .. 100000), and then stores (99 << 8) | 1 in `status`, the code every
+ * kernel of this library reports when one of its waits runs out.  Nothing faults or hangs; the
+ * context stays usable.  `status` must be zero on entry. */
+int xattn_b200_selftest_wait_timeout(int32_t* status, int64_t budget_us, xattn_stream_t stream);
+
 /* Reads `status` back (synchronises the stream).  0 when the word is zero. */
 int xattn_b200_check_status(const int32_t* status, xattn_stream_t stream);
 

@@ -99,9 +99,10 @@ def _llm_like_inputs(dtype, device, n=700, d=64, heads=4):
 @pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16), ids=("bf16", "fp16"))
 def test_sink_anchor_rows(dtype, cuda_device):
     """Hundreds of rows anchored on key 0 (tests/test_high_precision.py:352-368): gradients stay bitwise
-    repeatable, deterministic or not, and match the FP64 oracle to 2e-3 of each gradient's norm (the bound
-    the reference puts between its ordered and unordered reductions; the sink key's dK sums thousands of
-    rounded terms, which an element-wise FP16 tolerance does not allow for)."""
+    repeatable, deterministic or not, and match the FP64 oracle to 2e-3 (FP16) / 5e-3 (BF16, whose final
+    rounding alone is 2e-3 per element) of each gradient's norm; 2e-3 is the bound the reference puts
+    between its ordered and unordered reductions.  The sink key's dK sums thousands of rounded terms,
+    which an element-wise tolerance does not allow for."""
     inputs = _llm_like_inputs(dtype, cuda_device)
     n = inputs[0].shape[1]
     dy = (torch.randn(1, n, 4, 64, generator=torch.Generator().manual_seed(8)) / n ** 0.5).to(cuda_device, dtype)
@@ -124,7 +125,7 @@ def test_sink_anchor_rows(dtype, cuda_device):
     gr = torch.autograd.grad(yr, refs, dy.double().cpu())
     for got, ref in zip(results[0], gr):
         assert torch.isfinite(got).all()
-        assert (got.double().cpu() - ref).norm() <= 2e-3 * ref.norm()
+        assert (got.double().cpu() - ref).norm() <= (2e-3 if dtype == torch.float16 else 5e-3) * ref.norm()
 
 
 def test_deterministic_long_segments(cuda_device):

@@ -85,3 +85,81 @@ def test_visible_pair_count_causal():
     assert O.visible_pairs(lo, hi) == sum(min(i, 7) + 1 for i in range(64))
     lo, hi = O.row_intervals(64, 64, 1, "chunk", 8)
     assert O.visible_pairs(lo, hi) == sum(i - max(0, (i // 8 - 1) * 8) + 1 for i in range(64))
+
+
+def _compiled_reference():
+    from oracle import build_ref
+    return build_ref.load("_reference"), build_ref.load("reference")
+
+
+@pytest.mark.parametrize("operation", ("full", "window", "chunk"))
+def test_port_matches_compiled_reference(operation):
+    """oracle/_ref holds the reference's own oracle compiled from its sources (oracle/build_ref.py): on
+    the whole parity matrix the restatement gives the same masks bit for bit and the same reads and
+    gradients to FP64 rounding.  Skipped where oracle/_ref has not been built."""
+    ref, _ = _compiled_reference()
+    if ref is None:
+        pytest.skip("oracle/_ref not built (python oracle/build_ref.py <reference root>)")
+    from tests._cases import make_inputs
+    cpu = torch.device("cpu")
+    for case in cases_for(operation):
+        total = case.k_length + case.previous
+        if case.q_length * total > 80000:
+            continue
+        _, qi, ki = metadata_for(case, cpu)
+        mine = O.allowed_masks(case.q_length, total, case.batch, operation, case.span, qi, ki, case.reset)
+        theirs = ref._allowed_masks(case.q_length, total, case.batch, cpu, operation, case.span, qi, ki, case.reset)
+        for a, b in zip(mine, theirs):
+            assert torch.equal(a, b.expand_as(a)), case.name
+        inputs = make_inputs(operation, case, torch.bfloat16, 2, cpu)
+        q, k, v = (t.detach().double() for t in inputs[:3])
+        if case.previous:
+            k = torch.cat((inputs[-2].detach().double(), k), 1)
+            v = torch.cat((inputs[-1].detach().double(), v), 1)
+        outs = []
+        for read in (O.attention_from_mask, ref._attention_from_mask):
+            leaves = [t.clone().requires_grad_() for t in (q, k, v)]
+            y = read(*leaves, mine[0], case.dim ** -0.5)
+            dy = torch.randn(y.shape, generator=torch.Generator().manual_seed(5), dtype=torch.float64)
+            outs.append((y.detach(), *torch.autograd.grad(y, leaves, dy)))
+        for a, b in zip(*outs):
+            torch.testing.assert_close(a, b, rtol=1e-12, atol=1e-13)
+
+
+def test_softdelta_port_matches_compiled_reference():
+    _, ref = _compiled_reference()
+    if ref is None:
+        pytest.skip("oracle/_ref not built (python oracle/build_ref.py <reference root>)")
+    gen = torch.Generator().manual_seed(12)
+    B, L, H, Hkv, D, V = 2, 37, 4, 2, 16, 24
+    mk = lambda *s: torch.randn(s, generator=gen, dtype=torch.float64)
+    q, k, v, g = mk(B, L, H, D), mk(B, L, Hkv, D), mk(B, L, Hkv, V), mk(B, L, H)
+    ids = (torch.arange(L) // 11).expand(B, -1).contiguous()
+    for vis, span in (("full", None), ("window", 5), ("chunk", 8)):
+        kw = dict(scale=0.3, q_segment_idx=ids, k_segment_idx=ids, visibility=vis, span=span)
+        mine = O.softdelta(q, k, v, g, None, **kw)[0]
+        theirs = ref.softdelta_fp64_oracle(q, k, v, g, None, **kw)
+        theirs = theirs[0] if isinstance(theirs, tuple) else theirs
+        torch.testing.assert_close(mine, theirs, rtol=1e-12, atol=1e-13)
+
+
+def test_hand_written_gradients_of_the_bounds_helper():
+    """tests/_bounds.py writes the read's gradients out by hand (to get at the magnitudes its tolerances
+    scale with): they equal autograd of the oracle, and every magnitude is at least the value."""
+    from tests._bounds import read_with_scales
+    gen = torch.Generator().manual_seed(21)
+    B, R, Lk, H, Hkv, D, V = 2, 7, 33, 4, 2, 16, 24
+    mk = lambda *s: torch.randn(s, generator=gen, dtype=torch.float64)
+    q, k, v, dy = mk(B, R, H, D), mk(B, Lk, Hkv, D), mk(B, Lk, Hkv, V), mk(B, R, H, V)
+    rows = torch.tensor([0, 3, 9, 10, 20, 31, 32])
+    ids = (torch.arange(Lk) // 10).expand(B, -1).contiguous()
+    mask, _ = O.allowed_masks(Lk, Lk, B, "window", 6, ids, ids, False, rows=rows)
+    mask[:, 2] = False                        # a row without keys
+    leaves = [t.clone().requires_grad_() for t in (q, k, v)]
+    y = O.attention_from_mask(*leaves, mask, 0.25)
+    grads = torch.autograd.grad(y, leaves, dy)
+    got = read_with_scales(q, k, v, mask, dy, 0.25)
+    for a, b in zip((got.y, got.dq, got.dk, got.dv), (y.detach(), *grads)):
+        torch.testing.assert_close(a, b, rtol=1e-12, atol=1e-13)
+    for val, mag in ((got.y, got.y_scale), (got.dq, got.dq_scale), (got.dk, got.dk_scale), (got.dv, got.dv_scale)):
+        assert torch.all(mag + 1e-15 >= val.abs())

@@ -28,6 +28,7 @@ from .ops import (  # noqa: F401
     softdelta_attention_fwd,
 )
 from ._native import check_status  # noqa: F401
+from .ops._core import clear_plan_cache  # noqa: F401
 from .ops import __all__ as _ops_all
 
-__all__ = list(_ops_all) + ["check_status"]
+__all__ = list(_ops_all) + ["check_status", "clear_plan_cache"]

@@ -125,6 +125,7 @@ SYMBOLS = {
     "xattn_b200_softdelta_merge_gradients": (C.c_int, [C.POINTER(MergeArgs), C.c_void_p]),
     "xattn_b200_profile_enable": (C.c_int, [C.c_int]),
     "xattn_b200_profile_read": (C.c_int, [C.POINTER(C.c_int), C.POINTER(C.c_float), C.c_int]),
+    "xattn_b200_selftest_wait_timeout": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p]),
     "xattn_b200_check_status": (C.c_int, [C.c_void_p, C.c_void_p]),
 }
 

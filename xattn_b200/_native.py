@@ -102,6 +102,19 @@ def check_status(device: Optional[torch.device] = None) -> None:
         _raise_status(value)
 
 
+def selftest_wait_timeout(device: torch.device, budget_us: int = 2000) -> None:
+    """Launch the library's wait-timeout probe on ``device``: a kernel whose wait runs out after
+    ``budget_us`` microseconds and reports it in the device status word, exactly as a stuck tensor
+    kernel would.  The next status check on that device (``check_status()``, or the next launch)
+    raises."""
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        st = _pre_launch(device)
+        _lib.check(lib.xattn_b200_selftest_wait_timeout(st.status.data_ptr(), int(budget_us), _stream_ptr()),
+                   "xattn_b200_selftest_wait_timeout")
+        _post_launch(st)
+
+
 def require_cuda(t: Tensor, api_name: str) -> None:
     if not t.is_cuda:
         raise RuntimeError(f"{api_name} needs CUDA tensors; this build has no CPU path")

@@ -14,6 +14,7 @@ int zero_constant_entry(const XattnConstantKeyArgs* a, cudaStream_t stream);
 int merge_gradients_entry(const XattnMergeArgs* a, cudaStream_t stream);
 int build_plan_entry(const XattnPlanArgs* a, cudaStream_t stream);
 int build_varlen_plan_entry(const XattnVarlenPlanArgs* a, cudaStream_t stream);
+int wait_timeout_probe_entry(int32_t* status, int64_t budget_us, cudaStream_t stream);
 }  // namespace xb
 
 extern "C" {
@@ -94,6 +95,10 @@ int xattn_b200_profile_enable(int enable) { return xb::profile_enable(enable); }
 int xattn_b200_profile_read(int* kinds, float* ms, int capacity) {
   if (!kinds || !ms || capacity < 0) return XATTN_E_INVALID;
   return xb::profile_read(kinds, ms, capacity);
+}
+
+int xattn_b200_selftest_wait_timeout(int32_t* status, int64_t budget_us, xattn_stream_t stream) {
+  return xb::wait_timeout_probe_entry(status, budget_us, static_cast<cudaStream_t>(stream));
 }
 
 int xattn_b200_check_status(const int32_t* status, xattn_stream_t stream) {

@@ -453,4 +453,36 @@ int zero_constant_entry(const XattnConstantKeyArgs* a, cudaStream_t s) {
   return XATTN_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Self-test of the bounded wait: one CTA waits on a barrier that nothing will ever complete, with a
+// short time limit, and must come back with (site << 8) | kStatusWaitTimeout in the status word
+// instead of hanging.  This is the path every tensor kernel takes when a bulk copy or a product never
+// signals; nothing faults and the context stays usable.
+// ---------------------------------------------------------------------------
+constexpr int kProbeSite = 99;
+
+__global__ void __launch_bounds__(64) wait_timeout_probe_kernel(int* status, unsigned long long budget_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  WaitCtx ctx{&abort_flag, status, budget_ns};
+  if (threadIdx.x == 0) mbar_wait(ctx, &bar, 0, kProbeSite);            // runs out: sets the flag and the status
+  else if (threadIdx.x == 32) mbar_wait(ctx, &bar, 0, kProbeSite + 1);   // sees the flag or runs out itself
+  __syncthreads();
+}
+
+int wait_timeout_probe_entry(int32_t* status, int64_t budget_us, cudaStream_t s) {
+  if (!status) { set_error("null status word"); return XATTN_E_INVALID; }
+  if (budget_us < 1 || budget_us > 100000) { set_error("the probe's time limit must be 1 .. 100000 microseconds"); return XATTN_E_INVALID; }
+  wait_timeout_probe_kernel<<<1, 64, 0, s>>>(status, (unsigned long long)budget_us * 1000ull);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_error("probe launch: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
+  return XATTN_OK;
+}
+
 }  // namespace xb

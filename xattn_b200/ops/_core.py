@@ -10,6 +10,9 @@ host synchronisation.
 """
 from __future__ import annotations
 
+import os
+import threading
+from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -36,14 +39,105 @@ def concat_previous(k: Tensor, v: Tensor, prev_k: Optional[Tensor], prev_v: Opti
     return torch.cat((prev_k, k), dim=1), torch.cat((prev_v, v), dim=1)
 
 
+class _PlanCache(threading.local):
+    """Mask plans (and the segment ids of BOS masks) of recent calls, per thread.
+
+    The reference keeps a thread-local cache of its sliding-chunk forward plan for inference with
+    repeated BOS masks, keyed by tensor identity and stream
+    (csrc/flash_sca/sliding_chunk_attention.cc:113-518, xattn/ops/sliding_chunk_attention.py:2163-2297),
+    because building that plan synchronises with the host.  The plan here is built on the device, so
+    the cache only saves its three to five small kernels (and the running sum over a BOS mask): what
+    matters for decode-sized calls, where they cost as much as the attention itself.
+
+    * A dense plan (no segment metadata) depends on nothing but the shapes and the visibility rule: it
+      is cached for every call (per stream, like every entry: a plan is ready in the order of the stream
+      that built it).
+    * A plan built from segment ids or a BOS mask is cached only when autograd is off, keyed by the
+      identity of the metadata tensor (storage address, offset, shape, strides, version counter) and
+      the current stream; the entry holds the tensor, so its memory cannot be handed to another tensor
+      meanwhile.  Tensors created under inference mode have no version counter: after writing into
+      such a mask in place, call ``clear_plan_cache()``.
+    * Nothing is stored while a CUDA graph is being captured (memory of the capture's private pool
+      must not outlive it); lookups still work.
+    ``XATTN_B200_PLAN_CACHE=0`` disables it."""
+
+    CAPACITY = 16
+
+    def __init__(self):
+        self.entries: "OrderedDict[tuple, tuple]" = OrderedDict()
+        self.hits = 0
+        self.misses = 0
+
+    def get(self, key):
+        hit = self.entries.get(key)
+        if hit is None:
+            self.misses += 1
+            return None
+        self.entries.move_to_end(key)
+        self.hits += 1
+        return hit
+
+    def put(self, key, value):
+        if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():
+            return
+        self.entries[key] = value
+        while len(self.entries) > self.CAPACITY:
+            self.entries.popitem(last=False)
+
+
+_plan_cache = _PlanCache()
+
+
+def plan_cache_enabled() -> bool:
+    return os.environ.get("XATTN_B200_PLAN_CACHE", "1") != "0"
+
+
+def clear_plan_cache() -> None:
+    """Drop every cached plan of the calling thread (the reference's
+    ``_flash_sca_sm90_clear_inference_bos_fwd_plan_cache``)."""
+    _plan_cache.entries.clear()
+
+
+def plan_cache_stats() -> Tuple[int, int]:
+    """(hits, misses) of the calling thread since start."""
+    return _plan_cache.hits, _plan_cache.misses
+
+
+def _identity(t: Optional[Tensor]):
+    """What makes a metadata tensor 'the same tensor with the same contents' for the cache."""
+    if t is None:
+        return None
+    try:
+        version = t._version
+    except RuntimeError:            # inference tensors do not count their writes
+        version = -1
+    return (t.data_ptr(), t.storage_offset(), tuple(t.shape), tuple(t.stride()), t.dtype, version)
+
+
+def _metadata_cacheable() -> bool:
+    return plan_cache_enabled() and not torch.is_grad_enabled()
+
+
 def make_plan(q: Tensor, k_length: int, support: Support,
               q_segment_idx: Optional[Tensor], k_segment_idx: Optional[Tensor]) -> Tensor:
-    return _native.build_plan(
+    dense = q_segment_idx is None
+    use_cache = plan_cache_enabled() and q.is_cuda and (dense or not torch.is_grad_enabled())
+    key = None
+    if use_cache:
+        key = ("plan", q.device, q.shape[0], q.shape[1], k_length, support, _identity(q_segment_idx),
+               _identity(k_segment_idx), torch.cuda.current_stream(q.device).cuda_stream)
+        hit = _plan_cache.get(key)
+        if hit is not None:
+            return hit[0]
+    plan = _native.build_plan(
         q.shape[0], q.shape[1], k_length, q.device,
         visibility=support.kind, span=support.span, strict_past=support.strict,
         reset_positions=support.reset and q_segment_idx is not None,
         q_segment_idx=q_segment_idx, k_segment_idx=k_segment_idx,
     )
+    if use_cache:
+        _plan_cache.put(key, (plan, q_segment_idx, k_segment_idx))      # the ids stay alive with the entry
+    return plan
 
 
 def forward(
@@ -138,8 +232,24 @@ def prepare(
     V.normalize_backend(backend, api_name)
     prev_length = V.validate_qkv(q, k, v, prev_k, prev_v, api_name=api_name)
     _native.require_cuda(q, api_name)
-    return V.resolve_segments(q, k.shape[1] + prev_length, segment_idx, q_segment_idx, k_segment_idx,
-                              bos_mask, api_name=api_name)
+    return resolve_segments_cached(q, k.shape[1] + prev_length, segment_idx, q_segment_idx, k_segment_idx,
+                                   bos_mask, api_name=api_name)
+
+
+def resolve_segments_cached(q, k_length, segment_idx, q_segment_idx, k_segment_idx, bos_mask, *, api_name):
+    """``_validation.resolve_segments``, with the ids of a BOS mask seen before (autograd off) taken from
+    the plan cache: the same id tensors come back, so the plan built from them is found again too."""
+    only_bos = bos_mask is not None and segment_idx is None and q_segment_idx is None and k_segment_idx is None
+    if not (only_bos and isinstance(bos_mask, Tensor) and bos_mask.is_cuda and _metadata_cacheable()):
+        return V.resolve_segments(q, k_length, segment_idx, q_segment_idx, k_segment_idx, bos_mask, api_name=api_name)
+    key = ("bos", q.device, q.shape[0], q.shape[1], k_length, _identity(bos_mask),
+           torch.cuda.current_stream(q.device).cuda_stream)
+    hit = _plan_cache.get(key)
+    if hit is not None:
+        return hit[0], hit[1]
+    ids = V.resolve_segments(q, k_length, None, None, None, bos_mask, api_name=api_name)
+    _plan_cache.put(key, (ids[0], ids[1], bos_mask))
+    return ids
 
 
 def attention(q, k, v, support: Support, scale, prev_k, prev_v, q_segment_idx, k_segment_idx, *,

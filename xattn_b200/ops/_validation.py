@@ -105,7 +105,7 @@ def validate_qkv(
         if not isinstance(t, Tensor):
             raise TypeError(f"{api_name} q/k/v must be tensors")
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
-        raise ValueError(f"{api_name} expects 4D [B, L, H, D] q/k/v")
+        raise ValueError(f"{api_name} expects 4D q/k/v tensors laid out [B, L, H, D]")
     if q.device != k.device or q.device != v.device:
         raise ValueError(f"{api_name} q/k/v must share a device")
     if q.dtype != k.dtype or q.dtype != v.dtype:
@@ -146,6 +146,27 @@ def validate_qkv(
     ):
         raise ValueError(f"{api_name} previous K/V shapes are incompatible with Q/K/V")
     return prev_k.shape[1]
+
+
+def validate_gate_and_reader(q: Tensor, k: Tensor, g, k_read, deterministic, *, api_name: str) -> None:
+    """What SoftDelta adds to the q/k/v contract: one gate logit per (token, query head), an optional
+    second reader shaped like the aligned keys, both in q's dtype on q's device
+    (xattn/ops/softdelta_attention.py:101-166; message keywords ``g must have shape`` and
+    ``k_read must have shape`` are pinned by the reference's tests)."""
+    if not isinstance(deterministic, bool):
+        raise TypeError(f"{api_name} deterministic must be a bool")
+    extras = {"g": (g, tuple(q.shape[:3])), "k_read": (k_read, (q.shape[0], q.shape[1], k.shape[2], q.shape[3]))}
+    for name, (tensor, shape) in extras.items():
+        if tensor is None and name == "k_read":
+            continue
+        if not isinstance(tensor, Tensor):
+            raise TypeError(f"{api_name} {name} must be a tensor")
+        if tensor.device != q.device:
+            raise ValueError(f"{api_name} q/k/v/g/k_read must share a device")
+        if tensor.dtype != q.dtype:
+            raise ValueError(f"{api_name} q/k/v/g/k_read must share a dtype")
+        if tuple(tensor.shape) != shape:
+            raise ValueError(f"{api_name} {name} must have shape {list(shape)}")
 
 
 def resolve_segments(

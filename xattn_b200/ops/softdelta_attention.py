@@ -25,7 +25,8 @@ from .. import _native
 from . import _core
 from ._validation import (dispatch_nonpositive_scale, resolve_scale, resolve_segments,
                           validate_attention_scale, validate_chunk_size, validate_dimensions,
-                          validate_high_precision_level, validate_window_size)
+                          validate_gate_and_reader, validate_high_precision_level, validate_qkv,
+                          validate_window_size)
 
 __all__ = [
     "softdelta_attention", "softdelta_attention_fwd", "softdelta_attention_bwd",
@@ -46,56 +47,10 @@ def _normalize_backend(backend) -> str:
 
 
 def _validate(q, k, v, g, k_read, prev_k, prev_v, deterministic, api_name) -> int:
-    """The scalar-gate layout contract (xattn/ops/softdelta_attention.py:103-170)."""
-    if not isinstance(deterministic, bool):
-        raise TypeError(f"{api_name} deterministic must be a bool")
-    for t in (q, k, v, g):
-        if not isinstance(t, Tensor):
-            raise TypeError(f"{api_name} q/k/v/g must be tensors")
-    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
-        raise ValueError(f"{api_name} expects 4D q/k/v tensors")
-    tensors = (k, v, g) if k_read is None else (k, v, g, k_read)
-    if any(t.device != q.device for t in tensors):
-        raise ValueError(f"{api_name} q/k/v/g/k_read must share a device")
-    if any(t.dtype != q.dtype for t in tensors):
-        raise ValueError(f"{api_name} q/k/v/g/k_read must share a dtype")
-    if q.dtype not in (torch.float16, torch.bfloat16):
-        raise ValueError(f"{api_name} supports only fp16 and bf16 inputs")
-    batch, q_length, q_heads, qk_dim = q.shape
-    if batch <= 0 or q_length <= 0 or q_heads <= 0 or qk_dim <= 0:
-        raise ValueError(f"{api_name} q dimensions must be positive")
-    if k.shape[0] != batch or k.shape[:2] != v.shape[:2]:
-        raise ValueError(f"{api_name} batch dimensions and k/v lengths must match")
-    if q_length > k.shape[1]:
-        raise ValueError(f"{api_name} requires q length <= current k/v length")
-    kv_heads = k.shape[2]
-    if kv_heads <= 0 or v.shape[2] != kv_heads:
-        raise ValueError(f"{api_name} k/v head counts must match and be positive")
-    if q_heads % kv_heads != 0:
-        raise ValueError(f"{api_name} q head count must be divisible by KV heads")
-    if k.shape[-1] != qk_dim:
-        raise ValueError(f"{api_name} q/k head dimensions must match")
-    if k_read is not None and tuple(k_read.shape) != (batch, q_length, kv_heads, qk_dim):
-        raise ValueError(f"{api_name} k_read must have shape {[batch, q_length, kv_heads, qk_dim]}")
-    if v.shape[3] <= 0:
-        raise ValueError(f"{api_name} value dimension must be positive")
-    if tuple(g.shape) != (batch, q_length, q_heads):
-        raise ValueError(f"{api_name} g must have shape {[batch, q_length, q_heads]}")
-    if (prev_k is None) != (prev_v is None):
-        raise ValueError(f"{api_name} prev_k and prev_v must be provided together")
-    if prev_k is None:
-        return 0
-    if prev_k.device != q.device or prev_v.device != q.device:
-        raise ValueError(f"{api_name} previous and current tensors must share a device")
-    if prev_k.dtype != q.dtype or prev_v.dtype != q.dtype:
-        raise ValueError(f"{api_name} previous and current tensors must share a dtype")
-    prev_length = prev_k.shape[1] if prev_k.dim() == 4 else 0
-    if prev_length <= 0:
-        raise ValueError(f"{api_name} previous sequence length must be positive")
-    if tuple(prev_k.shape) != (batch, prev_length, kv_heads, qk_dim):
-        raise ValueError(f"{api_name} prev_k shape is incompatible with q/k")
-    if tuple(prev_v.shape) != (batch, prev_length, kv_heads, v.shape[3]):
-        raise ValueError(f"{api_name} prev_v shape is incompatible with v")
+    """The shared q/k/v (+ previous K/V) contract, then the gate and the second reader; returns the
+    previous-K/V length."""
+    prev_length = validate_qkv(q, k, v, prev_k, prev_v, api_name=api_name)
+    validate_gate_and_reader(q, k, g, k_read, deterministic, api_name=api_name)
     return prev_length
 
 
