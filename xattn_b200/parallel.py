@@ -5,12 +5,14 @@ The reference is a single-GPU library; its chunk-to-chunk seam ``prev_k / prev_v
 sequence-parallel run needs, and this module plugs communication into it:
 
 * sliding-window and sliding-chunk attention: rank ``r`` holds a contiguous slice of the sequence and
-  needs only the last ``window`` (or ``chunk``) keys / values of rank ``r-1`` — one send / recv of the
-  K/V halo forward, one of ``dprev_k / dprev_v`` backward (added into rank ``r-1``'s dK / dV).
+  needs only the last ``window`` (or ``chunk``) keys / values of rank ``r-1`` — one batched send / recv of
+  the K/V halo (and its segment ids) forward, landing in front of the rank's own K / V in one buffer,
+  and one of the halo's dK / dV backward (added into rank ``r-1``'s dK / dV).
 * causal attention: a ring.  At step ``t`` rank ``r`` reads the K/V block of rank ``r-t`` (diagonal
   block causal, earlier blocks unmasked, later blocks skipped), merges the partial outputs by their
-  log-sum-exp, and prefetches the next block while computing.  The backward sends each block's dK / dV
-  home.  With contiguous slices rank ``r`` has ``r + 1`` blocks of work; the ``zigzag`` layout (rank ``r``
+  log-sum-exp, and prefetches the next block while computing.  In the backward each block's dK / dV
+  accumulator travels with it and arrives home after a full turn; both the next block and the
+  accumulator move while the kernels of a step run.  With contiguous slices rank ``r`` has ``r + 1`` blocks of work; the ``zigzag`` layout (rank ``r``
   holds chunks ``r`` and ``2R-1-r`` of ``2R``) gives every rank the same work at every step: an earlier
   rank's block is seen by all local rows through its first chunk only, a later rank's block is seen
   whole by the local second chunk only, both unmasked.
@@ -39,67 +41,78 @@ def _global_rank(group, rank_in_group: int) -> int:
     return dist.get_global_rank(group, rank_in_group) if group is not None else rank_in_group
 
 
-def _exchange(send: Optional[Tensor], send_to: Optional[int], recv: Optional[Tensor], recv_from: Optional[int],
-              group) -> None:
-    """One batched point-to-point step (either side may be absent at the ends of the chain)."""
+def _p2p(sends, send_to: Optional[int], recvs, recv_from: Optional[int], group):
+    """One batched point-to-point step: every tensor of ``sends`` goes to ``send_to``, every buffer of
+    ``recvs`` is filled from ``recv_from`` (either side may be absent at the ends of the chain).  Returns
+    the pending work handles; the caller waits when it needs the data, so whatever it launches in
+    between runs beside the transfer.  Peers issue their sends and receives in the same order."""
     ops = []
-    if send is not None and send_to is not None:
-        ops.append(dist.P2POp(dist.isend, send.contiguous(), _global_rank(group, send_to), group))
-    if recv is not None and recv_from is not None:
-        ops.append(dist.P2POp(dist.irecv, recv, _global_rank(group, recv_from), group))
-    if ops:
-        for work in dist.batch_isend_irecv(ops):
-            work.wait()
+    if send_to is not None:
+        ops += [dist.P2POp(dist.isend, t.contiguous(), _global_rank(group, send_to), group) for t in sends]
+    if recv_from is not None:
+        ops += [dist.P2POp(dist.irecv, t, _global_rank(group, recv_from), group) for t in recvs]
+    return dist.batch_isend_irecv(ops) if ops else []
 
 
-class _Halo(torch.autograd.Function):
-    """(k, v) of this rank -> (k, v, prev_k, prev_v): the inputs passed through, plus the last
-    ``halo`` tokens of the previous rank's K / V (zero-length on rank 0).
+def _wait(works) -> None:
+    for work in works:
+        work.wait()
 
-    Backward: the gradient of the received halo travels back to the previous rank and is added to the
-    tail of its dK / dV.  K and V pass through the node so that every rank's graph contains it and
-    takes part in that exchange, whether or not it used a halo itself."""
+
+class _HaloAssemble(torch.autograd.Function):
+    """(k, v) of this rank -> (k_all, v_all, ids_all): the last ``halo`` tokens of the previous rank's K / V
+    (and segment ids) in front of this rank's own, in one buffer each.  The attention op then sees a
+    query slice that is shorter than its keys and right-aligned to them, which is the reference's own
+    short-Q contract (tests/_reference.py:47-49): no previous-K/V arguments, no concatenation inside
+    the op.  One batched exchange carries K, V and ids; this rank's own K / V are copied into place while
+    it is in flight.
+
+    Backward: the gradient of the halo rows travels back to the previous rank and is added to the tail
+    of its dK / dV (the reference's ``dprev_k / dprev_v`` seam, docs/sliding_window_attention.md:78-79).
+    K and V pass through this node on every rank, so every rank takes part in that exchange whether
+    or not it received a halo itself."""
 
     @staticmethod
-    def forward(ctx, k: Tensor, v: Tensor, halo: int, group):
+    def forward(ctx, k: Tensor, v: Tensor, halo: int, ids: Optional[Tensor], group):
         rank, world = _world(group)
-        ctx.group, ctx.halo, ctx.rank, ctx.world = group, halo, rank, world
-        n_prev = halo if rank > 0 else 0
-        prev_k = k.new_empty((k.shape[0], n_prev, *k.shape[2:]))
-        prev_v = v.new_empty((v.shape[0], n_prev, *v.shape[2:]))
         nxt = rank + 1 if rank + 1 < world else None
         prv = rank - 1 if rank > 0 else None
-        _exchange(k[:, -halo:] if nxt is not None else None, nxt, prev_k if prv is not None else None, prv, group)
-        _exchange(v[:, -halo:] if nxt is not None else None, nxt, prev_v if prv is not None else None, prv, group)
-        return k.view_as(k), v.view_as(v), prev_k, prev_v
+        n_prev = halo if prv is not None else 0
+        ctx.group, ctx.halo, ctx.n_prev, ctx.nxt, ctx.prv = group, halo, n_prev, nxt, prv
+        tensors = [k, v] + ([ids] if ids is not None else [])
+        out = [t.new_empty((t.shape[0], n_prev + t.shape[1], *t.shape[2:])) for t in tensors]
+        # a slice along the token axis is one block of memory only for a batch of one: otherwise the
+        # halo lands in a buffer of its own first
+        direct = k.shape[0] == 1
+        landing = [o[:, :n_prev] if direct else o.new_empty((o.shape[0], n_prev, *o.shape[2:])) for o in out]
+        works = _p2p([t[:, -halo:] for t in tensors], nxt, landing, prv, group)
+        for o, t in zip(out, tensors):
+            o[:, n_prev:].copy_(t)
+        _wait(works)
+        if not direct and n_prev:
+            for o, l in zip(out, landing):
+                o[:, :n_prev].copy_(l)
+        ids_all = out[2] if ids is not None else None
+        if ids_all is not None:
+            ctx.mark_non_differentiable(ids_all)
+        return out[0], out[1], ids_all
 
     @staticmethod
-    def backward(ctx, dk: Optional[Tensor], dv: Optional[Tensor], dprev_k: Optional[Tensor], dprev_v: Optional[Tensor]):
-        rank, world, halo, group = ctx.rank, ctx.world, ctx.halo, ctx.group
-        nxt = rank + 1 if rank + 1 < world else None
-        prv = rank - 1 if rank > 0 else None
-
-        def step(grad_out, grad_halo):
-            recv = grad_out.new_empty((grad_out.shape[0], halo, *grad_out.shape[2:])) if nxt is not None else None
-            _exchange(grad_halo if prv is not None else None, prv, recv, nxt, group)
-            if nxt is None:
-                return grad_out
-            total = grad_out.clone()
-            total[:, -halo:] += recv
-            return total
-
-        return step(dk, dprev_k), step(dv, dprev_v), None, None
+    def backward(ctx, dk_all: Tensor, dv_all: Tensor, _ids):
+        halo, n_prev, nxt, prv, group = ctx.halo, ctx.n_prev, ctx.nxt, ctx.prv, ctx.group
+        grads = [dk_all, dv_all]
+        recv = [g.new_empty((g.shape[0], halo, *g.shape[2:])) for g in grads] if nxt is not None else []
+        works = _p2p([g[:, :n_prev] for g in grads], prv, recv, nxt, group)
+        own = [g[:, n_prev:] for g in grads]
+        _wait(works)
+        for g, r in zip(own, recv):
+            g[:, -halo:] += r            # the gradients are this function's alone: updated in place
+        return own[0], own[1], None, None, None
 
 
-def _halo_ids(ids: Optional[Tensor], halo: int, group) -> Optional[Tensor]:
-    """Segment ids of the halo tokens (no gradient): [previous rank's tail ‖ own ids]."""
-    if ids is None:
-        return None
-    rank, world = _world(group)
-    recv = ids.new_empty((ids.shape[0], halo)) if rank > 0 else None
-    _exchange(ids[:, -halo:] if rank + 1 < world else None, rank + 1 if rank + 1 < world else None,
-              recv, rank - 1 if rank > 0 else None, group)
-    return ids if rank == 0 else torch.cat((recv, ids), dim=1)
+def _sequence_parallel_local(op, q, k, v, span, scale, segment_idx, group, op_kwargs):
+    k_all, v_all, ids_all = _HaloAssemble.apply(k, v, span, segment_idx, group)
+    return op(q, k_all, v_all, span, scale, segment_idx=ids_all, **op_kwargs)
 
 
 def sequence_parallel_flash_swa(q: Tensor, k: Tensor, v: Tensor, window_size: int, scale: Optional[float] = None,
@@ -117,33 +130,23 @@ def sequence_parallel_flash_swa(q: Tensor, k: Tensor, v: Tensor, window_size: in
         return op(q, k, v, window_size, scale, segment_idx=segment_idx, **op_kwargs)
     if k.shape[1] < window_size:
         raise ValueError("every rank's slice must be at least window_size tokens long")
-    rank, _ = _world(group)
-    k, v, prev_k, prev_v = _Halo.apply(k, v, window_size, group)
-    ids = _halo_ids(segment_idx, window_size, group)
-    if rank == 0:
-        return op(q, k, v, window_size, scale, segment_idx=ids, **op_kwargs)
-    return op(q, k, v, window_size, scale, prev_k, prev_v, segment_idx=ids, **op_kwargs)
+    return _sequence_parallel_local(op, q, k, v, window_size, scale, segment_idx, group, op_kwargs)
 
 
 def sequence_parallel_flash_sca(q: Tensor, k: Tensor, v: Tensor, chunk_size: int, scale: Optional[float] = None,
                                 *, segment_idx: Optional[Tensor] = None, group=None,
                                 op: Optional[Callable] = None, **op_kwargs) -> Tensor:
     """Sliding-chunk attention over a sequence split across ranks.  Slice lengths must be multiples of
-    ``chunk_size`` so that global chunk boundaries survive the split; the halo is exactly one chunk
-    (the reference's contract for previous K/V, xattn/ops/sliding_chunk_attention.py:538-541).
-    Per-segment reset positions are not supported across ranks."""
+    ``chunk_size`` so that global chunk boundaries survive the split (the halo, exactly one chunk, then
+    shifts every local key position by a multiple of the chunk size).  Per-segment reset positions are
+    not supported across ranks."""
     if op is None:
         from .ops import flash_sca as op
     if k.shape[1] % chunk_size:
         raise ValueError("every rank's slice must be a multiple of chunk_size long")
     if op_kwargs.get("reset_chunk_pos_per_seq"):
         raise ValueError("per-segment reset positions cannot be split across ranks")
-    rank, _ = _world(group)
-    k, v, prev_k, prev_v = _Halo.apply(k, v, chunk_size, group)
-    ids = _halo_ids(segment_idx, chunk_size, group)
-    if rank == 0:
-        return op(q, k, v, chunk_size, scale, segment_idx=ids, **op_kwargs)
-    return op(q, k, v, chunk_size, scale, prev_k, prev_v, segment_idx=ids, **op_kwargs)
+    return _sequence_parallel_local(op, q, k, v, chunk_size, scale, segment_idx, group, op_kwargs)
 
 
 # ---- causal ring ----------------------------------------------------------------------------------
@@ -232,8 +235,7 @@ class _RingCausal(torch.autograd.Function):
             elif t <= rank:     # the block of rank (rank - t): on or below the diagonal
                 y_t, lse_t = kernels.forward(q, blk_k, blk_v, scale, causal=(t == 0))
                 acc = _merge(acc, y_t, lse_t)
-            for work in pending:
-                work.wait()
+            _wait(pending)
             if t + 1 < world:
                 blk_k, blk_v = nxt_k, nxt_v
         y32, lse = acc
@@ -251,42 +253,62 @@ class _RingCausal(torch.autograd.Function):
         send_to, recv_from = (rank + 1) % world, (rank - 1) % world
         dy = dy.contiguous()
         blk_k, blk_v = k.contiguous(), v.contiguous()
-        # gradients of the block currently held travel around the ring with it and arrive home after
-        # `world` steps
+        # The K/V block held at step t came from rank - t; its dK / dV accumulate as it travels and are
+        # home after `world` steps.  Two transfers per step, both beside the kernels: the NEXT block's K / V
+        # (they never change, so they are requested before this step's kernels start), and the gradient
+        # accumulator of the block just worked on, which the previous rank sent on after ITS step and which
+        # is only needed once this step's own contribution exists.
         wide = torch.float64 if q.dtype == torch.float64 else torch.float32
-        dk_acc = torch.zeros(k.shape, dtype=wide, device=k.device)
-        dv_acc = torch.zeros(v.shape, dtype=wide, device=v.device)
         dq = torch.zeros(q.shape, dtype=wide, device=q.device)
+        nxt_rank, prv_rank = _global_rank(group, send_to), _global_rank(group, recv_from)
+        acc_in = None          # (works, dk, dv): the accumulator of the current block, arriving
+        sent = []              # keep buffers of sends in flight alive until their work is done
         for t in range(world):
+            nxt_k = nxt_v = None
+            kv_works = []
+            if t + 1 < world:
+                nxt_k, nxt_v = torch.empty_like(blk_k), torch.empty_like(blk_v)
+                kv_works = dist.batch_isend_irecv([
+                    dist.P2POp(dist.isend, blk_k, nxt_rank, group), dist.P2POp(dist.irecv, nxt_k, prv_rank, group),
+                    dist.P2POp(dist.isend, blk_v, nxt_rank, group), dist.P2POp(dist.irecv, nxt_v, prv_rank, group)])
+            dk_t = dv_t = None
+            rows = slice(None)
             if zigzag and t > 0:
                 if t <= rank:
                     dq_t, dk_t, dv_t = kernels.backward(dy, q, blk_k[:, :half], blk_v[:, :half], y, lse, scale,
                                                         causal=False)
                     dq += dq_t.to(wide)
-                    dk_acc[:, :half] += dk_t.to(wide)
-                    dv_acc[:, :half] += dv_t.to(wide)
+                    rows = slice(0, half)
                 else:
                     dq_t, dk_t, dv_t = kernels.backward(dy[:, half:], q[:, half:], blk_k, blk_v, y[:, half:],
                                                         lse[:, :, half:], scale, causal=False)
                     dq[:, half:] += dq_t.to(wide)
-                    dk_acc += dk_t.to(wide)
-                    dv_acc += dv_t.to(wide)
             elif t <= rank:
                 dq_t, dk_t, dv_t = kernels.backward(dy, q, blk_k, blk_v, y, lse, scale, causal=(t == 0))
                 dq += dq_t.to(wide)
-                dk_acc += dk_t.to(wide)
-                dv_acc += dv_t.to(wide)
-            # pass the block and its gradient accumulators on (the last step brings them home)
-            bufs = [blk_k, blk_v, dk_acc, dv_acc]
-            recv = [torch.empty_like(b) for b in bufs]
-            ops = []
-            for s_, r_ in zip(bufs, recv):
-                ops.append(dist.P2POp(dist.isend, s_, _global_rank(group, send_to), group))
-                ops.append(dist.P2POp(dist.irecv, r_, _global_rank(group, recv_from), group))
-            for work in dist.batch_isend_irecv(ops):
-                work.wait()
-            blk_k, blk_v, dk_acc, dv_acc = recv
-        return dq.to(q.dtype), dk_acc.to(k.dtype), dv_acc.to(v.dtype), None, None, None, None
+            # this block's accumulator: zero on its home rank (t == 0), else what the previous rank sent on
+            if acc_in is None:
+                dk_acc = torch.zeros(k.shape, dtype=wide, device=k.device)
+                dv_acc = torch.zeros(v.shape, dtype=wide, device=v.device)
+            else:
+                _wait(acc_in[0])
+                dk_acc, dv_acc = acc_in[1], acc_in[2]
+            if dk_t is not None:
+                dk_acc[:, rows] += dk_t.to(wide)
+                dv_acc[:, rows] += dv_t.to(wide)
+            # pass the accumulator on (the last step brings it home) and ask for the next one
+            recv_dk, recv_dv = torch.empty_like(dk_acc), torch.empty_like(dv_acc)
+            works = dist.batch_isend_irecv([
+                dist.P2POp(dist.isend, dk_acc, nxt_rank, group), dist.P2POp(dist.irecv, recv_dk, prv_rank, group),
+                dist.P2POp(dist.isend, dv_acc, nxt_rank, group), dist.P2POp(dist.irecv, recv_dv, prv_rank, group)])
+            sent.append((dk_acc, dv_acc))
+            acc_in = (works, recv_dk, recv_dv)
+            _wait(kv_works)
+            if t + 1 < world:
+                blk_k, blk_v = nxt_k, nxt_v
+        _wait(acc_in[0])
+        dk_home, dv_home = acc_in[1], acc_in[2]
+        return dq.to(q.dtype), dk_home.to(k.dtype), dv_home.to(v.dtype), None, None, None, None
 
 
 def ring_causal_flash_attn(q: Tensor, k: Tensor, v: Tensor, scale: Optional[float] = None, *, group=None,
