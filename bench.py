@@ -79,6 +79,8 @@ WORKLOADS = {
                          text="profiling case: dense causal B=1 S=8192 Hq=32 Hkv=8 D=128 (0.24 GB of tensors, above L2)"),
     "causal_c2_row": dict(B=1, S=8192, Hq=32, Hkv=8, D=128, segments=True,
                           text="profiling case: one batch row of configs[1] (causal, packed segments ~U[512,4096]; 0.17 GB of tensors, above L2)"),
+    "copy_probe": dict(B=4, S=8192, Hq=32, Hkv=8, D=128, segments=True, copy_probe=True,
+                       text="host <-> device copies of the headline step's end-to-end leg, no kernels"),
     "causal_c2_dense": dict(B=4, S=8192, Hq=32, Hkv=8, D=128, segments=False,
                             text="configs[1] shape with one segment per sequence (dense causal)"),
     # sequence-sharded across the ranks (strong scaling): each rank holds S / N tokens and receives a
@@ -129,6 +131,43 @@ def make_host_inputs(w, seed):
                 pos += length
                 seg += 1
     return q, k, v, dy, ids
+
+
+_ORIGINAL_AFFINITY = None
+
+
+def bind_to_gpu_numa_node(local_rank):
+    """Run this process (and so first-touch its pinned host buffers) on the CPUs of the NUMA node the GPU
+    hangs off: with one rank per GPU and every rank copying 1.3 GB per step, buffers that all sit on one
+    socket make the other socket's GPUs cross the inter-socket link both ways.  Best effort: returns what
+    was found and done; containers that hide the topology simply stay unbound."""
+    global _ORIGINAL_AFFINITY
+    _ORIGINAL_AFFINITY = os.sched_getaffinity(0)
+    info = {"numa_node": None, "cpus_before": len(_ORIGINAL_AFFINITY), "bound": False}
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(local_rank)).busId
+        bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()
+        if len(bus.split(":")[0]) == 8:          # NVML pads the PCI domain to eight digits, sysfs uses four
+            bus = bus[4:]
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        info["numa_node"] = node
+        if node < 0:
+            return info
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus |= set(range(int(lo), int(hi or lo) + 1))
+        usable = cpus & os.sched_getaffinity(0)
+        if usable:
+            os.sched_setaffinity(0, usable)
+            info.update(bound=True, cpus_after=len(usable))
+    except Exception as exc:                       # no NVML, no sysfs, no permission: stay as we are
+        info["error"] = type(exc).__name__
+    return info
 
 
 class ClockSampler(threading.Thread):
@@ -260,6 +299,9 @@ def run_ours(args, w):
     import xattn_b200 as xattn
     from xattn_b200 import _native
 
+    # Every timed step builds its mask plan, as a training step with fresh masks would: the library's
+    # plan cache (which would find the same segment-id tensor again every step) is off for the bench.
+    os.environ["XATTN_B200_PLAN_CACHE"] = "0"
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -268,6 +310,9 @@ def run_ours(args, w):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    host_binding = None if args.no_numa_bind else bind_to_gpu_numa_node(local)
+    if w.get("copy_probe"):
+        return run_copy_probe(args, w, world, rank, dev, host_binding)
     if "window" in w or w.get("ring"):
         return run_swa_sharded(args, w, world, rank, dev)
     if w.get("decode"):
@@ -453,6 +498,7 @@ def run_ours(args, w):
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": w["text"] if level == 0 else w["text"].replace("level 0", "level 1"),
                        "high_precision_level": level, "l2": "inputs (0.67 GB per step) exceed the 126 MB L2",
+                       "mask_plan": "built in every step (plan cache off)",
                        "visible_pairs_per_step": pairs, "flops_per_step": flops_step,
                        "parallelism": f"batch x heads sharded over {world} GPU(s): embarrassingly parallel, no "
                                       "communication (every rank runs its own batch); the sequence-sharded "
@@ -466,6 +512,7 @@ def run_ours(args, w):
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
             "gpu_launches": launches,
             "clocks": clocks,
+            "host": host_binding,
             "roofline": {"bound": "tensor", "kernel": dominant,
                          **tensor_roofline(achieved, peaks, peak_src, ms_total * 1e-3),
                          "traffic": row_traffic * w["B"] if row_traffic else None,
@@ -478,8 +525,69 @@ def run_ours(args, w):
         if sharded is not None:
             line["sharded"] = sharded
         if world == 1 and not args.no_cpu_baseline:
+            if _ORIGINAL_AFFINITY:
+                os.sched_setaffinity(0, _ORIGINAL_AFFINITY)      # the CPU baseline gets every core back
             line["cpu_baseline"] = cpu_baseline_config0(os.cpu_count() or 1)
         print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_copy_probe(args, w, world, rank, dev, host_binding):
+    """The host-buffer leg of the headline step with the kernels taken out: every rank copies its
+    q, k, v, dy (0.67 GB) from pinned memory to the GPU and as many bytes back, both directions at
+    once, batch row by batch row as the end-to-end step does.  Shows what the host side of N
+    simultaneous ranks delivers per GPU."""
+    import torch.distributed as dist
+    host = make_host_inputs(WORKLOADS["causal_c2"], seed=1 + rank)
+    pinned = [t.pin_memory() for t in host[:4]]
+    back = [torch.empty_like(t).pin_memory() for t in pinned]
+    dev_in = [torch.empty_like(t, device=dev) for t in pinned]
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    nbytes = sum(t.numel() * t.element_size() for t in pinned)
+
+    def step(h2d=True, d2h=True):
+        for b in range(pinned[0].shape[0]):
+            if h2d:
+                with torch.cuda.stream(s_in):
+                    for dst, src in zip(dev_in, pinned):
+                        dst[b:b + 1].copy_(src[b:b + 1], non_blocking=True)
+            if d2h:
+                with torch.cuda.stream(s_out):
+                    for dst, src in zip(back, dev_in):
+                        dst[b:b + 1].copy_(src[b:b + 1], non_blocking=True)
+
+    def timed(**kw):
+        for _ in range(3):
+            step(**kw)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step(**kw)
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / args.steps
+
+    res = {}
+    for name, kw in (("h2d_alone", dict(d2h=False)), ("d2h_alone", dict(h2d=False)), ("both", {})):
+        dt = timed(**kw)
+        rates = torch.tensor([nbytes / dt * 1e-9], dtype=torch.float64, device=dev)
+        if world > 1:
+            gathered = [torch.zeros_like(rates) for _ in range(world)]
+            dist.all_gather(gathered, rates)
+            rates = torch.cat(gathered)
+        res[name] = {"gb_per_s_per_direction_min": float(rates.min()), "max": float(rates.max()),
+                     "sum_over_ranks": float(rates.sum()), "ms": dt * 1e3}
+    nodes = [host_binding]
+    if world > 1:
+        nodes = [None] * world
+        dist.all_gather_object(nodes, host_binding)
+    if rank == 0:
+        print(json.dumps({"metric": "host <-> device copy rate of the end-to-end leg, per GPU", "unit": "GB/s",
+                          "n_gpus": world, "steps": args.steps, "bytes_per_direction_per_step": nbytes,
+                          "value": res["both"]["gb_per_s_per_direction_min"], "higher_is_better": True,
+                          "rates": res, "host": nodes, "cpu_count": os.cpu_count()}))
     if world > 1:
         dist.destroy_process_group()
 
@@ -521,6 +629,27 @@ def run_decode(args, w, world, rank, dev):
     records = _native.profile_read()
     clocks = sampler.stop()
     _native.check_status()
+    # The repeated-mask inference path of the reference's sliding-chunk op keeps its forward plan between
+    # calls.  The same question here: one decode step with a BOS mask over the key cache, plan cache off
+    # and on (the mask tensor is the same every step, as in a serving loop between cache updates).
+    bos = torch.zeros(B, S, dtype=torch.bool, device=dev)
+    bos[:, ::4096] = True
+    cache_ms = {}
+    for state in ("0", "1"):
+        os.environ["XATTN_B200_PLAN_CACHE"] = state
+        with torch.inference_mode():
+            for _ in range(5):
+                xattn.flash_sca_fwd(q, k, v, 2048, bos_mask=bos)
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            c0.record()
+            for _ in range(50):
+                xattn.flash_sca_fwd(q, k, v, 2048, bos_mask=bos)
+            c1.record()
+            torch.cuda.synchronize()
+        cache_ms["off" if state == "0" else "on"] = c0.elapsed_time(c1) / 50
+    os.environ["XATTN_B200_PLAN_CACHE"] = "0"
+    _native.check_status()
     times = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -546,6 +675,9 @@ def run_decode(args, w, world, rank, dev):
                                            "kernel on this workload",
                          "peak_source": f"{peak_src} hbm_gbs (copy bandwidth)"},
             "kernel_ms": kernel_ms,
+            "plan_cache": {"workload": "sliding-chunk decode step (chunk 2048) with a BOS mask over the 32768 cached keys, "
+                                       "same mask tensor every step, launched from Python under inference mode",
+                           "ms_per_step_cache_off": cache_ms["off"], "ms_per_step_cache_on": cache_ms["on"]},
         }))
     if world > 1:
         dist.destroy_process_group()
@@ -826,11 +958,13 @@ def main():
                     help="high_precision_level (default 0; the causal, sca_c4 and softdelta workloads take 1 too)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-numa-bind", action="store_true",
+                    help="do not move the process to the CPUs of the GPU's NUMA node before pinning host buffers")
     ap.add_argument("--no-sharded", action="store_true",
                     help="with more than one GPU: skip the sequence-sharded workloads after the headline measurement")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
-    if args.impl == "reference" and (w.get("decode") or w.get("other") or w["S"] > 8192):
+    if args.impl == "reference" and (w.get("decode") or w.get("other") or w.get("copy_probe") or w["S"] > 8192):
         print(json.dumps({"impl": "reference", "unavailable": "the CPU arm runs the causal S=8192 workloads: one "
                           "(batch row, head) slice of a 32768-token sequence needs 4.3 GB per score matrix in fp32"}))
     elif args.impl == "reference":

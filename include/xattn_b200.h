@@ -216,10 +216,11 @@ typedef struct {
  * Delta_i = sum_j P_ij (dP_ij - dP_ia) (csrc/attention/precision/row_statistics_sm90.cuh:39-188), and both
  * mainloops use dS_ij = P_ij ((dP_ij - dP_ia) - Delta_i) with P = root * root,
  * root = exp2((s_ij c - lse2) / 2), so that a probability below the FP32 normal range still meets a
- * huge dP correctly, and with the centred value exactly zero on the anchor.  The workspace needs
- * xattn_b200_bwd_workspace_bytes_hp() bytes.  Not reproduced: the split hi / lo operands and the
- * FP64 row sums with zero-sum and probability repair (csrc/attention/precision/zero_sum_repair.cu,
- * probability_repair.cu); the operands of the dV / dK / dQ products are rounded once. */
+ * huge dP correctly, and with the centred value exactly zero on the anchor.  P and dS enter the
+ * dV / dK / dQ products as two 16-bit parts, hi + lo (hopper/mainloop_bwd_sm90_tma_gmma_ws.hpp:1811-1868).
+ * The workspace needs xattn_b200_bwd_workspace_bytes_hp() bytes.  Not reproduced: the FP64 row sums
+ * of the operands as fed, with zero-sum and probability repair (csrc/attention/precision/zero_sum_repair.cu,
+ * probability_repair.cu): rows sum to zero up to the rounding of their (16-bit-accurate) terms. */
 size_t xattn_b200_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);
 size_t xattn_b200_bwd_workspace_bytes_hp(int64_t batch, int64_t q_heads, int64_t q_len);
 int xattn_b200_bwd(const XattnBwdArgs* args, xattn_stream_t stream);

@@ -42,19 +42,28 @@ def test_repeated_bos_mask_reuses_ids_and_plan(cuda_device):
     xattn.check_status()
 
 
-def test_dense_plans_are_shared_and_training_masks_are_not_cached(cuda_device):
+def test_plans_are_shared_in_training_too(cuda_device):
     q, k, v = _inputs(cuda_device)
     xattn.clear_plan_cache()
     h0, m0 = _core.plan_cache_stats()
     leaves = [t.clone().requires_grad_() for t in (q, k, v)]
     xattn.flash_swa(*leaves, 100)
-    xattn.flash_swa(*leaves, 100)                  # dense: cached with autograd on as well
+    y = xattn.flash_swa(*leaves, 100)
     h1, m1 = _core.plan_cache_stats()
     assert (h1 - h0, m1 - m0) == (1, 1)
     ids = (torch.arange(700, device=cuda_device) // 300).expand(2, -1).contiguous()
     xattn.flash_swa(*leaves, 100, segment_idx=ids)
-    xattn.flash_swa(*leaves, 100, segment_idx=ids)
-    assert _core.plan_cache_stats() == (h1, m1)    # metadata plans are cached only with autograd off
+    y_ids = xattn.flash_swa(*leaves, 100, segment_idx=ids)
+    h2, m2 = _core.plan_cache_stats()
+    assert (h2 - h1, m2 - m1) == (1, 1)
+    ids[:, 350:] += 1                               # a write bumps the version: the old plan is not reused
+    y_new = xattn.flash_swa(*leaves, 100, segment_idx=ids)
+    assert _core.plan_cache_stats() == (h2, m2 + 1)
+    assert not torch.equal(y_ids, y_new) and not torch.equal(y, y_ids)
+    # the backward uses the plan its forward saved, whatever the cache holds by then
+    xattn.clear_plan_cache()
+    grads = torch.autograd.grad(y_new, leaves, torch.ones_like(y_new))
+    assert all(torch.isfinite(g).all() for g in grads)
     xattn.check_status()
 
 

@@ -33,11 +33,23 @@ def test_static_scratch_backward_matches_regular_entry(cuda_device):
         want = _native.attention_bwd(dy, q, k, v, y, lse, plan, scale)
         # outputs exist before the call; poison them so that an entry point that did nothing is caught
         got = [torch.full_like(t, float("nan")) for t in want]
+        _native.prepare_device(dev)
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated(dev)
         _native.attention_bwd_static_scratch(dy, q, k, v, y, lse, plan, scale, *got)
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated(dev) == before, "the entry point must not allocate through torch"
+        # a raw cudaMalloc would not show in torch's counter: the driver's free-memory figure must not
+        # move either across a further call (the first one may have loaded the module)
+        free_before = torch.cuda.mem_get_info(dev)[0]
+        again = [torch.empty_like(t) for t in want]
+        torch.cuda.synchronize()
+        free_mid = torch.cuda.mem_get_info(dev)[0]        # after torch took what `again` needs
+        _native.attention_bwd_static_scratch(dy, q, k, v, y, lse, plan, scale, *again)
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info(dev)[0] == free_mid <= free_before, "device memory was taken during the call"
+        for a, b in zip(again, want):
+            assert torch.equal(a, b)
         _native.check_status()
         for name, a, b in zip(("dq", "dk", "dv"), got, want):
             assert torch.isfinite(a).all(), name

@@ -44,6 +44,13 @@ def _state(device: torch.device) -> _DeviceState:
     return st
 
 
+def prepare_device(device: Optional[torch.device] = None) -> None:
+    """Create this module's per-device state now: the device status word (4 bytes) and its pinned host
+    mirror.  Every entry point does this on first use; callers of ``attention_bwd_static_scratch``, which
+    may not allocate later on, call it once at start-up instead."""
+    _state(torch.device("cuda", torch.cuda.current_device()) if device is None else device)
+
+
 def _stream_ptr() -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
@@ -449,7 +456,10 @@ def attention_bwd_static_scratch(dy: Tensor, q: Tensor, k: Tensor, v: Tensor, y:
     multiple of 128) is limited to ``STATIC_SCRATCH_MAX_ROWS``; calls on one device share that array and must not overlap on the
     GPU.  Every tensor must already be laid out the way the kernels read it (unit last stride,
     16-byte aligned base and strides): nothing is copied or made contiguous here.  The first call
-    on a device resolves the array's address and belongs outside any stream capture.
+    on a device resolves the array's address (and, where CUDA loads modules lazily, loads the module
+    and reserves the array): make it at start-up, outside any stream capture.  The device status word
+    must exist already: ``prepare_device()`` at start-up, or any earlier call of this module on the
+    device, creates it; this function refuses to allocate it.
     """
     lib = _lib.load()
     require_cuda(q, "xattn_b200 backward (static scratch)")
@@ -476,8 +486,13 @@ def attention_bwd_static_scratch(dy: Tensor, q: Tensor, k: Tensor, v: Tensor, y:
     args.plan = plan.data_ptr()
     args.dq, args.dk, args.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
     args.workspace = None
-    st = _state(q.device)
-    args.status = st.status.data_ptr()
+    index = q.device.index if q.device.index is not None else torch.cuda.current_device()
+    if index not in _states:
+        raise RuntimeError("the device status word does not exist yet and this entry point may not allocate it: "
+                           "call xattn_b200._native.prepare_device() once at start-up")
     with torch.cuda.device(q.device):
+        st = _pre_launch(q.device)
+        args.status = st.status.data_ptr()
         _lib.check(lib.xattn_b200_bwd_static_scratch(C.byref(args), _stream_ptr()),
                    "xattn_b200_bwd_static_scratch")
+        _post_launch(st)

@@ -471,8 +471,9 @@ __global__ void __launch_bounds__(64) wait_timeout_probe_kernel(int* status, uns
   }
   __syncthreads();
   WaitCtx ctx{&abort_flag, status, budget_ns};
-  if (threadIdx.x == 0) mbar_wait(ctx, &bar, 0, kProbeSite);            // runs out: sets the flag and the status
-  else if (threadIdx.x == 32) mbar_wait(ctx, &bar, 0, kProbeSite + 1);   // sees the flag or runs out itself
+  WaitCtx patient{&abort_flag, status, 8 * budget_ns};
+  if (threadIdx.x == 0) mbar_wait(ctx, &bar, 0, kProbeSite);                // runs out: sets the flag and the status
+  else if (threadIdx.x == 32) mbar_wait(patient, &bar, 0, kProbeSite + 1);   // leaves when it sees the flag
   __syncthreads();
 }
 

@@ -278,7 +278,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_dq, const BwdParams p) {
   using Smem = DqSmem<HD, BN>;
   constexpr bool kHigh = MODE != kDqPlain, kStats = MODE == kDqStats;
-  constexpr bool kDsOverDp = HD > 128 && !kStats;   // no TMEM columns left for dS
+  // kDqHigh feeds dS to the dQ product as two 16-bit parts, hi + lo (the rounding residue of hi), so the
+  // operand carries 16 significant bits instead of 8 (bf16) / 11 (fp16): the split of the reference's
+  // high-precision mainloop (hopper/mainloop_bwd_sm90_tma_gmma_ws.hpp:1811-1868).  Both parts lie over
+  // the dP columns they came from (hi in the first half of each 32-column chunk, lo in the second).
+  constexpr bool kSplit = MODE == kDqHigh;
+  constexpr bool kDsOverDp = (HD > 128 || kSplit) && !kStats;   // dS is written over dP
   constexpr int kKStages = Smem::kKStages;
   constexpr int kDoBox = kBlockM * 64 * 2;     // 64-column box of the 128-row dO tile
   constexpr int kKvBox = BN * 64 * 2;          // 64-column box of a BN-row K / V tile
@@ -456,6 +461,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
         if (!ok) break;
         tc_fence_after();
         uint32_t pk[CH / 2];
+        uint32_t pk_lo[kSplit ? CH / 2 : 1];
         const int ac = anchor - col0;         // the anchor's column in this thread's share, if any
 #pragma unroll
         for (int c0 = 0; c0 < CH; c0 += 32) {
@@ -475,7 +481,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
                 else stat_a = fma2(pr, mul2(pr, cent), stat_a);
               } else {
                 const float2 ds = mul2(pr, mul2(pr, add2(cent, nd)));
-                pk[(c0 + c) >> 1] = Pack2<T>::pack(ds.x, ds.y);
+                const uint32_t hi = Pack2<T>::pack(ds.x, ds.y);
+                pk[(c0 + c) >> 1] = hi;
+                if (kSplit) {
+                  const float2 back = Pack2<T>::unpack(hi);
+                  pk_lo[(c0 + c) >> 1] = Pack2<T>::pack(ds.x - back.x, ds.y - back.y);
+                }
               }
             } else {
               const float2 ds = mul2(pr, add2(make_float2(dpv[c], dpv[c + 1]), nd));
@@ -483,6 +494,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
             }
           }
           if (kDsOverDp) tmem_st_x16(t_dp, pk + (c0 >> 1));
+          if (kSplit) tmem_st_x16(t_dp + 16, pk_lo + (c0 >> 1));
         }
         if (kStats) {
           tc_fence_before();
@@ -606,6 +618,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
         const uint32_t a_col = kDsOverDp ? cDP + (js >> 1) * 32 + (js & 1) * 8 : cDS + js * 8;
         umma_ts(tmem + cDQ, tmem + a_col, make_smem_desc(ka + js * 2048, kKvBox, 1024), idesc_dq,
                 (i > 0 || js > 0) ? 1u : 0u);
+        if (kSplit) umma_ts(tmem + cDQ, tmem + a_col + 16, make_smem_desc(ka + js * 2048, kKvBox, 1024), idesc_dq, 1u);
       }
       umma_commit(&s.dq_done);
       umma_commit(&s.k_empty[ks]);
@@ -946,13 +959,24 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // the 16-bit results go over the first half of the chunk's own columns
         if (kWantDv) {
           uint32_t pp[kChunk / 2];
+          uint32_t pp_lo[HP ? kChunk / 2 : 1];
 #pragma unroll
           for (int c = 0; c < kChunk; c += 2) {
             float2 pr = make_float2(pv[j * kChunk + c], pv[j * kChunk + c + 1]);
             if (HP) pr = mul2(pr, pr);
             pp[c >> 1] = Pack2<T>::pack(pr.x, pr.y);
+            if (HP) {
+              // high precision: P goes to the dV product as hi + lo, the lo part in the second half
+              // of the chunk's own columns (the dQ kernel's kSplit says why)
+              const float2 back = Pack2<T>::unpack(pp[c >> 1]);
+              pp_lo[c >> 1] = Pack2<T>::pack(pr.x - back.x, pr.y - back.y);
+            }
           }
           if (kChunk == 32) tmem_st_x16(t_s + j * kChunk, pp); else tmem_st_x8(t_s + j * kChunk, pp);
+          if (HP) {
+            if (kChunk == 32) tmem_st_x16(t_s + j * kChunk + kChunk / 2, pp_lo);
+            else tmem_st_x8(t_s + j * kChunk + kChunk / 2, pp_lo);
+          }
           tc_wait_st();
         }
         // chunk by chunk, so that dV starts on the first while the second is still being computed
@@ -981,6 +1005,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
           }
           uint32_t pd[kChunk / 2];
+          uint32_t pd_lo[HP ? kChunk / 2 : 1];
 #pragma unroll
           for (int c = 0; c < kChunk; c += 2) {
             const int g2 = j * kChunk + c;
@@ -988,8 +1013,16 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             float2 d = mul2(pr, make_float2(dpv[c], dpv[c + 1]));
             if (HP) d = mul2(pr, d);
             pd[c >> 1] = Pack2<T>::pack(d.x, d.y);
+            if (HP) {
+              const float2 back = Pack2<T>::unpack(pd[c >> 1]);
+              pd_lo[c >> 1] = Pack2<T>::pack(d.x - back.x, d.y - back.y);
+            }
           }
           if (kChunk == 32) tmem_st_x16(t_dp + j * kChunk, pd); else tmem_st_x8(t_dp + j * kChunk, pd);
+          if (HP) {
+            if (kChunk == 32) tmem_st_x16(t_dp + j * kChunk + kChunk / 2, pd_lo);
+            else tmem_st_x8(t_dp + j * kChunk + kChunk / 2, pd_lo);
+          }
         }
         tc_wait_st();
         tc_fence_before();
@@ -1134,6 +1167,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               const int js = chunk * kStepsPerChunk + i;       // k-step: 16 query rows
               const uint32_t a_col = tmem + cS + buf * SM + chunk * kChunk + i * 8;
               umma_ts(tmem + cDV, a_col, make_smem_desc(da + js * 2048, kQBox, 1024), idesc_dv, fresh ? 0u : 1u);
+              if (HP) umma_ts(tmem + cDV, a_col + kChunk / 2, make_smem_desc(da + js * 2048, kQBox, 1024), idesc_dv, 1u);
               fresh = false;
             }
           }
@@ -1149,6 +1183,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int js = 0; js < SM / 16; ++js) {
           const uint32_t a_col = tmem + cDP + buf * SM + (js / kStepsPerChunk) * kChunk + (js % kStepsPerChunk) * 8;
           umma_ts(tmem + cDK, a_col, make_smem_desc(qa + js * 2048, kQBox, 1024), idesc_dk, (cnt > 0 || js > 0) ? 1u : 0u);
+          if (HP) umma_ts(tmem + cDK, a_col + kChunk / 2, make_smem_desc(qa + js * 2048, kQBox, 1024), idesc_dk, 1u);
         }
         umma_commit(&s.dp_free[buf]);
       }

@@ -52,11 +52,12 @@ class _PlanCache(threading.local):
     * A dense plan (no segment metadata) depends on nothing but the shapes and the visibility rule: it
       is cached for every call (per stream, like every entry: a plan is ready in the order of the stream
       that built it).
-    * A plan built from segment ids or a BOS mask is cached only when autograd is off, keyed by the
-      identity of the metadata tensor (storage address, offset, shape, strides, version counter) and
-      the current stream; the entry holds the tensor, so its memory cannot be handed to another tensor
-      meanwhile.  Tensors created under inference mode have no version counter: after writing into
-      such a mask in place, call ``clear_plan_cache()``.
+    * A plan built from segment ids or a BOS mask is keyed by the identity of the metadata tensor
+      (storage address, offset, shape, strides, version counter) and the current stream; the entry
+      holds the tensor, so its memory cannot be handed to another tensor meanwhile, and a write into
+      the mask changes its version.  Tensors created under inference mode have no version counter:
+      after writing into such a mask in place, call ``clear_plan_cache()``.  A training loop whose
+      masks change every step only cycles the cache's sixteen entries.
     * Nothing is stored while a CUDA graph is being captured (memory of the capture's private pool
       must not outlive it); lookups still work.
     ``XATTN_B200_PLAN_CACHE=0`` disables it."""
@@ -114,14 +115,9 @@ def _identity(t: Optional[Tensor]):
     return (t.data_ptr(), t.storage_offset(), tuple(t.shape), tuple(t.stride()), t.dtype, version)
 
 
-def _metadata_cacheable() -> bool:
-    return plan_cache_enabled() and not torch.is_grad_enabled()
-
-
 def make_plan(q: Tensor, k_length: int, support: Support,
               q_segment_idx: Optional[Tensor], k_segment_idx: Optional[Tensor]) -> Tensor:
-    dense = q_segment_idx is None
-    use_cache = plan_cache_enabled() and q.is_cuda and (dense or not torch.is_grad_enabled())
+    use_cache = plan_cache_enabled() and q.is_cuda
     key = None
     if use_cache:
         key = ("plan", q.device, q.shape[0], q.shape[1], k_length, support, _identity(q_segment_idx),
@@ -237,10 +233,10 @@ def prepare(
 
 
 def resolve_segments_cached(q, k_length, segment_idx, q_segment_idx, k_segment_idx, bos_mask, *, api_name):
-    """``_validation.resolve_segments``, with the ids of a BOS mask seen before (autograd off) taken from
-    the plan cache: the same id tensors come back, so the plan built from them is found again too."""
+    """``_validation.resolve_segments``, with the ids of a BOS mask seen before taken from the plan cache:
+    the same id tensors come back, so the plan built from them is found again too."""
     only_bos = bos_mask is not None and segment_idx is None and q_segment_idx is None and k_segment_idx is None
-    if not (only_bos and isinstance(bos_mask, Tensor) and bos_mask.is_cuda and _metadata_cacheable()):
+    if not (only_bos and isinstance(bos_mask, Tensor) and bos_mask.is_cuda and plan_cache_enabled()):
         return V.resolve_segments(q, k_length, segment_idx, q_segment_idx, k_segment_idx, bos_mask, api_name=api_name)
     key = ("bos", q.device, q.shape[0], q.shape[1], k_length, _identity(bos_mask),
            torch.cuda.current_stream(q.device).cuda_stream)
