@@ -30,11 +30,7 @@
 #ifndef XB_FWD_PARTS
 #define XB_FWD_PARTS 2
 #endif
-// 1: the softmax warpgroups take the row maximum of the tile BEFORE the current one as reference
-// (see the loop), so that the exchange between the column parts is off the critical path
-#ifndef XB_FWD_STALE_MAX
-#define XB_FWD_STALE_MAX 0
-#endif
+
 
 namespace xb {
 
@@ -274,23 +270,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       // ahead could overwrite a maximum another part has not read yet.
       s.xmax[j & 3][hf][r] = mx;
       mbar_arrive_warp(&s.max_x[j & 3]);
-      // Stale reference (16-bit formats with FP32 range only, low precision only): the parts agree on
-      // the maximum over the tiles BEFORE this one, which every part posted a whole tile ago, so
-      // nobody waits here.  P of this tile may then exceed 1 by whatever the maximum grows within
-      // the tile, which BF16 and the FP32 sums absorb; FP16's range would not.  The first tile, and
-      // a warp holding a row that has seen no key yet (no reference to be stale about), wait for the
-      // current tile's maxima as before; the partner warp holds the same rows and decides the same.
-      constexpr bool kStale = XB_FWD_STALE_MAX && !HP && Pack2<T>::kFormat == 1 && kParts == 2;
-      const bool fresh = !kStale || j == 0 || __any_sync(0xffffffffu, m == -INFINITY);
-      const int slot = fresh ? j : j - 1;
-      ok = mbar_wait(ctx, &s.max_x[slot & 3], (slot >> 2) & 1, 11);
+      ok = mbar_wait(ctx, &s.max_x[j & 3], (j >> 2) & 1, 11);
       if (!ok) break;
-      if (fresh) {
 #pragma unroll
-        for (int o = 1; o < kParts; ++o) mx = fmaxf(mx, s.xmax[j & 3][(hf + o) % kParts][r]);
-      } else {
-        mx = fmaxf(s.xmax[slot & 3][0][r], s.xmax[slot & 3][1][r]);
-      }
+      for (int o = 1; o < kParts; ++o) mx = fmaxf(mx, s.xmax[j & 3][(hf + o) % kParts][r]);
       float m_new = fmaxf(m, mx);
       if (!HP) {
         // keep the old reference while the maximum grew by less than 2^8: the accumulator is then
