@@ -465,7 +465,8 @@ def run_ours(args, w):
             if rank == 0:
                 sharded[name] = {key: res[key] for key in (
                     "metric", "value", "unit", "ms_per_step", "scaling", "per_gpu_tflops", "single_gpu_ms",
-                    "efficiency_vs_1gpu", "kernel_ms_per_step", "non_kernel_ms_per_step", "kernels")}
+                    "efficiency_vs_1gpu", "kernel_ms_per_step", "kernel_ms_per_step_slowest_rank",
+                    "non_kernel_ms_per_step", "work_share_of_slowest_rank", "kernels")}
                 sharded[name]["workload"] = res["config"]["workload"]
 
     if rank == 0:
@@ -888,9 +889,10 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
         _native.check_status()
         del qf, kf, vf, dyf
     barrier()
-    times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+    own_kernel_ms = sum(t for _, t in records) / steps
+    times = torch.tensor([ms, e2e_ms, own_kernel_ms], dtype=torch.float64, device=dev)
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = float(times[0]), float(times[1])
+    ms, e2e_ms, slowest_kernel_ms = float(times[0]), float(times[1]), float(times[2])
     if rank != 0:
         return None
     peaks, peak_src = measured_peaks()
@@ -923,8 +925,14 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
         # strong scaling: time of the unsharded sequence on one GPU over N times the sharded time
         "single_gpu_ms": single_ms,
         "efficiency_vs_1gpu": None if single_ms is None else single_ms / (world * ms),
-        # rank 0's kernels against its step: the rest is exchange, copies and launch gaps
-        "kernel_ms_per_step": kernel_ms, "non_kernel_ms_per_step": ms - kernel_ms,
+        # kernel time of rank 0 and of the slowest rank against the step: what is left of the step beyond the
+        # slowest rank's kernels is exchange, copies and launch gaps.  With contiguous slices rank 0 has
+        # less work than the others (its first rows see fewer keys), so it waits for them.
+        "kernel_ms_per_step": kernel_ms, "kernel_ms_per_step_slowest_rank": slowest_kernel_ms,
+        "non_kernel_ms_per_step": ms - slowest_kernel_ms,
+        "work_share_of_slowest_rank": (1.0 / world if ring else
+                                       max(sum(min(i, window) + 1 for i in range(r * n, (r + 1) * n))
+                                           for r in range(world)) * w["Hq"] / pairs),
         "e2e": None if not e2e_steps else {"value": flops_step / e2e_ms * 1e-9, "unit": "TFLOP/s",
                                            "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                                            "d2h_bytes_per_step": d2h, "steps": e2e_steps},

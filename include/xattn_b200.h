@@ -299,6 +299,22 @@ typedef struct {
 
 int xattn_b200_softdelta_merge_gradients(const XattnMergeArgs* args, xattn_stream_t stream);
 
+/* Ring attention across GPUs (no counterpart in the reference, a single-GPU library): folds the
+ * normalised FP32 partial output of one K/V block, with its lse, into the running result, in place:
+ *   new = log(exp(lse_acc) + exp(lse_part)),  y_acc = y_acc exp(lse_acc - new) + y_part exp(lse_part - new).
+ * The partial result covers query rows [row_offset, row_offset + rows) of the accumulated one.
+ * y: [B][rows][H][V] FP32 (the forward's `y_state`), lse: [B][H][rows] FP32; v_dim a multiple of 4. */
+typedef struct {
+  int64_t batch, rows, heads, v_dim;
+  int64_t acc_rows, row_offset;  /* rows of the accumulated result; where the partial one starts */
+  float* y_acc;                  /* [B][acc_rows][H][V], updated in place      */
+  float* lse_acc;                /* [B][H][acc_rows], updated in place         */
+  const float* y_part;           /* [B][rows][H][V]                            */
+  const float* lse_part;         /* [B][H][rows]                               */
+} XattnMergeOutputsArgs;
+
+int xattn_b200_merge_partial_outputs(const XattnMergeOutputsArgs* args, xattn_stream_t stream);
+
 /* Per-kernel timing for benchmarks (no counterpart in the reference, whose benchmark tool times
  * whole ops from Python, tests/_benchmark.py:22-35).  While enabled, every entry point brackets
  * its kernels with CUDA events on the launch stream.  xattn_b200_profile_read() synchronises

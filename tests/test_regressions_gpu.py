@@ -224,3 +224,27 @@ def test_level1_autograd_equals_standalone_backward(operation, cuda_device):
     other = getattr(xattn, operation + "_bwd")(dy, q, k, v, y0, lse0, **extra, segment_idx=ids, high_precision_level=1)
     for a, b in zip(grads, other[:3]):
         assert torch.equal(a, b)
+
+
+def test_partial_output_merge_kernel(cuda_device):
+    """The ring's merge of normalised partial outputs by their lse (one kernel, in place) against the same
+    formula in torch, including rows one side or neither side has a key for, and a row offset."""
+    from xattn_b200 import _native, parallel as P
+    gen = torch.Generator().manual_seed(3)
+    B, L, H, V, start = 2, 300, 4, 96, 116
+    mk = lambda *s: torch.randn(s, generator=gen).to(cuda_device)
+    y0, l0 = mk(B, L, H, V), mk(B, H, L) * 3
+    y1, l1 = mk(B, L - start, H, V), mk(B, H, L - start) * 3
+    l0[:, :, 5] = float("-inf"); y0[:, 5] = 0            # no key so far
+    l1[:, :, 7] = float("-inf"); y1[:, 7] = 0            # no key in this block
+    l0[:, :, start + 9] = float("-inf"); y0[:, start + 9] = 0
+    l1[:, :, 9] = float("-inf"); y1[:, 9] = 0            # neither
+    want_y, want_l = y0.clone(), l0.clone()
+    my, ml = P._merge((want_y[:, start:], want_l[:, :, start:]), y1, l1)
+    want_y[:, start:], want_l[:, :, start:] = my, ml
+    got_y, got_l = y0.clone(), l0.clone()
+    _native.merge_partial_outputs(got_y, got_l, y1, l1, start)
+    torch.testing.assert_close(got_y, want_y, atol=1e-6, rtol=1e-5)
+    torch.testing.assert_close(got_l, want_l, atol=1e-6, rtol=1e-6)
+    assert torch.equal(got_y[:, :start], y0[:, :start])
+    assert torch.isinf(got_l[:, :, start + 9]).all() and torch.count_nonzero(got_y[:, start + 9]) == 0

@@ -101,6 +101,14 @@ class MergeArgs(C.Structure):
     ]
 
 
+class MergeOutputsArgs(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int64), ("rows", C.c_int64), ("heads", C.c_int64), ("v_dim", C.c_int64),
+        ("acc_rows", C.c_int64), ("row_offset", C.c_int64),
+        ("y_acc", C.c_void_p), ("lse_acc", C.c_void_p), ("y_part", C.c_void_p), ("lse_part", C.c_void_p),
+    ]
+
+
 _lock = threading.Lock()
 _lib: Optional[C.CDLL] = None
 
@@ -125,6 +133,7 @@ SYMBOLS = {
     "xattn_b200_softdelta_merge_gradients": (C.c_int, [C.POINTER(MergeArgs), C.c_void_p]),
     "xattn_b200_profile_enable": (C.c_int, [C.c_int]),
     "xattn_b200_profile_read": (C.c_int, [C.POINTER(C.c_int), C.POINTER(C.c_float), C.c_int]),
+    "xattn_b200_merge_partial_outputs": (C.c_int, [C.POINTER(MergeOutputsArgs), C.c_void_p]),
     "xattn_b200_selftest_wait_timeout": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p]),
     "xattn_b200_check_status": (C.c_int, [C.c_void_p, C.c_void_p]),
 }

@@ -425,6 +425,22 @@ def softdelta_gate_bwd(dy: Tensor, y: Tensor, neg_read: Tensor, g: Tensor) -> Tu
     return read, dneg, dg
 
 
+def merge_partial_outputs(y_acc: Tensor, lse_acc: Tensor, y_part: Tensor, lse_part: Tensor, row_offset: int = 0) -> None:
+    """Fold a K/V block's normalised FP32 partial output (``y_part`` [B, R, H, V], ``lse_part`` [B, H, R])
+    into the running result, in place; the partial result covers the rows from ``row_offset`` on."""
+    lib = _lib.load()
+    for t in (y_acc, lse_acc, y_part, lse_part):
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise ValueError("partial outputs and their lse must be contiguous FP32 tensors")
+    args = _lib.MergeOutputsArgs()
+    args.batch, args.rows, args.heads, args.v_dim = y_part.shape
+    args.acc_rows, args.row_offset = y_acc.shape[1], int(row_offset)
+    args.y_acc, args.lse_acc = y_acc.data_ptr(), lse_acc.data_ptr()
+    args.y_part, args.lse_part = y_part.data_ptr(), lse_part.data_ptr()
+    with torch.cuda.device(y_acc.device):
+        _lib.check(lib.xattn_b200_merge_partial_outputs(C.byref(args), _stream_ptr()), "xattn_b200_merge_partial_outputs")
+
+
 PROFILE_KINDS = {1: "plan", 2: "fwd", 3: "bwd_pre", 4: "bwd_dq", 5: "bwd_dkv", 6: "gate", 7: "repair",
                  8: "bwd_stats"}
 

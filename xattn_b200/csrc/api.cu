@@ -15,6 +15,7 @@ int merge_gradients_entry(const XattnMergeArgs* a, cudaStream_t stream);
 int build_plan_entry(const XattnPlanArgs* a, cudaStream_t stream);
 int build_varlen_plan_entry(const XattnVarlenPlanArgs* a, cudaStream_t stream);
 int wait_timeout_probe_entry(int32_t* status, int64_t budget_us, cudaStream_t stream);
+int merge_outputs_entry(const XattnMergeOutputsArgs* a, cudaStream_t stream);
 }  // namespace xb
 
 extern "C" {
@@ -95,6 +96,10 @@ int xattn_b200_profile_enable(int enable) { return xb::profile_enable(enable); }
 int xattn_b200_profile_read(int* kinds, float* ms, int capacity) {
   if (!kinds || !ms || capacity < 0) return XATTN_E_INVALID;
   return xb::profile_read(kinds, ms, capacity);
+}
+
+int xattn_b200_merge_partial_outputs(const XattnMergeOutputsArgs* args, xattn_stream_t stream) {
+  return xb::merge_outputs_entry(args, static_cast<cudaStream_t>(stream));
 }
 
 int xattn_b200_selftest_wait_timeout(int32_t* status, int64_t budget_us, xattn_stream_t stream) {

@@ -454,6 +454,61 @@ int zero_constant_entry(const XattnConstantKeyArgs* a, cudaStream_t s) {
 }
 
 // ---------------------------------------------------------------------------
+// Ring attention: fold one K/V block's normalised partial output into the running result.
+//   new = log(exp(lse_acc) + exp(lse_part)),  y_acc = y_acc exp(lse_acc - new) + y_part exp(lse_part - new)
+// One warp per (batch row, query row, head), in place; a row neither side has a key for keeps
+// y = 0 and lse = -inf.  HBM-bound: reads both partial results once, writes one.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) merge_outputs_kernel(float* __restrict__ y_acc, float* __restrict__ lse_acc,
+                                                            const float* __restrict__ y_part,
+                                                            const float* __restrict__ lse_part, long long units,
+                                                            int rows, int heads, int v_dim, int acc_rows,
+                                                            int row_offset) {
+  const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (unit >= units) return;
+  const int lane = threadIdx.x & 31;
+  const int h = (int)(unit % heads);
+  const long long br = unit / heads;
+  const int i = (int)(br % rows);
+  const long long b = br / rows;
+  const size_t l_acc = ((size_t)b * heads + h) * acc_rows + row_offset + i;
+  const float l0 = lse_acc[l_acc], l1 = lse_part[((size_t)b * heads + h) * rows + i];
+  const float mx = fmaxf(l0, l1);
+  float w0 = 0.f, w1 = 0.f, merged = -INFINITY;
+  if (mx != -INFINITY) {
+    const float e0 = expf(l0 - mx), e1 = expf(l1 - mx);
+    const float sum = e0 + e1;
+    merged = mx + logf(sum);
+    w0 = e0 / sum;
+    w1 = e1 / sum;
+  }
+  float4* acc = reinterpret_cast<float4*>(y_acc + (((size_t)b * acc_rows + row_offset + i) * heads + h) * v_dim);
+  const float4* part = reinterpret_cast<const float4*>(y_part + (((size_t)b * rows + i) * heads + h) * v_dim);
+  for (int c = lane; c < v_dim / 4; c += 32) {
+    const float4 a = acc[c], p = part[c];
+    acc[c] = make_float4(a.x * w0 + p.x * w1, a.y * w0 + p.y * w1, a.z * w0 + p.z * w1, a.w * w0 + p.w * w1);
+  }
+  if (lane == 0) lse_acc[l_acc] = merged;
+}
+
+int merge_outputs_entry(const XattnMergeOutputsArgs* a, cudaStream_t s) {
+  if (!a || !a->y_acc || !a->lse_acc || !a->y_part || !a->lse_part) { set_error("null merge arguments"); return XATTN_E_INVALID; }
+  if (a->batch <= 0 || a->rows <= 0 || a->heads <= 0 || a->v_dim <= 0 || a->v_dim % 4 || a->row_offset < 0 ||
+      a->row_offset + a->rows > a->acc_rows) { set_error("bad merge sizes"); return XATTN_E_INVALID; }
+  for (const void* ptr : {(const void*)a->y_acc, (const void*)a->y_part}) {
+    if (reinterpret_cast<uintptr_t>(ptr) & 15) { set_error("partial outputs must be 16-byte aligned"); return XATTN_E_INVALID; }
+  }
+  const long long units = (long long)a->batch * a->rows * a->heads;
+  const long long blocks = (units + 3) / 4;
+  if (blocks > 0x7fffffffLL) { set_error("merge grid out of range"); return XATTN_E_INVALID; }
+  merge_outputs_kernel<<<(unsigned)blocks, 128, 0, s>>>(a->y_acc, a->lse_acc, a->y_part, a->lse_part, units, (int)a->rows,
+                                                        (int)a->heads, (int)a->v_dim, (int)a->acc_rows, (int)a->row_offset);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_error("merge launch: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
+  return XATTN_OK;
+}
+
+// ---------------------------------------------------------------------------
 // Self-test of the bounded wait: one CTA waits on a barrier that nothing will ever complete, with a
 // short time limit, and must come back with (site << 8) | kStatusWaitTimeout in the status word
 // instead of hanging.  This is the path every tensor kernel takes when a bulk copy or a product never

@@ -171,6 +171,13 @@ class NativeBlockKernels:
         plan = _native.build_plan(q.shape[0], q.shape[1], k.shape[1], q.device, visibility="full" if causal else "all")
         return _native.attention_bwd(dy, q, k, v, y, lse, plan, scale)
 
+    @staticmethod
+    def merge(acc: Tuple[Tensor, Tensor], y: Tensor, lse: Tensor, start: int = 0) -> Tuple[Tensor, Tensor]:
+        """Fold a block's partial result into the running one, in place, with one kernel."""
+        from . import _native
+        _native.merge_partial_outputs(acc[0], acc[1], y, lse, start)
+        return acc
+
 
 def _merge(acc: Optional[Tuple[Tensor, Tensor]], y: Tensor, lse: Tensor) -> Tuple[Tensor, Tensor]:
     """Combine normalised partial outputs by their log-sum-exp (lse [B,H,L], y [B,L,H,V])."""
@@ -214,6 +221,16 @@ class _RingCausal(torch.autograd.Function):
         send_to, recv_from = (rank + 1) % world, (rank - 1) % world
         blk_k, blk_v = k.contiguous(), v.contiguous()
         acc = None
+        native_merge = getattr(kernels, "merge", None)
+
+        def fold(acc, y_t, lse_t, start):
+            """Running result after one more block; the block kernels' own merge where they have one."""
+            if acc is None:
+                return _merge(None, y_t, lse_t)
+            if native_merge is not None:
+                return native_merge(acc, y_t, lse_t, start)
+            return _merge_rows(acc, y_t, lse_t, start) if start else _merge(acc, y_t, lse_t)
+
         for t in range(world):
             nxt_k = nxt_v = None
             pending = []
@@ -228,13 +245,13 @@ class _RingCausal(torch.autograd.Function):
             if zigzag and t > 0:
                 if t <= rank:   # an earlier rank's block: its first chunk lies before both local chunks
                     y_t, lse_t = kernels.forward(q, blk_k[:, :half], blk_v[:, :half], scale, causal=False)
-                    acc = _merge(acc, y_t, lse_t)
+                    acc = fold(acc, y_t, lse_t, 0)
                 else:           # a later rank's block: both of its chunks lie between the local ones
                     y_t, lse_t = kernels.forward(q[:, half:], blk_k, blk_v, scale, causal=False)
-                    acc = _merge_rows(acc, y_t, lse_t, half)
+                    acc = fold(acc, y_t, lse_t, half)
             elif t <= rank:     # the block of rank (rank - t): on or below the diagonal
                 y_t, lse_t = kernels.forward(q, blk_k, blk_v, scale, causal=(t == 0))
-                acc = _merge(acc, y_t, lse_t)
+                acc = fold(acc, y_t, lse_t, 0)
             _wait(pending)
             if t + 1 < world:
                 blk_k, blk_v = nxt_k, nxt_v
@@ -277,15 +294,15 @@ class _RingCausal(torch.autograd.Function):
                 if t <= rank:
                     dq_t, dk_t, dv_t = kernels.backward(dy, q, blk_k[:, :half], blk_v[:, :half], y, lse, scale,
                                                         causal=False)
-                    dq += dq_t.to(wide)
+                    dq += dq_t
                     rows = slice(0, half)
                 else:
                     dq_t, dk_t, dv_t = kernels.backward(dy[:, half:], q[:, half:], blk_k, blk_v, y[:, half:],
                                                         lse[:, :, half:], scale, causal=False)
-                    dq[:, half:] += dq_t.to(wide)
+                    dq[:, half:] += dq_t
             elif t <= rank:
                 dq_t, dk_t, dv_t = kernels.backward(dy, q, blk_k, blk_v, y, lse, scale, causal=(t == 0))
-                dq += dq_t.to(wide)
+                dq += dq_t
             # this block's accumulator: zero on its home rank (t == 0), else what the previous rank sent on
             if acc_in is None:
                 dk_acc = torch.zeros(k.shape, dtype=wide, device=k.device)
@@ -294,8 +311,8 @@ class _RingCausal(torch.autograd.Function):
                 _wait(acc_in[0])
                 dk_acc, dv_acc = acc_in[1], acc_in[2]
             if dk_t is not None:
-                dk_acc[:, rows] += dk_t.to(wide)
-                dv_acc[:, rows] += dv_t.to(wide)
+                dk_acc[:, rows] += dk_t          # FP32 accumulators take the 16-bit results as they are
+                dv_acc[:, rows] += dv_t
             # pass the accumulator on (the last step brings it home) and ask for the next one
             recv_dk, recv_dv = torch.empty_like(dk_acc), torch.empty_like(dv_acc)
             works = dist.batch_isend_irecv([
