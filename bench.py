@@ -334,9 +334,13 @@ def run_ours(args, w):
 
     level = args.level
 
+    leaves = [t.requires_grad_() for t in (q, k, v)]
+
     def step():
-        y, lse = xattn.causal_flash_attn_fwd(q, k, v, **meta, high_precision_level=level)
-        return (y, *xattn.causal_flash_attn_bwd(dy, q, k, v, y, lse, **meta, high_precision_level=level))
+        # the training form of the op: forward, then autograd's backward on the forward's saved state
+        # (one mask plan per step; at level 1 the backward reuses the forward's statistics and anchors)
+        y = xattn.causal_flash_attn(*leaves, **meta, high_precision_level=level)
+        return (y, *torch.autograd.grad(y, leaves, dy))
 
     def barrier():
         torch.cuda.synchronize()
