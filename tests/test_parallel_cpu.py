@@ -175,3 +175,44 @@ def test_zigzag_indices_partition_the_sequence():
         P.ring_causal_flash_attn(q, q, q, layout="zigzag")
     with pytest.raises(ValueError, match="layout"):
         P.ring_causal_flash_attn(q, q, q, layout="striped")
+
+
+def _failing_worker(rank, world, port, results):
+    """Rank 1 leaves before the exchange (as a crashed rank would, between steps, with nothing in flight);
+    rank 0 must come back from its halo exchange with an error instead of waiting for ever."""
+    import datetime
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    from xattn_b200 import parallel as P
+    if rank == 1:
+        results[rank] = "left"
+        os._exit(0)                      # no destroy_process_group: the peer only sees the connection go
+    q = torch.randn(1, 16, 2, 8, dtype=torch.float64)
+    try:
+        P.sequence_parallel_flash_swa(q, q[:, :, :1], q[:, :, :1], 4, op=_oracle_op("window"))
+        results[rank] = "returned"
+    except Exception as exc:             # gloo reports the closed connection or the timeout
+        results[rank] = "error: " + type(exc).__name__
+
+
+def test_a_rank_that_left_ends_the_halo_exchange_with_an_error():
+    """Failure detection on the host side: no GPU is involved, nothing hangs.  The surviving rank's send to
+    the rank that left fails (connection closed, or the process group's timeout), it reports the error and
+    exits; a rank that is still alive after the grace period is killed."""
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as manager:
+        results = manager.dict()
+        port = _free_port()
+        procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, results)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout=60)
+        stragglers = [p for p in procs if p.is_alive()]
+        for p in stragglers:
+            p.kill()
+            p.join()
+        assert not stragglers, "the surviving rank did not return from the exchange"
+        assert results.get(1) == "left"
+        assert str(results.get(0, "")).startswith("error"), dict(results)
