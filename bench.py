@@ -209,7 +209,8 @@ class ClockSampler(threading.Thread):
 
     def stop(self):
         self._stop_event.set()
-        self.join(timeout=2)
+        if self.is_alive():
+            self.join(timeout=2)
         return {
             "sm_mhz": statistics.median(self.samples) if self.samples else None,
             "sm_max_mhz": self.max_mhz,
@@ -469,7 +470,8 @@ def run_ours(args, w):
             if rank == 0:
                 sharded[name] = {key: res[key] for key in (
                     "metric", "value", "unit", "ms_per_step", "scaling", "per_gpu_tflops", "single_gpu_ms",
-                    "efficiency_vs_1gpu", "kernel_ms_per_step", "kernel_ms_per_step_slowest_rank",
+                    "efficiency_vs_1gpu", "launch", "eager_ms_per_step", "eager_host_enqueue_ms_per_step",
+                    "kernel_ms_per_step", "kernel_ms_per_step_slowest_rank",
                     "non_kernel_ms_per_step", "work_share_of_slowest_rank", "kernels")}
                 sharded[name]["workload"] = res["config"]["workload"]
 
@@ -835,19 +837,64 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
     for _ in range(max(args.warmup, 3)):
         step(ql, kl, vl, dyl)
     _native.check_status()
-    sampler = ClockSampler(dev.index)
+    # 1. A few eager steps with the library's per-launch events on: the kernel breakdown, and what a step
+    #    costs when every launch and every NCCL call is issued from Python.
+    eager_steps = max(3, min(steps, 5))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    sampler.start()
     _native.profile_enable(True)
+    h0 = time.perf_counter()
     e0.record()
-    for _ in range(steps):
+    for _ in range(eager_steps):
         step(ql, kl, vl, dyl)
     e1.record()
+    host_ms = (time.perf_counter() - h0) / eager_steps * 1e3
     barrier()
     _native.profile_enable(False)
     records = _native.profile_read()
-    ms = e0.elapsed_time(e1) / steps
+    eager_ms = e0.elapsed_time(e1) / eager_steps
+    # 2. The timed region: the same step captured once in a CUDA graph (exchanges included: NCCL send / recv
+    #    are stream operations) and replayed.  A sharded step is short (about a millisecond of kernels per
+    #    rank at eight GPUs) against some forty Python-issued launches and two NCCL group calls of about half a
+    #    millisecond of host time each, so issued eagerly it is bound by the host, not by the GPUs or NVLink.
+    #    XATTN_BENCH_NO_GRAPH=1 times the eager step instead.
+    launch = "eager (one Python call per launch)"
+    graph = None
+    if not os.environ.get("XATTN_BENCH_NO_GRAPH"):
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            step(ql, kl, vl, dyl)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            captured = step(ql, kl, vl, dyl)
+        barrier()
+        for _ in range(3):
+            graph.replay()
+        launch = "CUDA graph replay of the captured step, exchanges included"
+    run = graph.replay if graph is not None else (lambda: step(ql, kl, vl, dyl))
+    sampler = ClockSampler(dev.index)
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    g0.record()
+    for _ in range(steps):
+        run()
+    g1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = g0.elapsed_time(g1) / steps
+    _native.check_status()
+    if graph is not None:
+        # the graph holds NCCL work: it has to be gone before the process group is torn down (a live
+        # graph made the teardown wait for ever), so it goes before anything else happens
+        del graph, captured, run
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
+    barrier()
     out_host = None
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2e_steps = max(3, min(steps, 10)) if with_e2e else 0
@@ -869,7 +916,6 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
     f1.record()
     barrier()
     e2e_ms = f0.elapsed_time(f1) / max(e2e_steps, 1)
-    clocks = sampler.stop()
     # the same sequence unsharded on one GPU (rank 0 alone), device-timed
     single_ms = None
     if world > 1 and rank == 0:
@@ -893,7 +939,7 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
         _native.check_status()
         del qf, kf, vf, dyf
     barrier()
-    own_kernel_ms = sum(t for _, t in records) / steps
+    own_kernel_ms = sum(t for _, t in records) / eager_steps
     times = torch.tensor([ms, e2e_ms, own_kernel_ms], dtype=torch.float64, device=dev)
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms, slowest_kernel_ms = float(times[0]), float(times[1]), float(times[2])
@@ -903,13 +949,13 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
     per_kind = {}
     for kind, t in records:
         per_kind.setdefault(kind, []).append(t)
-    kernels = {kd: {"launches": len(vs), "avg_ms": sum(vs) / len(vs), "ms_per_step": sum(vs) / steps,
-                    "share": sum(vs) / (ms * steps)} for kd, vs in per_kind.items()}
+    kernels = {kd: {"launches": len(vs), "avg_ms": sum(vs) / len(vs), "ms_per_step": sum(vs) / eager_steps,
+                    "share": sum(vs) / (ms * eager_steps)} for kd, vs in per_kind.items()}
     kernel_ms = sum(kv["ms_per_step"] for kv in kernels.values())
     rank_pairs = pairs / world
     dkv = kernels.get("bwd_dkv", {"avg_ms": float("inf"), "launches": 1})
     # the ring launches the kernel once per block step; the work of a rank is spread over them
-    achieved = 8 * D * rank_pairs / (dkv["avg_ms"] * dkv["launches"] / steps) * 1e-9
+    achieved = 8 * D * rank_pairs / (dkv["avg_ms"] * dkv["launches"] / eager_steps) * 1e-9
     h2d = sum(t.numel() * t.element_size() for t in pinned) * world
     d2h = sum(t.numel() * t.element_size() for t in out_host) * world if out_host else 0
     return {
@@ -932,6 +978,8 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
         # kernel time of rank 0 and of the slowest rank against the step: what is left of the step beyond the
         # slowest rank's kernels is exchange, copies and launch gaps.  With contiguous slices rank 0 has
         # less work than the others (its first rows see fewer keys), so it waits for them.
+        "launch": launch,
+        "eager_ms_per_step": eager_ms, "eager_host_enqueue_ms_per_step": host_ms,
         "kernel_ms_per_step": kernel_ms, "kernel_ms_per_step_slowest_rank": slowest_kernel_ms,
         "non_kernel_ms_per_step": ms - slowest_kernel_ms,
         "work_share_of_slowest_rank": (1.0 / world if ring else
@@ -940,7 +988,8 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
         "e2e": None if not e2e_steps else {"value": flops_step / e2e_ms * 1e-9, "unit": "TFLOP/s",
                                            "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                                            "d2h_bytes_per_step": d2h, "steps": e2e_steps},
-        "gpu_launches": len(records) + 3 * len(per_kind.get("plan", [])),
+        # kernels of this library per timed step (counted on the eager steps) times the timed steps
+        "gpu_launches": (len(records) + 3 * len(per_kind.get("plan", []))) // eager_steps * steps,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "bwd_dkv",
                      **tensor_roofline(achieved, peaks, peak_src, ms * steps * 1e-3), "traffic": None},

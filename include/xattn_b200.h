@@ -207,7 +207,16 @@ typedef struct {
   const float* grad_unscale;     /* optional device scalar multiplied into dq, dk and dv before they are
                                     rounded (undoes a power-of-two prescale of dy, the reference's
                                     xattn/ops/_precision_backend.py:203-225), or NULL  */
+  int phases;                    /* 0: the whole backward.  Else a set of XATTN_BWD_PHASE_* bits: the
+                                    call runs only those kernels.  For a caller that wants dK / dV
+                                    before dQ (sequence sharding sends the halo's dK / dV to the
+                                    previous GPU while the dQ kernel runs): first PRE | DKV, then DQ,
+                                    with the same arguments and workspace.  PRE (the row statistics)
+                                    must have run before DQ or DKV.  No counterpart in the reference,
+                                    a single-GPU library whose backward is one launch sequence        */
 } XattnBwdArgs;
+
+enum { XATTN_BWD_PHASE_PRE = 1, XATTN_BWD_PHASE_DQ = 2, XATTN_BWD_PHASE_DKV = 4 };
 
 /* With high_precision = 1 the backward restates the reference's precision pipeline
  * (xattn/ops/_precision_backend.py:29-170) on this library's kernels: `lse` and `anchor` must come

@@ -248,3 +248,28 @@ def test_partial_output_merge_kernel(cuda_device):
     torch.testing.assert_close(got_l, want_l, atol=1e-6, rtol=1e-6)
     assert torch.equal(got_y[:, :start], y0[:, :start])
     assert torch.isinf(got_l[:, :, start + 9]).all() and torch.count_nonzero(got_y[:, start + 9]) == 0
+
+
+@pytest.mark.parametrize("level", (0, 1))
+def test_backward_in_phases_gives_the_same_bits(level, cuda_device):
+    """dK / dV first and dQ in a second call (the order sequence sharding uses to send the halo's gradients
+    while the dQ kernel runs) against the one-call backward."""
+    from xattn_b200 import _lib, _native
+    gen = torch.Generator().manual_seed(17)
+    B, Lq, Lk, H, Hkv, D = 2, 300, 428, 4, 2, 128
+    mk = lambda *s: torch.randn(s, generator=gen).to(cuda_device, torch.bfloat16)
+    q, k, v, dy = mk(B, Lq, H, D), mk(B, Lk, Hkv, D), mk(B, Lk, Hkv, D), mk(B, Lq, H, D)
+    plan = _native.build_plan(B, Lq, Lk, cuda_device, visibility="window", span=77)
+    out = _native.attention_fwd(q, k, v, plan, D ** -0.5, high_precision=bool(level), return_anchor=bool(level))
+    y, lse = out[0], out[1]
+    anchor = out[2] if level else None
+    whole = _native.BackwardCall(dy, q, k, v, y, lse, plan, D ** -0.5, anchor=anchor).run()
+    split = _native.BackwardCall(dy, q, k, v, y, lse, plan, D ** -0.5, anchor=anchor)
+    split.dq.fill_(float("nan"))
+    split.run(_lib.BWD_PHASE_PRE | _lib.BWD_PHASE_DKV)
+    torch.cuda.synchronize()
+    assert torch.equal(split.dk, whole.dk) and torch.equal(split.dv, whole.dv)
+    assert torch.isnan(split.dq).all()                  # not touched yet
+    split.run(_lib.BWD_PHASE_DQ)
+    assert torch.equal(split.dq, whole.dq)
+    xattn.check_status()

@@ -17,6 +17,7 @@ LIB_PATH = os.environ.get("XATTN_B200_LIBRARY") or os.path.join(_HERE, "libxattn
 XATTN_DTYPE_F16, XATTN_DTYPE_BF16 = 0, 1
 VIS_FULL, VIS_WINDOW, VIS_CHUNK, VIS_ALL = 0, 1, 2, 3
 ABI_VERSION = 2          # XATTN_B200_ABI_VERSION of include/xattn_b200.h
+BWD_PHASE_PRE, BWD_PHASE_DQ, BWD_PHASE_DKV = 1, 2, 4
 
 
 class PlanArgs(C.Structure):
@@ -69,6 +70,7 @@ class BwdArgs(C.Structure):
         ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
         ("workspace", C.c_void_p), ("status", C.c_void_p),
         ("high_precision", C.c_int), ("anchor", C.c_void_p), ("grad_unscale", C.c_void_p),
+        ("phases", C.c_int),
     ]
 
 

@@ -287,6 +287,63 @@ def attention_fwd(
     return (y, lse, anchor) if return_anchor else (y, lse)
 
 
+class BackwardCall:
+    """One backward of ``attention_fwd``'s result, runnable in phases.
+
+    ``run()`` launches the whole backward.  ``run(_lib.BWD_PHASE_PRE | _lib.BWD_PHASE_DKV)`` followed by
+    ``run(_lib.BWD_PHASE_DQ)`` launches dK / dV first, so that a caller can start sending parts of them
+    (the K/V halo's gradients of a sequence-sharded run) while the dQ kernel runs.  Outputs ``dq``,
+    ``dk``, ``dv`` (shaped like q, k, v with previous K/V included, input dtype) and the workspace are
+    allocated here once and shared by the phases."""
+
+    def __init__(self, dy: Tensor, q: Tensor, k: Tensor, v: Tensor, y: Tensor, lse: Tensor, plan: Tensor,
+                 scale: float, *, anchor: Optional[Tensor] = None, grad_unscale: Optional[Tensor] = None):
+        lib = _lib.load()
+        require_cuda(q, "xattn_b200 backward")
+        q, k, v, y, dy = tma_ready(q), tma_ready(k), tma_ready(v), tma_ready(y), tma_ready(dy)
+        lse = lse.contiguous()
+        B, Lq, Hq, D = q.shape
+        Lk, Hkv, V = k.shape[1], k.shape[2], v.shape[3]
+        self.dq = torch.empty((B, Lq, Hq, D), dtype=q.dtype, device=q.device)
+        self.dk = torch.empty((B, Lk, Hkv, D), dtype=q.dtype, device=q.device)
+        self.dv = torch.empty((B, Lk, Hkv, V), dtype=q.dtype, device=q.device)
+        nbytes = lib.xattn_b200_bwd_workspace_bytes_hp if anchor is not None else lib.xattn_b200_bwd_workspace_bytes
+        ws = torch.empty(int(nbytes(B, Hq, Lq)) // 4, dtype=torch.float32, device=q.device)
+        args = _lib.BwdArgs()
+        args.dtype = _DTYPES[q.dtype]
+        args.batch, args.q_len, args.k_len = B, Lq, Lk
+        args.q_heads, args.kv_heads, args.qk_dim, args.v_dim = Hq, Hkv, D, V
+        args.q, args.k, args.v, args.y, args.dy = q.data_ptr(), k.data_ptr(), v.data_ptr(), y.data_ptr(), dy.data_ptr()
+        for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("y_strides", y), ("dy_strides", dy)):
+            setattr(args, name, (C.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2)))
+        args.lse = lse.data_ptr()
+        args.scale = float(scale)
+        args.plan = plan.data_ptr()
+        args.dq, args.dk, args.dv = self.dq.data_ptr(), self.dk.data_ptr(), self.dv.data_ptr()
+        args.workspace = ws.data_ptr()
+        if anchor is not None:
+            if anchor.shape != (B, Hq, Lq) or anchor.dtype != torch.int32 or not anchor.is_contiguous():
+                raise ValueError("anchor must be a contiguous int32 tensor [B, Hq, Lq]")
+            args.high_precision = 1
+            args.anchor = anchor.data_ptr()
+        if grad_unscale is not None:
+            if grad_unscale.dtype != torch.float32 or grad_unscale.numel() != 1 or grad_unscale.device != q.device:
+                raise ValueError("grad_unscale must be one FP32 number on the inputs' device")
+            args.grad_unscale = grad_unscale.data_ptr()
+        self._args, self._device = args, q.device
+        self._keep = (q, k, v, y, dy, lse, plan, ws, anchor, grad_unscale)    # alive until the last phase has run
+
+    def run(self, phases: int = 0) -> "BackwardCall":
+        lib = _lib.load()
+        self._args.phases = int(phases)
+        with torch.cuda.device(self._device):
+            st = _pre_launch(self._device)
+            self._args.status = st.status.data_ptr()
+            _lib.check(lib.xattn_b200_bwd(C.byref(self._args), _stream_ptr()), "xattn_b200_bwd")
+            _post_launch(st)
+        return self
+
+
 def attention_bwd(
     dy: Tensor,
     q: Tensor,
@@ -307,44 +364,8 @@ def attention_bwd(
     centred terms, P formed as a square of its root (xattn/ops/_precision_backend.py:29-170).
     ``grad_unscale``: optional FP32 device scalar multiplied into the three gradients before they are
     rounded (undoes a power-of-two prescale of ``dy``)."""
-    lib = _lib.load()
-    require_cuda(q, "xattn_b200 backward")
-    q, k, v, y, dy = tma_ready(q), tma_ready(k), tma_ready(v), tma_ready(y), tma_ready(dy)
-    lse = lse.contiguous()
-    B, Lq, Hq, D = q.shape
-    Lk, Hkv, V = k.shape[1], k.shape[2], v.shape[3]
-    dq = torch.empty((B, Lq, Hq, D), dtype=q.dtype, device=q.device)
-    dk = torch.empty((B, Lk, Hkv, D), dtype=q.dtype, device=q.device)
-    dv = torch.empty((B, Lk, Hkv, V), dtype=q.dtype, device=q.device)
-    nbytes = lib.xattn_b200_bwd_workspace_bytes_hp if anchor is not None else lib.xattn_b200_bwd_workspace_bytes
-    ws = torch.empty(int(nbytes(B, Hq, Lq)) // 4, dtype=torch.float32, device=q.device)
-    args = _lib.BwdArgs()
-    args.dtype = _DTYPES[q.dtype]
-    args.batch, args.q_len, args.k_len = B, Lq, Lk
-    args.q_heads, args.kv_heads, args.qk_dim, args.v_dim = Hq, Hkv, D, V
-    args.q, args.k, args.v, args.y, args.dy = q.data_ptr(), k.data_ptr(), v.data_ptr(), y.data_ptr(), dy.data_ptr()
-    for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("y_strides", y), ("dy_strides", dy)):
-        setattr(args, name, (C.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2)))
-    args.lse = lse.data_ptr()
-    args.scale = float(scale)
-    args.plan = plan.data_ptr()
-    args.dq, args.dk, args.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
-    args.workspace = ws.data_ptr()
-    if anchor is not None:
-        if anchor.shape != (B, Hq, Lq) or anchor.dtype != torch.int32 or not anchor.is_contiguous():
-            raise ValueError("anchor must be a contiguous int32 tensor [B, Hq, Lq]")
-        args.high_precision = 1
-        args.anchor = anchor.data_ptr()
-    if grad_unscale is not None:
-        if grad_unscale.dtype != torch.float32 or grad_unscale.numel() != 1 or grad_unscale.device != q.device:
-            raise ValueError("grad_unscale must be one FP32 number on the inputs' device")
-        args.grad_unscale = grad_unscale.data_ptr()
-    with torch.cuda.device(q.device):
-        st = _pre_launch(q.device)
-        args.status = st.status.data_ptr()
-        _lib.check(lib.xattn_b200_bwd(C.byref(args), _stream_ptr()), "xattn_b200_bwd")
-        _post_launch(st)
-    return dq, dk, dv
+    call = BackwardCall(dy, q, k, v, y, lse, plan, scale, anchor=anchor, grad_unscale=grad_unscale).run()
+    return call.dq, call.dk, call.dv
 
 
 def zero_constant_key_rows(dq: Tensor, k_all: Tensor, plan: Tensor) -> Tensor:

@@ -1275,8 +1275,12 @@ static int launch_dkv(const XattnBwdArgs& a, const BwdParams& p, cudaStream_t st
   return XATTN_OK;
 }
 
+// Which parts of the backward a call runs (XattnBwdArgs.phases; 0 means all three).
+constexpr int kPhasePre = XATTN_BWD_PHASE_PRE, kPhaseDq = XATTN_BWD_PHASE_DQ, kPhaseDkv = XATTN_BWD_PHASE_DKV;
+
 template <typename T, bool HP>
 static int launch_bwd(const XattnBwdArgs& a, BwdParams& p, cudaStream_t stream) {
+  const int phases = a.phases ? a.phases : (kPhasePre | kPhaseDq | kPhaseDkv);
   // 1. preprocess
   // workspace: -delta, -lse2 (FP32 each), the 32-byte rows of extra GEMM columns, and (high precision)
   // -dP at the anchor key
@@ -1287,7 +1291,9 @@ static int launch_bwd(const XattnBwdArgs& a, BwdParams& p, cudaStream_t stream) 
   float* ndpa = a.workspace + 10 * rows;
   p.ndelta = ndelta; p.nlse2 = nlse2; p.row_terms = row_terms;
   p.ndpa = HP ? ndpa : nullptr; p.ndelta_out = ndelta; p.row_terms_out = row_terms;
-  if (HP) {
+  if (!(phases & kPhasePre)) {
+    // the statistics are in the workspace already (an earlier call with the same arguments)
+  } else if (HP) {
     const long long blocks = ((long long)rows + 7) / 8;
     if (blocks > 0x7fffffffLL) { set_error("backward preprocess grid out of range"); return XATTN_E_INVALID; }
     ProfileScope prof(kProfBwdPre, stream);
@@ -1309,20 +1315,21 @@ static int launch_bwd(const XattnBwdArgs& a, BwdParams& p, cudaStream_t stream) 
   const int hd = p.D > p.V ? p.D : p.V;
   constexpr int kDq = HP ? kDqHigh : kDqPlain;
   int rc;
-  // (high precision: the statistics pass)   2. dQ   3. dK / dV
+  const bool pre = phases & kPhasePre, dq = phases & kPhaseDq, dkv = phases & kPhaseDkv;
+  // (high precision: the statistics pass belongs to the preprocess phase)   2. dQ   3. dK / dV
   if (hd <= 64) {
-    if (HP && (rc = launch_dq<T, 64, 128, kDqStats>(a, p, stream))) return rc;
-    if ((rc = launch_dq<T, 64, 128, kDq>(a, p, stream))) return rc;
-    if ((rc = launch_dkv<T, 64, kDkvBoth, 128, HP>(a, p, stream))) return rc;
+    if (HP && pre && (rc = launch_dq<T, 64, 128, kDqStats>(a, p, stream))) return rc;
+    if (dq && (rc = launch_dq<T, 64, 128, kDq>(a, p, stream))) return rc;
+    if (dkv && (rc = launch_dkv<T, 64, kDkvBoth, 128, HP>(a, p, stream))) return rc;
   } else if (hd <= 128) {
-    if (HP && (rc = launch_dq<T, 128, 128, kDqStats>(a, p, stream))) return rc;
-    if ((rc = launch_dq<T, 128, 128, kDq>(a, p, stream))) return rc;
-    if ((rc = launch_dkv<T, 128, kDkvBoth, 128, HP>(a, p, stream))) return rc;
+    if (HP && pre && (rc = launch_dq<T, 128, 128, kDqStats>(a, p, stream))) return rc;
+    if (dq && (rc = launch_dq<T, 128, 128, kDq>(a, p, stream))) return rc;
+    if (dkv && (rc = launch_dkv<T, 128, kDkvBoth, 128, HP>(a, p, stream))) return rc;
   } else {
-    if (HP && (rc = launch_dq<T, 256, 64, kDqStats>(a, p, stream))) return rc;
-    if ((rc = launch_dq<T, 256, 64, kDq>(a, p, stream))) return rc;
-    if ((rc = launch_dkv<T, 256, kDvOnly, 64, HP>(a, p, stream))) return rc;
-    if ((rc = launch_dkv<T, 256, kDkOnly, 32, HP>(a, p, stream))) return rc;
+    if (HP && pre && (rc = launch_dq<T, 256, 64, kDqStats>(a, p, stream))) return rc;
+    if (dq && (rc = launch_dq<T, 256, 64, kDq>(a, p, stream))) return rc;
+    if (dkv && (rc = launch_dkv<T, 256, kDvOnly, 64, HP>(a, p, stream))) return rc;
+    if (dkv && (rc = launch_dkv<T, 256, kDkOnly, 32, HP>(a, p, stream))) return rc;
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("backward launch: %s", cudaGetErrorString(e)); return XATTN_E_CUDA; }
@@ -1340,6 +1347,7 @@ int bwd_entry(const XattnBwdArgs* a, cudaStream_t stream) {
   if (!(a->scale > 0.f) || !isfinite(a->scale)) { set_error("scale must be finite and positive"); return XATTN_E_INVALID; }
   if (!a->q || !a->k || !a->v || !a->y || !a->dy || !a->lse || !a->plan || !a->dq || !a->dk || !a->dv ||
       !a->workspace || !a->status) { set_error("null tensor pointer"); return XATTN_E_INVALID; }
+  if (a->phases & ~(XATTN_BWD_PHASE_PRE | XATTN_BWD_PHASE_DQ | XATTN_BWD_PHASE_DKV)) { set_error("unknown backward phase bits"); return XATTN_E_INVALID; }
   if (a->high_precision && !a->anchor) { set_error("the high-precision backward needs the forward's anchor keys"); return XATTN_E_INVALID; }
   for (const void* ptr : {a->q, a->y, a->dy, (const void*)a->dq, (const void*)a->dk, (const void*)a->dv,
                           (const void*)a->workspace}) {

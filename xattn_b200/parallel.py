@@ -59,6 +59,30 @@ def _wait(works) -> None:
         work.wait()
 
 
+def _assemble_halo(ctx, k: Tensor, v: Tensor, halo: int, ids: Optional[Tensor], group):
+    """[previous rank's last ``halo`` tokens ‖ own tokens] for K, V and the segment ids; what the backward
+    needs to know about the exchange is left on ``ctx``."""
+    rank, world = _world(group)
+    nxt = rank + 1 if rank + 1 < world else None
+    prv = rank - 1 if rank > 0 else None
+    n_prev = halo if prv is not None else 0
+    ctx.group, ctx.halo, ctx.n_prev, ctx.nxt, ctx.prv = group, halo, n_prev, nxt, prv
+    tensors = [k, v] + ([ids] if ids is not None else [])
+    out = [t.new_empty((t.shape[0], n_prev + t.shape[1], *t.shape[2:])) for t in tensors]
+    # a slice along the token axis is one block of memory only for a batch of one: otherwise the
+    # halo lands in a buffer of its own first
+    direct = k.shape[0] == 1
+    landing = [o[:, :n_prev] if direct else o.new_empty((o.shape[0], n_prev, *o.shape[2:])) for o in out]
+    works = _p2p([t[:, -halo:] for t in tensors], nxt, landing, prv, group)
+    for o, t in zip(out, tensors):
+        o[:, n_prev:].copy_(t)
+    _wait(works)
+    if not direct and n_prev:
+        for o, l in zip(out, landing):
+            o[:, :n_prev].copy_(l)
+    return out[0], out[1], (out[2] if ids is not None else None)
+
+
 class _HaloAssemble(torch.autograd.Function):
     """(k, v) of this rank -> (k_all, v_all, ids_all): the last ``halo`` tokens of the previous rank's K / V
     (and segment ids) in front of this rank's own, in one buffer each.  The attention op then sees a
@@ -74,28 +98,10 @@ class _HaloAssemble(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, k: Tensor, v: Tensor, halo: int, ids: Optional[Tensor], group):
-        rank, world = _world(group)
-        nxt = rank + 1 if rank + 1 < world else None
-        prv = rank - 1 if rank > 0 else None
-        n_prev = halo if prv is not None else 0
-        ctx.group, ctx.halo, ctx.n_prev, ctx.nxt, ctx.prv = group, halo, n_prev, nxt, prv
-        tensors = [k, v] + ([ids] if ids is not None else [])
-        out = [t.new_empty((t.shape[0], n_prev + t.shape[1], *t.shape[2:])) for t in tensors]
-        # a slice along the token axis is one block of memory only for a batch of one: otherwise the
-        # halo lands in a buffer of its own first
-        direct = k.shape[0] == 1
-        landing = [o[:, :n_prev] if direct else o.new_empty((o.shape[0], n_prev, *o.shape[2:])) for o in out]
-        works = _p2p([t[:, -halo:] for t in tensors], nxt, landing, prv, group)
-        for o, t in zip(out, tensors):
-            o[:, n_prev:].copy_(t)
-        _wait(works)
-        if not direct and n_prev:
-            for o, l in zip(out, landing):
-                o[:, :n_prev].copy_(l)
-        ids_all = out[2] if ids is not None else None
+        k_all, v_all, ids_all = _assemble_halo(ctx, k, v, halo, ids, group)
         if ids_all is not None:
             ctx.mark_non_differentiable(ids_all)
-        return out[0], out[1], ids_all
+        return k_all, v_all, ids_all
 
     @staticmethod
     def backward(ctx, dk_all: Tensor, dv_all: Tensor, _ids):
@@ -110,7 +116,49 @@ class _HaloAssemble(torch.autograd.Function):
         return own[0], own[1], None, None, None
 
 
-def _sequence_parallel_local(op, q, k, v, span, scale, segment_idx, group, op_kwargs):
+class _ShardedLocalAttention(torch.autograd.Function):
+    """The halo exchange and this package's kernels as one autograd node, so that the backward can order
+    its kernels around the exchange: dK / dV first, the halo rows' gradients start their way back to the
+    previous rank, the dQ kernel runs meanwhile, and only then does this rank wait for the gradients coming
+    from the next rank.  (With the exchange in a node of its own, ``_HaloAssemble``, it can only start after
+    the whole attention backward.)  Level 0, the library's own ops; everything else takes the generic path."""
+
+    @staticmethod
+    def forward(ctx, q: Tensor, k: Tensor, v: Tensor, kind: str, span: int, scale: float, ids: Optional[Tensor], group):
+        from .ops import _core
+        k_all, v_all, ids_all = _assemble_halo(ctx, k, v, span, ids, group)     # leaves halo, n_prev, nxt, prv on ctx
+        q_ids = None if ids_all is None else ids_all[:, ids_all.shape[1] - q.shape[1]:]
+        support = _core.Support(kind, span)
+        y, lse, _, plan = _core.forward(q, k_all, v_all, support, scale, None, None, q_ids, ids_all, return_plan=True)
+        ctx.save_for_backward(q, k_all, v_all, y, lse, plan)
+        ctx.scale = scale
+        return y
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        from . import _lib, _native
+        q, k_all, v_all, y, lse, plan = ctx.saved_tensors
+        halo, n_prev, nxt, prv, group = ctx.halo, ctx.n_prev, ctx.nxt, ctx.prv, ctx.group
+        call = _native.BackwardCall(dy, q, k_all, v_all, y, lse, plan, ctx.scale)
+        call.run(_lib.BWD_PHASE_PRE | _lib.BWD_PHASE_DKV)
+        grads = [call.dk, call.dv]
+        recv = [g.new_empty((g.shape[0], halo, *g.shape[2:])) for g in grads] if nxt is not None else []
+        works = _p2p([g[:, :n_prev] for g in grads], prv, recv, nxt, group)
+        call.run(_lib.BWD_PHASE_DQ)                     # beside the exchange
+        own = [g[:, n_prev:] for g in grads]
+        _wait(works)
+        for g, r in zip(own, recv):
+            g[:, -halo:] += r
+        return call.dq, own[0], own[1], None, None, None, None, None
+
+
+def _sequence_parallel_local(op, q, k, v, span, scale, segment_idx, group, op_kwargs, kind):
+    if op is None and not op_kwargs and q.is_cuda:
+        s = float(scale) if scale is not None else q.shape[-1] ** -0.5
+        return _ShardedLocalAttention.apply(q, k, v, kind, span, s, segment_idx, group)
+    if op is None:
+        from . import ops
+        op = ops.flash_swa if kind == "window" else ops.flash_sca
     k_all, v_all, ids_all = _HaloAssemble.apply(k, v, span, segment_idx, group)
     return op(q, k_all, v_all, span, scale, segment_idx=ids_all, **op_kwargs)
 
@@ -124,13 +172,13 @@ def sequence_parallel_flash_swa(q: Tensor, k: Tensor, v: Tensor, window_size: in
     rank's slice must hold at least ``window_size`` tokens so that the halo comes from one neighbour.
     Differentiable: dK / dV of the halo return to the rank that owns those tokens.
     """
-    if op is None:
-        from .ops import flash_swa as op
     if window_size <= 0:
+        if op is None:
+            from .ops import flash_swa as op
         return op(q, k, v, window_size, scale, segment_idx=segment_idx, **op_kwargs)
     if k.shape[1] < window_size:
         raise ValueError("every rank's slice must be at least window_size tokens long")
-    return _sequence_parallel_local(op, q, k, v, window_size, scale, segment_idx, group, op_kwargs)
+    return _sequence_parallel_local(op, q, k, v, window_size, scale, segment_idx, group, op_kwargs, "window")
 
 
 def sequence_parallel_flash_sca(q: Tensor, k: Tensor, v: Tensor, chunk_size: int, scale: Optional[float] = None,
@@ -140,13 +188,11 @@ def sequence_parallel_flash_sca(q: Tensor, k: Tensor, v: Tensor, chunk_size: int
     ``chunk_size`` so that global chunk boundaries survive the split (the halo, exactly one chunk, then
     shifts every local key position by a multiple of the chunk size).  Per-segment reset positions are
     not supported across ranks."""
-    if op is None:
-        from .ops import flash_sca as op
     if k.shape[1] % chunk_size:
         raise ValueError("every rank's slice must be a multiple of chunk_size long")
     if op_kwargs.get("reset_chunk_pos_per_seq"):
         raise ValueError("per-segment reset positions cannot be split across ranks")
-    return _sequence_parallel_local(op, q, k, v, chunk_size, scale, segment_idx, group, op_kwargs)
+    return _sequence_parallel_local(op, q, k, v, chunk_size, scale, segment_idx, group, op_kwargs, "chunk")
 
 
 # ---- causal ring ----------------------------------------------------------------------------------
