@@ -309,7 +309,10 @@ def run_ours(args, w):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # NCCL kernels on high-priority streams: an exchange posted while an attention kernel fills the GPU
+        # then starts when the first CTA retires instead of after the last one was scheduled
+        dist.init_process_group("nccl", device_id=dev,
+                                pg_options=dist.ProcessGroupNCCL.Options(is_high_priority_stream=True))
 
     host_binding = None if args.no_numa_bind else bind_to_gpu_numa_node(local)
     if w.get("copy_probe"):
@@ -470,7 +473,7 @@ def run_ours(args, w):
             if rank == 0:
                 sharded[name] = {key: res[key] for key in (
                     "metric", "value", "unit", "ms_per_step", "scaling", "per_gpu_tflops", "single_gpu_ms",
-                    "efficiency_vs_1gpu", "launch", "eager_ms_per_step", "eager_host_enqueue_ms_per_step",
+                    "efficiency_vs_1gpu", "launch", "transport", "eager_ms_per_step", "eager_host_enqueue_ms_per_step",
                     "kernel_ms_per_step", "kernel_ms_per_step_slowest_rank",
                     "non_kernel_ms_per_step", "work_share_of_slowest_rank", "kernels")}
                 sharded[name]["workload"] = res["config"]["workload"]
@@ -811,6 +814,11 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
     from xattn_b200 import _native, parallel as P
 
     ring = bool(w.get("ring"))
+    # a two-rank communicator per pair of neighbours (a transfer inside the N-rank communicator gets a
+    # share of the channels that shrinks with N); XATTN_BENCH_NO_LINKS=1 keeps everything on the job's own
+    links = world > 2 and not os.environ.get("XATTN_BENCH_NO_LINKS")
+    if links and not P.neighbor_links_open():
+        P.open_neighbor_links()
     S, D, window = w["S"], w["D"], w.get("window", 0)
     if S % (2 * world) or S // world < window:
         raise SystemExit("sequence length must split into even slices of at least one window")
@@ -979,6 +987,8 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
         # slowest rank's kernels is exchange, copies and launch gaps.  With contiguous slices rank 0 has
         # less work than the others (its first rows see fewer keys), so it waits for them.
         "launch": launch,
+        "transport": ("NCCL send/recv on high-priority streams, " +
+                      ("one two-rank communicator per pair of neighbours" if links else "the job's communicator")),
         "eager_ms_per_step": eager_ms, "eager_host_enqueue_ms_per_step": host_ms,
         "kernel_ms_per_step": kernel_ms, "kernel_ms_per_step_slowest_rank": slowest_kernel_ms,
         "non_kernel_ms_per_step": ms - slowest_kernel_ms,

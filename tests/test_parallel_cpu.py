@@ -83,6 +83,11 @@ def _worker(rank, world, port, mode, results):
     try:
         from oracle import attention_oracle as O
         from xattn_b200 import parallel as P
+        if mode.endswith("+links"):
+            # pair communicators for the neighbours; the exchanges must take them and give the same results
+            mode = mode[:-len("+links")]
+            P.open_neighbor_links()
+            assert len(P._LINKS[None]) == (world if world > 2 else 0)
         torch.manual_seed(0)
         B, L, Hq, Hkv, D = 2, 48, 4, 2, 8
         q = torch.randn(B, L, Hq, D, dtype=torch.float64)
@@ -119,6 +124,16 @@ def _worker(rank, world, port, mode, results):
 def test_sequence_sharding_matches_unsharded_oracle(mode, world):
     if mode == "sca" and world == 3:
         world = 2      # 48 / 3 = 16 is a multiple of 8 as well, but keep one 3-rank case per family short
+    _run_ranks(mode, world)
+
+
+@pytest.mark.parametrize("mode,world", (("swa+links", 3), ("ring+links", 3), ("zigzag+links", 4)))
+def test_sequence_sharding_over_neighbor_links(mode, world):
+    """The same results when every pair of neighbours talks over a communicator of its own."""
+    _run_ranks(mode, world)
+
+
+def _run_ranks(mode, world):
     ctx = mp.get_context("spawn")
     with ctx.Manager() as manager:
         # the rendezvous port is picked, released and then bound by rank 0: if another process takes it in

@@ -41,17 +41,77 @@ def _global_rank(group, rank_in_group: int) -> int:
     return dist.get_global_rank(group, rank_in_group) if group is not None else rank_in_group
 
 
+# Pair communicators of neighbouring ranks, by the group they were opened for (None = the default group).
+_LINKS: dict = {}
+
+
+def _links_key(group):
+    return None if group is None or group is dist.group.WORLD else group
+
+
+def open_neighbor_links(group=None, high_priority: bool = True) -> None:
+    """Give every pair of neighbouring ranks of ``group`` (the ring's wrap-around pair included) a
+    communicator of its own, which the exchanges of this module then use instead of ``group``'s.
+
+    Why: inside an N-rank NCCL communicator a point-to-point transfer gets a share of the channels that
+    shrinks with N (the 17 MB halo of the window benchmark took 83 us between 2 ranks and 240 us among 8,
+    same data, same NVLink); a two-rank communicator keeps the two-rank figure at every N.
+    ``high_priority`` puts the links' NCCL kernels on high-priority streams, so that a transfer posted
+    while an attention kernel fills the GPU starts when the first of its CTAs retires, not after the last
+    one was scheduled.
+
+    Like ``torch.distributed.new_group`` this is a collective over the DEFAULT process group: every rank
+    of the job calls it, with the same arguments, before the first sharded call.  Without it everything
+    works on ``group``'s own communicator.  Two-rank groups need no links."""
+    ranks = dist.get_process_group_ranks(group if group is not None else dist.group.WORLD)
+    world = len(ranks)
+    links = {}
+    if world > 2:
+        options = None
+        if high_priority and dist.get_backend(group) == "nccl":
+            options = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        # one fixed order for all ranks (new_group is collective and blocks)
+        for a in range(world):
+            b = (a + 1) % world
+            links[frozenset((a, b))] = dist.new_group(sorted((ranks[a], ranks[b])), pg_options=options)
+    _LINKS[_links_key(group)] = links
+
+
+def neighbor_links_open(group=None) -> bool:
+    return _links_key(group) in _LINKS
+
+
+def close_neighbor_links(group=None) -> None:
+    """Forget the links of ``group`` (their communicators end with the process group teardown)."""
+    _LINKS.pop(_links_key(group), None)
+
+
 def _p2p(sends, send_to: Optional[int], recvs, recv_from: Optional[int], group):
     """One batched point-to-point step: every tensor of ``sends`` goes to ``send_to``, every buffer of
     ``recvs`` is filled from ``recv_from`` (either side may be absent at the ends of the chain).  Returns
     the pending work handles; the caller waits when it needs the data, so whatever it launches in
-    between runs beside the transfer.  Peers issue their sends and receives in the same order."""
-    ops = []
+    between runs beside the transfer.  Peers issue their sends and receives in the same order.  With
+    neighbour links open (``open_neighbor_links``) the sends and the receives go out as one batch each on
+    the communicator of their pair."""
+    rank = dist.get_rank(group)
+    links = _LINKS.get(_links_key(group)) or {}
+    out_link = links.get(frozenset((rank, send_to))) if send_to is not None else None
+    in_link = links.get(frozenset((rank, recv_from))) if recv_from is not None else None
+    send_ops, recv_ops = [], []
     if send_to is not None:
-        ops += [dist.P2POp(dist.isend, t.contiguous(), _global_rank(group, send_to), group) for t in sends]
+        peer = _global_rank(group, send_to)
+        send_ops = [dist.P2POp(dist.isend, t.contiguous(), peer, group if out_link is None else out_link) for t in sends]
     if recv_from is not None:
-        ops += [dist.P2POp(dist.irecv, t, _global_rank(group, recv_from), group) for t in recvs]
-    return dist.batch_isend_irecv(ops) if ops else []
+        peer = _global_rank(group, recv_from)
+        recv_ops = [dist.P2POp(dist.irecv, t, peer, group if in_link is None else in_link) for t in recvs]
+    if (out_link is None and in_link is None) or out_link is in_link:
+        ops = send_ops + recv_ops
+        return dist.batch_isend_irecv(ops) if ops else []
+    works = []
+    for ops in (send_ops, recv_ops):
+        if ops:
+            works += dist.batch_isend_irecv(ops)
+    return works
 
 
 def _wait(works) -> None:
@@ -283,11 +343,7 @@ class _RingCausal(torch.autograd.Function):
             if t + 1 < world:
                 # prefetch the next block while this one is computed
                 nxt_k, nxt_v = torch.empty_like(blk_k), torch.empty_like(blk_v)
-                ops = [dist.P2POp(dist.isend, blk_k, _global_rank(group, send_to), group),
-                       dist.P2POp(dist.irecv, nxt_k, _global_rank(group, recv_from), group),
-                       dist.P2POp(dist.isend, blk_v, _global_rank(group, send_to), group),
-                       dist.P2POp(dist.irecv, nxt_v, _global_rank(group, recv_from), group)]
-                pending = dist.batch_isend_irecv(ops)
+                pending = _p2p([blk_k, blk_v], send_to, [nxt_k, nxt_v], recv_from, group)
             if zigzag and t > 0:
                 if t <= rank:   # an earlier rank's block: its first chunk lies before both local chunks
                     y_t, lse_t = kernels.forward(q, blk_k[:, :half], blk_v[:, :half], scale, causal=False)
@@ -323,7 +379,6 @@ class _RingCausal(torch.autograd.Function):
         # is only needed once this step's own contribution exists.
         wide = torch.float64 if q.dtype == torch.float64 else torch.float32
         dq = torch.zeros(q.shape, dtype=wide, device=q.device)
-        nxt_rank, prv_rank = _global_rank(group, send_to), _global_rank(group, recv_from)
         acc_in = None          # (works, dk, dv): the accumulator of the current block, arriving
         sent = []              # keep buffers of sends in flight alive until their work is done
         for t in range(world):
@@ -331,9 +386,7 @@ class _RingCausal(torch.autograd.Function):
             kv_works = []
             if t + 1 < world:
                 nxt_k, nxt_v = torch.empty_like(blk_k), torch.empty_like(blk_v)
-                kv_works = dist.batch_isend_irecv([
-                    dist.P2POp(dist.isend, blk_k, nxt_rank, group), dist.P2POp(dist.irecv, nxt_k, prv_rank, group),
-                    dist.P2POp(dist.isend, blk_v, nxt_rank, group), dist.P2POp(dist.irecv, nxt_v, prv_rank, group)])
+                kv_works = _p2p([blk_k, blk_v], send_to, [nxt_k, nxt_v], recv_from, group)
             dk_t = dv_t = None
             rows = slice(None)
             if zigzag and t > 0:
@@ -361,9 +414,7 @@ class _RingCausal(torch.autograd.Function):
                 dv_acc[:, rows] += dv_t
             # pass the accumulator on (the last step brings it home) and ask for the next one
             recv_dk, recv_dv = torch.empty_like(dk_acc), torch.empty_like(dv_acc)
-            works = dist.batch_isend_irecv([
-                dist.P2POp(dist.isend, dk_acc, nxt_rank, group), dist.P2POp(dist.irecv, recv_dk, prv_rank, group),
-                dist.P2POp(dist.isend, dv_acc, nxt_rank, group), dist.P2POp(dist.irecv, recv_dv, prv_rank, group)])
+            works = _p2p([dk_acc, dv_acc], send_to, [recv_dk, recv_dv], recv_from, group)
             sent.append((dk_acc, dv_acc))
             acc_in = (works, recv_dk, recv_dv)
             _wait(kv_works)
