@@ -311,6 +311,24 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
   const int h = kvh * G + (rem % G);
   const int b = bk / p.Hkv;
 
+  // This thread's half of its Q row (element-wise warps: thread = query row, hf = column half) is
+  // requested from global memory before anything else: it goes to TMEM as the A operand of S = Q K^T,
+  // every CTA starts with the chain  row load -> TMEM store -> first S product, and the set-up below
+  // (barriers, TMEM allocation, the CTA-wide barrier) fits inside the load's latency.
+  constexpr int kQRegs = HD / 4;              // packed 16-bit pairs per half row
+  uint32_t q_pre[kQRegs];
+  if (warp < 8) {
+    const int hf = warp >> 2, row = qt * kBlockM + (tid & 127);
+    const T* src = reinterpret_cast<const T*>(p.q) + b * p.q_sb + (row < p.Lq ? row : 0) * p.q_sl + h * p.q_sh;
+#pragma unroll
+    for (int c = 0; c < kQRegs; c += 4) {
+      const int e = (hf * kQRegs + c) * 2;     // first element of this 16-byte chunk
+      uint4 u = make_uint4(0, 0, 0, 0);
+      if (row < p.Lq && e < p.D) u = *reinterpret_cast<const uint4*>(src + e);
+      q_pre[c] = u.x; q_pre[c + 1] = u.y; q_pre[c + 2] = u.z; q_pre[c + 3] = u.w;
+    }
+  }
+
   if (warp == 9 && lane == 0) {
     // The dO tile needs nothing but the block index: its load starts before anything else, the
     // mask plan's tile summary included (its barrier is initialised here, by its first user).
@@ -333,12 +351,27 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
     }
   }
   const int iters = n_hi - n_lo;
+  // the first K and V tiles are requested as soon as the tile summary says which they are, before
+  // the CTA's set-up barrier
+  if (warp == 9 && lane == 0) {
+    for (int i = 0; i < kKStages; ++i) mbar_init(&s.k_full[i], 1);
+    for (int i = 0; i < 2; ++i) mbar_init(&s.v_full[i], 1);
+    fence_mbar_init();
+    if (iters > 0) {
+      mbar_arrive_expect_tx(&s.k_full[0], ((p.D + 63) / 64) * kKvBox);
+      for (int bx = 0; bx < (p.D + 63) / 64; ++bx)
+        tma_load_4d(s.k[0] + bx * kKvBox, &tm_k, &s.k_full[0], bx * 64, kvh, n_lo * BN, b);
+      mbar_arrive_expect_tx(&s.v_full[0], ((p.V + 63) / 64) * kKvBox);
+      for (int bx = 0; bx < (p.V + 63) / 64; ++bx)
+        tma_load_4d(s.v[0] + bx * kKvBox, &tm_v, &s.v_full[0], bx * 64, kvh, n_lo * BN, b);
+    }
+  }
 
   if (tid == 0) {
     s.abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 2 : 0;
     mbar_init(&s.q_ready, 8);
-    for (int i = 0; i < kKStages; ++i) { mbar_init(&s.k_full[i], 1); mbar_init(&s.k_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s.v_full[i], 1); mbar_init(&s.v_empty[i], 1); }
+    for (int i = 0; i < kKStages; ++i) mbar_init(&s.k_empty[i], 1);     // k_full, v_full: by the TMA thread, above
+    for (int i = 0; i < 2; ++i) mbar_init(&s.v_empty[i], 1);
     mbar_init(&s.s_full, 1);
     mbar_init(&s.s_free, 8);
     mbar_init(&s.dp_full, 1);
@@ -390,25 +423,16 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
           *reinterpret_cast<uint4*>(dq_row + c) = make_uint4(0, 0, 0, 0);
       }
     } else {
-      // stage this thread's half of the Q row in TMEM: packed pairs, row = lane
-      auto stage_row = [&](const T* src, int width, uint32_t col) {
-        constexpr int kCols = HD / 4;           // packed columns per half
-        constexpr int kStep = kCols < 32 ? kCols : 32;
+      // this thread's half of the Q row (requested at the top of the kernel) goes to TMEM: packed
+      // pairs, row = lane
+      {
+        constexpr int kStep = kQRegs < 32 ? kQRegs : 32;
 #pragma unroll
-        for (int c0 = 0; c0 < kCols; c0 += kStep) {
-          uint32_t w[kStep];
-#pragma unroll
-          for (int c = 0; c < kStep; c += 4) {
-            const int e = (hf * kCols + c0 + c) * 2;   // first element of this 16-byte chunk
-            uint4 u = make_uint4(0, 0, 0, 0);
-            if (live && e < width) u = *reinterpret_cast<const uint4*>(src + e);
-            w[c] = u.x; w[c + 1] = u.y; w[c + 2] = u.z; w[c + 3] = u.w;
-          }
-          if (kStep == 32) tmem_st_x32(tmem + lane_off + col + hf * kCols + c0, w);
-          else tmem_st_x16(tmem + lane_off + col + hf * kCols + c0, w);
+        for (int c0 = 0; c0 < kQRegs; c0 += kStep) {
+          if (kStep == 32) tmem_st_x32(tmem + lane_off + cQ + hf * kQRegs + c0, q_pre + c0);
+          else tmem_st_x16(tmem + lane_off + cQ + hf * kQRegs + c0, q_pre + c0);
         }
-      };
-      stage_row(reinterpret_cast<const T*>(p.q) + b * p.q_sb + (live ? row : 0) * p.q_sl + h * p.q_sh, p.D, cQ);
+      }
       tc_wait_st();
       tc_fence_before();
       mbar_arrive_warp(&s.q_ready);
@@ -626,7 +650,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
   } else if (warp == 9 && lane == 0 && iters > 0) {
     // ------------------------------ TMA producer ------------------------------
     bool ok = true;
-    for (int i = 0; i < iters && ok; ++i) {
+    for (int i = 1; i < iters && ok; ++i) {       // tile 0 was requested before the set-up barrier
       const int st = i & 1, ks = i % kKStages, n = n_lo + i;
       if (i >= kKStages) ok = mbar_wait(ctx, &s.k_empty[ks], ((i / kKStages) - 1) & 1, 70);
       if (!ok) break;
@@ -644,6 +668,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_do, const __grid_constant__
   if ((dead || iters == 0) && warp == 9 && lane == 0) {
     // the dO load was issued before anything was known: let it land (bounded)
     for (int i = 0; i < (1 << 20) && !mbar_try_wait(&s.do_full, 0); ++i) { }
+    if (iters > 0) {
+      for (int i = 0; i < (1 << 20) && !mbar_try_wait(&s.k_full[0], 0); ++i) { }
+      for (int i = 0; i < (1 << 20) && !mbar_try_wait(&s.v_full[0], 0); ++i) { }
+    }
   }
   tc_fence_before();
   __syncthreads();

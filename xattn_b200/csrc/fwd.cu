@@ -4,7 +4,8 @@
 // visible-key intervals touch.  Roles (XB_FWD_PARTS = 2: 16 warps):
 //   warps 0-7         two softmax warpgroups: thread = (query row, half of the key tile's 128
 //                     columns); the parts exchange their row maxima through shared memory
-//   warps 8-11        correction + epilogue warpgroup (rescales O in TMEM, writes y and lse)
+//   warps 8-11        correction warpgroup (rescales O in TMEM); the epilogue (y and lse) is shared by
+//                     warps 0-11
 //   warp 12           tcgen05.mma issuer of O += P V (one thread)
 //   warp 13           TMA producer (one thread); also owns the TMEM allocation
 //   warp 14           tcgen05.mma issuer of S = Q K^T (one thread): an issuing thread stalls while
@@ -73,7 +74,7 @@ struct FwdSmem {
   uint64_t k_full[kKStages], k_empty[kKStages];
   uint64_t v_full[kVStages], v_empty[kVStages];
   uint64_t s_full[2], s_free[2], p_full[2], p_free[2], max_x[4];
-  uint64_t o_ready, pv_done, corr_full, final_full, y_staged;
+  uint64_t o_ready, pv_done, corr_full, final_full, y_staged, o_final;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -153,12 +154,25 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     n_hi = min(n_lo + per, n_hi);
   }
   const int iters = n_hi - n_lo;
+  // The first K tiles are requested as soon as the tile summary says which they are, before the
+  // CTA's set-up barrier: tile summary -> K load -> first S product is the chain every CTA starts
+  // with, and with short key ranges (packed segments) it is a good part of the CTA's life.
+  constexpr int kEarlyK = kKStages < 2 ? kKStages : 2;
+  if (warp == kTmaWarp && lane == 0) {
+    for (int i = 0; i < kKStages; ++i) mbar_init(&s.k_full[i], 1);
+    fence_mbar_init();
+    for (int i = 0; i < kEarlyK && i < iters; ++i) {
+      mbar_arrive_expect_tx(&s.k_full[i], ((p.D + 63) / 64) * kBoxBytes);
+      for (int bx = 0; bx < (p.D + 63) / 64; ++bx)
+        tma_load_4d(s.k[i] + bx * kBoxBytes, &tm_k, &s.k_full[i], bx * 64, kvh, (n_lo + i) * kBlockN, b);
+    }
+  }
 
   // ---- set-up ----------------------------------------------------------------
   if (tid == 0) {
     // an earlier CTA gave up: do not pile on
     s.abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 2 : 0;
-    for (int i = 0; i < kKStages; ++i) { mbar_init(&s.k_full[i], 1); mbar_init(&s.k_empty[i], 1); }
+    for (int i = 0; i < kKStages; ++i) mbar_init(&s.k_empty[i], 1);       // k_full: by the TMA thread, above
     for (int i = 0; i < kVStages; ++i) { mbar_init(&s.v_full[i], 1); mbar_init(&s.v_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.s_full[i], 1); mbar_init(&s.p_full[i], 4 * kParts);
@@ -172,7 +186,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     mbar_init(&s.pv_done, 1);
     mbar_init(&s.corr_full, 4);
     mbar_init(&s.final_full, 4 * kParts);
-    mbar_init(&s.y_staged, 4);
+    mbar_init(&s.y_staged, 4 * (kParts + 1));
+    mbar_init(&s.o_final, 1);               // the last O += P V product has run
     fence_mbar_init();
   }
   if (warp == kTmaWarp) {
@@ -200,6 +215,100 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     static_assert(kParts != 4 || 512 * (88 - 80) <= 128 * (80 - 40), "register budget");
     if (warp < 16) setmaxnreg_inc<88>(); else if (warp >= 20) setmaxnreg_dec<40>();
   }
+
+  // Epilogue: y = O / l, lse = ln2 * (m * c + log2 l).  Shared by all warpgroups that worked on the
+  // tile (softmax parts 0 .. kParts-1, correction = kParts): each converts every (kParts+1)-th
+  // 16-column chunk of the rows' output.  The conversion is a chain of latencies (TMEM load, convert,
+  // shared-memory store) that four warps alone do not hide: in-kernel cycle counters gave 1 300 clk
+  // for the staging of a 128 x 128 tile by three warpgroups.  A lambda, so that every role
+  // instantiates it inside its own register allotment (a code path shared across the roles would
+  // be compiled for the smallest of them).
+  auto epilogue = [&](const int part, bool ok) {
+    const int r = tid & 127;
+    const int row = DEC ? (r >> p.g_shift) : qt * kBlockM + r;
+    const int hr = DEC ? h + (r & (G - 1)) : h;       // this row's query head
+    const bool live = row < p.Lq;
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    if (ok) ok = mbar_wait(ctx, &s.final_full, 0, 24);
+    // (not pv_done: a warp that has not followed that barrier's phases cannot tell the last product
+    // from the one two before it)
+    if (ok && iters > 0) ok = mbar_wait(ctx, &s.o_final, 0, 26);
+    if (ok && iters == 0) ok = mbar_wait(ctx, &s.q_full, 0, 28);   // the Q load has landed: its buffer is reused below
+    if (ok) {
+      tc_fence_after();
+      float l = 0.f;
+#pragma unroll
+      for (int o = 0; o < kParts; ++o) l += s.final_l[o][r];
+      const float m = s.final_m[r];
+      const bool has = l > 0.f && iters > 0;
+      float inv = 0.f;
+      if (has) inv = HP ? __frcp_rn(l) : __fdividef(1.f, l);
+      if (live && part == kParts) {
+        const float c_log2 = p.scale * 1.4426950408889634f;
+        float* lse_out = DEC ? p.part_lse + (size_t)split * p.B * p.Hq * p.Lq : p.lse;
+        lse_out[((size_t)b * p.Hq + hr) * p.Lq + row] =
+            has ? (m * c_log2 + log2f(l)) * 0.6931471805599453f : -INFINITY;
+        if (HP && !DEC && p.anchor) {
+          float bs = -INFINITY;
+          int bi = -1;
+          if (iters > 0) {
+#pragma unroll
+            for (int o = 0; o < kParts; ++o) {
+              const float v = s.best_s[o][r];
+              const int i = s.best_i[o][r];
+              if (i >= 0 && (v > bs || (v == bs && i < bi))) { bs = v; bi = i; }
+            }
+          }
+          p.anchor[((size_t)b * p.Hq + hr) * p.Lq + row] = bi;
+        }
+      }
+      // y leaves through shared memory and bulk tensor stores (the Q tile's buffer is free by now:
+      // every S product has run): coalesced, clipped to the tensor by the hardware, and the CTA
+      // does not have to wait for the writes themselves.  Layout: 64-column boxes of 128-byte
+      // rows in the 128-byte swizzle (16-byte chunk c of row r sits at chunk c ^ (r & 7)).
+      const uint32_t t_o = tmem + lane_off + cO;
+      float* ys_base = DEC ? p.part_y + (size_t)split * p.B * p.Lq * p.Hq * p.V : p.y_state;
+      float* ys_row = ys_base ? ys_base + (((size_t)b * p.Lq + (live ? row : 0)) * p.Hq + hr) * p.V : nullptr;
+      for (int c0 = 16 * part; c0 < v_pad; c0 += 16 * (kParts + 1)) {
+        uint32_t o[16];
+        if (iters > 0) {
+          tmem_ld_x16(t_o + c0, o);   // warp-collective: executed by all lanes
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) o[c] = 0u;
+        }
+        uint8_t* box = s.q + (c0 >> 6) * kBoxBytes + r * 128;
+#pragma unroll
+        for (int c = 0; c < 16; c += 8) {
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[c + e]) * inv;
+          uint4 pk;
+          pk.x = Pack2<T>::pack(f[0], f[1]);
+          pk.y = Pack2<T>::pack(f[2], f[3]);
+          pk.z = Pack2<T>::pack(f[4], f[5]);
+          pk.w = Pack2<T>::pack(f[6], f[7]);
+          const int chunk = ((c0 & 63) + c) >> 3;
+          if (!DEC) *reinterpret_cast<uint4*>(box + ((chunk ^ (r & 7)) << 4)) = pk;
+          if (ys_row && live && c0 + c < p.V) {
+            *reinterpret_cast<float4*>(ys_row + c0 + c) = make_float4(f[0], f[1], f[2], f[3]);
+            *reinterpret_cast<float4*>(ys_row + c0 + c + 4) = make_float4(f[4], f[5], f[6], f[7]);
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive_warp(&s.y_staged);
+      if (!DEC && warp == kCorrWarp && lane == 0) {
+        ok = mbar_wait(ctx, &s.y_staged, 0, 27);
+        if (ok) {
+          for (int bx = 0; bx < nbox_v; ++bx) tma_store_4d(&tm_y, s.q + bx * kBoxBytes, bx * 64, h, qt * kBlockM, b);
+          tma_store_commit();
+          tma_store_wait_read_all();
+        }
+      }
+    }
+  };
 
   if (dead) {
     // nothing to do
@@ -356,12 +465,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     if (hf == 0) s.final_m[r] = m;
     if (HP) { s.best_s[hf][r] = best; s.best_i[hf][r] = best_idx; }
     mbar_arrive_warp(&s.final_full);
+    epilogue(hf, ok);
   } else if (warp < kCorrWarp + 4) {
     // ======================= correction + epilogue warpgroup =======================
     const int r = tid & 127;
-    const int row = DEC ? (r >> p.g_shift) : qt * kBlockM + r;
-    const int hr = DEC ? h + (r & (G - 1)) : h;       // this row's query head
-    const bool live = row < p.Lq;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
     for (int j = 1; j < iters && ok; ++j) {
@@ -386,84 +493,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       tc_fence_before();
       mbar_arrive_warp(&s.o_ready);
     }
-    // epilogue: y = O / l, lse = ln2 * (m * c + log2 l)
-    if (ok) ok = mbar_wait(ctx, &s.final_full, 0, 24);
-    if (ok && iters > 0) ok = mbar_wait(ctx, &s.pv_done, (iters - 1) & 1, 26);
-    if (ok && iters == 0) ok = mbar_wait(ctx, &s.q_full, 0, 28);   // the Q load has landed: its buffer is reused below
-    if (ok) {
-      tc_fence_after();
-      float l = 0.f;
-#pragma unroll
-      for (int o = 0; o < kParts; ++o) l += s.final_l[o][r];
-      const float m = s.final_m[r];
-      const bool has = l > 0.f && iters > 0;
-      float inv = 0.f;
-      if (has) inv = HP ? __frcp_rn(l) : __fdividef(1.f, l);
-      if (live) {
-        const float c_log2 = p.scale * 1.4426950408889634f;
-        float* lse_out = DEC ? p.part_lse + (size_t)split * p.B * p.Hq * p.Lq : p.lse;
-        lse_out[((size_t)b * p.Hq + hr) * p.Lq + row] =
-            has ? (m * c_log2 + log2f(l)) * 0.6931471805599453f : -INFINITY;
-        if (HP && !DEC && p.anchor) {
-          float bs = -INFINITY;
-          int bi = -1;
-          if (iters > 0) {
-#pragma unroll
-            for (int o = 0; o < kParts; ++o) {
-              const float v = s.best_s[o][r];
-              const int i = s.best_i[o][r];
-              if (i >= 0 && (v > bs || (v == bs && i < bi))) { bs = v; bi = i; }
-            }
-          }
-          p.anchor[((size_t)b * p.Hq + hr) * p.Lq + row] = bi;
-        }
-      }
-      // y leaves through shared memory and bulk tensor stores (the Q tile's buffer is free by now:
-      // every S product has run): coalesced, clipped to the tensor by the hardware, and the CTA
-      // does not have to wait for the writes themselves.  Layout: 64-column boxes of 128-byte
-      // rows in the 128-byte swizzle (16-byte chunk c of row r sits at chunk c ^ (r & 7)).
-      const uint32_t t_o = tmem + lane_off + cO;
-      float* ys_base = DEC ? p.part_y + (size_t)split * p.B * p.Lq * p.Hq * p.V : p.y_state;
-      float* ys_row = ys_base ? ys_base + (((size_t)b * p.Lq + (live ? row : 0)) * p.Hq + hr) * p.V : nullptr;
-      for (int c0 = 0; c0 < v_pad; c0 += 32) {
-        uint32_t o[32];
-        if (iters > 0) {
-          tmem_ld_x32(t_o + c0, o);   // warp-collective: executed by all lanes
-          tc_wait_ld();
-        } else {
-#pragma unroll
-          for (int c = 0; c < 32; ++c) o[c] = 0u;
-        }
-        uint8_t* box = s.q + (c0 >> 6) * kBoxBytes + r * 128;
-#pragma unroll
-        for (int c = 0; c < 32; c += 8) {
-          float f[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[c + e]) * inv;
-          uint4 pk;
-          pk.x = Pack2<T>::pack(f[0], f[1]);
-          pk.y = Pack2<T>::pack(f[2], f[3]);
-          pk.z = Pack2<T>::pack(f[4], f[5]);
-          pk.w = Pack2<T>::pack(f[6], f[7]);
-          const int chunk = ((c0 & 63) + c) >> 3;
-          if (!DEC) *reinterpret_cast<uint4*>(box + ((chunk ^ (r & 7)) << 4)) = pk;
-          if (ys_row && live && c0 + c < p.V) {
-            *reinterpret_cast<float4*>(ys_row + c0 + c) = make_float4(f[0], f[1], f[2], f[3]);
-            *reinterpret_cast<float4*>(ys_row + c0 + c + 4) = make_float4(f[4], f[5], f[6], f[7]);
-          }
-        }
-      }
-      fence_proxy_async_smem();
-      mbar_arrive_warp(&s.y_staged);
-      if (!DEC && warp == kCorrWarp && lane == 0) {
-        ok = mbar_wait(ctx, &s.y_staged, 0, 27);
-        if (ok) {
-          for (int bx = 0; bx < nbox_v; ++bx) tma_store_4d(&tm_y, s.q + bx * kBoxBytes, bx * 64, h, qt * kBlockM, b);
-          tma_store_commit();
-          tma_store_wait_read_all();
-        }
-      }
-    }
+    epilogue(kParts, ok);
   } else if (warp == kQkWarp && lane == 0 && iters > 0) {
     // ------------------------------ S = Q K^T issuer ------------------------------
     const uint32_t idesc_qk = make_idesc(kBlockM, kBlockN, kFormat, 0, 0);
@@ -508,13 +538,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       umma_commit(&s.v_empty[vs]);
       umma_commit(&s.p_free[n & 1]);
       if (kAliasP) umma_commit(&s.s_free[n & 1]);
+      if (n == iters - 1) umma_commit(&s.o_final);
     }
   } else if (warp == kTmaWarp && lane == 0 && iters > 0) {
     // ------------------------------ TMA producer ------------------------------
     bool ok = true;
     // K runs kLA tiles ahead of V, the order in which the two products consume them
     for (int i = 0; i < iters + kLA && ok; ++i) {
-      if (i < iters) {
+      if (i >= kEarlyK && i < iters) {
         const int st = i % kKStages;
         if (i >= kKStages) ok = mbar_wait(ctx, &s.k_empty[st], ((i / kKStages) - 1) & 1, 40);
         if (!ok) break;
@@ -536,8 +567,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
   // ---- tail -----------------------------------------------------------------
   if (dead && warp == kTmaWarp && lane == 0) {
-    // the Q load was issued before the abort flag was read: let it land (bounded)
+    // the Q and first K loads were issued before the abort flag was read: let them land (bounded)
     for (int i = 0; i < (1 << 20) && !mbar_try_wait(&s.q_full, 0); ++i) { }
+    for (int t = 0; t < kEarlyK && t < iters; ++t)
+      for (int i = 0; i < (1 << 20) && !mbar_try_wait(&s.k_full[t], 0); ++i) { }
   }
   tc_fence_before();
   __syncthreads();
