@@ -126,7 +126,7 @@ def make_host_inputs(w, seed):
         for b in range(B):
             pos, seg = 0, 0
             while pos < S:
-                length = int(torch.randint(512, 4097, (1,), generator=g))
+                length = int(torch.randint(w.get("seg_lo", 512), w.get("seg_hi", 4096) + 1, (1,), generator=g))
                 ids[b, pos:pos + length] = seg
                 pos += length
                 seg += 1
@@ -1027,6 +1027,9 @@ def main():
     ap.add_argument("--workload", default="causal_c2", choices=sorted(WORKLOADS))
     ap.add_argument("--level", type=int, default=0, choices=(0, 1),
                     help="high_precision_level (default 0; the causal, sca_c4 and softdelta workloads take 1 too)")
+    ap.add_argument("--segment-lengths", default=None, metavar="LO,HI",
+                    help="packed causal workloads: draw segment lengths ~U[LO,HI] instead of the headline's 512,4096 "
+                         "(LO = HI gives equal segments)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--no-numa-bind", action="store_true",
@@ -1035,6 +1038,11 @@ def main():
                     help="with more than one GPU: skip the sequence-sharded workloads after the headline measurement")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
+    if args.segment_lengths:
+        lo, hi = (int(x) for x in args.segment_lengths.split(","))
+        if not w.get("segments") or lo < 1 or hi < lo:
+            raise SystemExit("--segment-lengths needs a packed causal workload and 1 <= LO <= HI")
+        w = dict(w, seg_lo=lo, seg_hi=hi, text=w["text"].replace("~U[512,4096]", f"~U[{lo},{hi}]"))
     if args.impl == "reference" and (w.get("decode") or w.get("other") or w.get("copy_probe") or w["S"] > 8192):
         print(json.dumps({"impl": "reference", "unavailable": "the CPU arm runs the causal S=8192 workloads: one "
                           "(batch row, head) slice of a 32768-token sequence needs 4.3 GB per score matrix in fp32"}))
