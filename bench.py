@@ -475,7 +475,7 @@ def run_ours(args, w):
                     "metric", "value", "unit", "ms_per_step", "scaling", "per_gpu_tflops", "single_gpu_ms",
                     "efficiency_vs_1gpu", "launch", "transport", "eager_ms_per_step", "eager_host_enqueue_ms_per_step",
                     "kernel_ms_per_step", "kernel_ms_per_step_slowest_rank",
-                    "non_kernel_ms_per_step", "work_share_of_slowest_rank", "kernels")}
+                    "non_kernel_ms_per_step", "work_share_of_slowest_rank", "slice_rows", "kernels")}
                 sharded[name]["workload"] = res["config"]["workload"]
 
     if rank == 0:
@@ -823,10 +823,24 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
     if S % (2 * world) or S // world < window:
         raise SystemExit("sequence length must split into even slices of at least one window")
     n = S // world
+    # Window workload: contiguous slices with about equal numbers of visible pairs (the first `window` rows
+    # of the sequence see fewer keys, so with equal slices rank 0 has less to do than everybody else),
+    # boundaries on multiples of 128 rows, every slice at least one window long (the halo comes from the
+    # previous rank alone).  Where that cannot be had (eight ranks: a slice IS one window) the slices are equal.
+    bounds = [r * n for r in range(world + 1)]
+    if not ring and world > 1:
+        cum, acc = [], 0
+        for i in range(S):
+            acc += min(i, window) + 1
+            cum.append(acc)
+        import bisect
+        cand = [0] + [min(S, (bisect.bisect_left(cum, acc * r / world) + 1 + 64) // 128 * 128) for r in range(1, world)] + [S]
+        if all(b - a >= max(window, 128) for a, b in zip(cand, cand[1:])):
+            bounds = cand
     g = torch.Generator().manual_seed(2)
     draw = lambda *shape: torch.randn(shape, generator=g, dtype=torch.float32).to(torch.bfloat16)
     q, k, v, dy = draw(1, S, w["Hq"], D), draw(1, S, w["Hkv"], D), draw(1, S, w["Hkv"], D), draw(1, S, w["Hq"], D)
-    sl = P.zigzag_indices(S, rank, world) if ring else slice(rank * n, (rank + 1) * n)
+    sl = P.zigzag_indices(S, rank, world) if ring else slice(bounds[rank], bounds[rank + 1])
     pinned = [t[:, sl].contiguous().pin_memory() for t in (q, k, v, dy)]
     ql, kl, vl, dyl = (t.to(dev) for t in pinned)
     pairs = w["Hq"] * (S * (S + 1) // 2 if ring else sum(min(i, window) + 1 for i in range(S)))   # whole job
@@ -977,8 +991,8 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
                    "parallelism": (f"sequence split over {world} GPU(s) in the zig-zag layout; ring of K/V blocks "
                                    "(NCCL send/recv), partial outputs merged by lse, dK/dV travel home with their block"
                                    if ring else
-                                   f"sequence split over {world} GPU(s); K/V halo of {window} tokens from the "
-                                   "previous rank (NCCL send/recv), halo gradients sent back")},
+                                   f"sequence split over {world} GPU(s) in contiguous slices of about equal work; K/V "
+                                   f"halo of {window} tokens from the previous rank (NCCL send/recv), halo gradients sent back")},
         "per_gpu_tflops": flops_step / ms * 1e-9 / world,
         # strong scaling: time of the unsharded sequence on one GPU over N times the sharded time
         "single_gpu_ms": single_ms,
@@ -993,8 +1007,9 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
         "kernel_ms_per_step": kernel_ms, "kernel_ms_per_step_slowest_rank": slowest_kernel_ms,
         "non_kernel_ms_per_step": ms - slowest_kernel_ms,
         "work_share_of_slowest_rank": (1.0 / world if ring else
-                                       max(sum(min(i, window) + 1 for i in range(r * n, (r + 1) * n))
+                                       max(sum(min(i, window) + 1 for i in range(bounds[r], bounds[r + 1]))
                                            for r in range(world)) * w["Hq"] / pairs),
+        "slice_rows": None if ring else [b - a for a, b in zip(bounds, bounds[1:])],
         "e2e": None if not e2e_steps else {"value": flops_step / e2e_ms * 1e-9, "unit": "TFLOP/s",
                                            "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                                            "d2h_bytes_per_step": d2h, "steps": e2e_steps},

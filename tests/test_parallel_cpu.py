@@ -88,6 +88,9 @@ def _worker(rank, world, port, mode, results):
             mode = mode[:-len("+links")]
             P.open_neighbor_links()
             assert len(P._LINKS[None]) == (world if world > 2 else 0)
+        uneven = mode == "swa-uneven"
+        if uneven:
+            mode = "swa"
         torch.manual_seed(0)
         B, L, Hq, Hkv, D = 2, 48, 4, 2, 8
         q = torch.randn(B, L, Hq, D, dtype=torch.float64)
@@ -97,6 +100,11 @@ def _worker(rank, world, port, mode, results):
         ids = (torch.arange(L) // 19).expand(B, -1).contiguous() if mode in ("swa", "sca") else None
         n = L // world
         sl = P.zigzag_indices(L, rank, world) if mode == "zigzag" else slice(rank * n, (rank + 1) * n)
+        if uneven:
+            # slices of different lengths (a caller balancing the work of a window workload): only the halo
+            # has to have the same size on both sides of an exchange
+            cuts = [0, 21, 34, L][:world] + [L]
+            sl = slice(cuts[rank], cuts[rank + 1])
         ql, kl, vl = (t[:, sl].clone().requires_grad_() for t in (q, k, v))
         if mode == "swa":
             y = P.sequence_parallel_flash_swa(ql, kl, vl, 7, segment_idx=ids[:, sl], op=_oracle_op("window"))
@@ -124,6 +132,11 @@ def _worker(rank, world, port, mode, results):
 def test_sequence_sharding_matches_unsharded_oracle(mode, world):
     if mode == "sca" and world == 3:
         world = 2      # 48 / 3 = 16 is a multiple of 8 as well, but keep one 3-rank case per family short
+    _run_ranks(mode, world)
+
+
+@pytest.mark.parametrize("mode,world", (("swa-uneven", 3),))
+def test_window_sharding_with_slices_of_different_lengths(mode, world):
     _run_ranks(mode, world)
 
 
