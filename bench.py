@@ -469,7 +469,9 @@ def run_ours(args, w):
         torch.cuda.empty_cache()
         sharded = {}
         for name in ("swa_c3", "ring_causal"):
-            res = measure_sharded(args, WORKLOADS[name], world, rank, dev, with_e2e=False, steps=max(3, min(args.steps, 10)))
+            # the ring comes second: the window workload's chain exchanges have connected the neighbour links by then
+            res = measure_sharded(args, WORKLOADS[name], world, rank, dev, with_e2e=False, steps=max(3, min(args.steps, 10)),
+                                  ring_links=(name == "ring_causal"))
             if rank == 0:
                 sharded[name] = {key: res[key] for key in (
                     "metric", "value", "unit", "ms_per_step", "scaling", "per_gpu_tflops", "single_gpu_ms",
@@ -804,7 +806,7 @@ def run_other(args, w, world, rank, dev):
         dist.destroy_process_group()
 
 
-def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
+def measure_sharded(args, w, world, rank, dev, with_e2e, steps, ring_links=False):
     """One sequence of S tokens split over the ranks of the current process group, total work fixed:
     configs[2] (sliding window, contiguous slices, K/V halo exchange) or the causal ring (zig-zag
     slices).  Returns the result dictionary on rank 0 (None elsewhere).  Rank 0 also times the same
@@ -826,7 +828,8 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
     # Window workload: contiguous slices with about equal numbers of visible pairs (the first `window` rows
     # of the sequence see fewer keys, so with equal slices rank 0 has less to do than everybody else),
     # boundaries on multiples of 128 rows, every slice at least one window long (the halo comes from the
-    # previous rank alone).  Where that cannot be had (eight ranks: a slice IS one window) the slices are equal.
+    # previous rank alone).  Where that cannot be had (eight ranks: an equal slice IS one window) the slices
+    # stay equal.
     bounds = [r * n for r in range(world + 1)]
     if not ring and world > 1:
         cum, acc = [], 0
@@ -835,8 +838,12 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
             cum.append(acc)
         import bisect
         cand = [0] + [min(S, (bisect.bisect_left(cum, acc * r / world) + 1 + 64) // 128 * 128) for r in range(1, world)] + [S]
-        if all(b - a >= max(window, 128) for a, b in zip(cand, cand[1:])):
+        # XATTN_BENCH_EQUAL_SLICES=1 keeps the slices equal; XATTN_BENCH_SHORT_SLICES=1 also accepts slices down to
+        # half a window, whose halo then reaches two ranks back (slice_lengths below)
+        shortest = window // 2 if os.environ.get("XATTN_BENCH_SHORT_SLICES") else window
+        if all(b - a >= max(shortest, 128) for a, b in zip(cand, cand[1:])) and not os.environ.get("XATTN_BENCH_EQUAL_SLICES"):
             bounds = cand
+    lengths = [b - a for a, b in zip(bounds, bounds[1:])]
     g = torch.Generator().manual_seed(2)
     draw = lambda *shape: torch.randn(shape, generator=g, dtype=torch.float32).to(torch.bfloat16)
     q, k, v, dy = draw(1, S, w["Hq"], D), draw(1, S, w["Hkv"], D), draw(1, S, w["Hkv"], D), draw(1, S, w["Hq"], D)
@@ -848,7 +855,8 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
 
     def step(a, b, c, d):
         a, b, c = (t.detach().requires_grad_() for t in (a, b, c))
-        y = P.ring_causal_flash_attn(a, b, c, layout="zigzag") if ring else P.sequence_parallel_flash_swa(a, b, c, window)
+        y = (P.ring_causal_flash_attn(a, b, c, layout="zigzag", use_links=links and ring_links) if ring else
+             P.sequence_parallel_flash_swa(a, b, c, window, slice_lengths=lengths))
         return (y, *torch.autograd.grad(y, (a, b, c), d))
 
     def barrier():
@@ -1002,7 +1010,8 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps):
         # less work than the others (its first rows see fewer keys), so it waits for them.
         "launch": launch,
         "transport": ("NCCL send/recv on high-priority streams, " +
-                      ("one two-rank communicator per pair of neighbours" if links else "the job's communicator")),
+                      ("one two-rank communicator per pair of neighbours" if links and (ring_links or not ring)
+                       else "the job's communicator")),
         "eager_ms_per_step": eager_ms, "eager_host_enqueue_ms_per_step": host_ms,
         "kernel_ms_per_step": kernel_ms, "kernel_ms_per_step_slowest_rank": slowest_kernel_ms,
         "non_kernel_ms_per_step": ms - slowest_kernel_ms,

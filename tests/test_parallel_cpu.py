@@ -88,8 +88,8 @@ def _worker(rank, world, port, mode, results):
             mode = mode[:-len("+links")]
             P.open_neighbor_links()
             assert len(P._LINKS[None]) == (world if world > 2 else 0)
-        uneven = mode == "swa-uneven"
-        if uneven:
+        uneven, twohop = mode == "swa-uneven", mode == "swa-twohop"
+        if uneven or twohop:
             mode = "swa"
         torch.manual_seed(0)
         B, L, Hq, Hkv, D = 2, 48, 4, 2, 8
@@ -105,16 +105,25 @@ def _worker(rank, world, port, mode, results):
             # has to have the same size on both sides of an exchange
             cuts = [0, 21, 34, L][:world] + [L]
             sl = slice(cuts[rank], cuts[rank + 1])
+        lengths = None
+        if twohop:
+            # slices shorter than the window (13): ranks 2 and 3 take 10 rows from the previous rank and 3 from
+            # the one before it, and the gradients go back the same two ways
+            lengths = [18, 10, 10, 10]
+            sl = slice(sum(lengths[:rank]), sum(lengths[:rank + 1]))
         ql, kl, vl = (t[:, sl].clone().requires_grad_() for t in (q, k, v))
         if mode == "swa":
-            y = P.sequence_parallel_flash_swa(ql, kl, vl, 7, segment_idx=ids[:, sl], op=_oracle_op("window"))
-            full = dict(visibility="window", span=7)
+            span = 13 if twohop else 7
+            y = P.sequence_parallel_flash_swa(ql, kl, vl, span, segment_idx=ids[:, sl], op=_oracle_op("window"),
+                                              slice_lengths=lengths)
+            full = dict(visibility="window", span=span)
         elif mode == "sca":
             y = P.sequence_parallel_flash_sca(ql, kl, vl, 8, segment_idx=ids[:, sl], op=_oracle_op("chunk"))
             full = dict(visibility="chunk", span=8)
         else:
             y = P.ring_causal_flash_attn(ql, kl, vl, kernels=_OracleBlocks,
-                                         layout="zigzag" if mode == "zigzag" else "contiguous")
+                                         layout="zigzag" if mode == "zigzag" else "contiguous",
+                                         use_links=P.neighbor_links_open())
             full = dict(visibility="full")
         grads = torch.autograd.grad(y, (ql, kl, vl), dy[:, sl])
         ref_leaves = [t.clone().requires_grad_() for t in (q, k, v)]
@@ -135,7 +144,7 @@ def test_sequence_sharding_matches_unsharded_oracle(mode, world):
     _run_ranks(mode, world)
 
 
-@pytest.mark.parametrize("mode,world", (("swa-uneven", 3),))
+@pytest.mark.parametrize("mode,world", (("swa-uneven", 3), ("swa-twohop", 4)))
 def test_window_sharding_with_slices_of_different_lengths(mode, world):
     _run_ranks(mode, world)
 

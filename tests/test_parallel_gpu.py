@@ -32,8 +32,8 @@ def _worker(rank, world, port, mode, results):
     try:
         import xattn_b200 as xattn
         from xattn_b200 import parallel as P
-        if world > 2 and mode in ("swa", "zigzag"):
-            P.open_neighbor_links()      # these two over a communicator per pair of neighbours, the others without
+        if world > 2 and mode == "swa":
+            P.open_neighbor_links()      # this one over a communicator per pair of neighbours, the others without
         g = torch.Generator().manual_seed(0)
         B, L, Hq, Hkv, D = 1, 2048 * world, 8, 2, 128
         mk = lambda *s: torch.randn(s, generator=g).to(device=dev, dtype=torch.bfloat16)

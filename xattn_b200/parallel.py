@@ -26,7 +26,7 @@ ops), which lets the CPU test-suite drive the communication logic with the oracl
 """
 from __future__ import annotations
 
-from typing import Callable, Optional, Tuple
+from typing import Callable, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -71,9 +71,18 @@ def open_neighbor_links(group=None, high_priority: bool = True) -> None:
         if high_priority and dist.get_backend(group) == "nccl":
             options = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
         # one fixed order for all ranks (new_group is collective and blocks)
+        me = dist.get_rank()
         for a in range(world):
             b = (a + 1) % world
-            links[frozenset((a, b))] = dist.new_group(sorted((ranks[a], ranks[b])), pg_options=options)
+            link = dist.new_group(sorted((ranks[a], ranks[b])), pg_options=options)
+            links[frozenset((a, b))] = link
+            # A communicator is set up at its first use, by both of its ranks together.  Left to the first
+            # exchange, a ring would deadlock there: every rank would set up the link to its successor first
+            # and wait for a successor that is busy with its own.  So each link is used once here, in the one
+            # order all ranks share.
+            if me in (ranks[a], ranks[b]):
+                probe = torch.zeros(1, device="cuda" if dist.get_backend(link) == "nccl" else "cpu")
+                dist.all_reduce(probe, group=link)
     _LINKS[_links_key(group)] = links
 
 
@@ -86,15 +95,15 @@ def close_neighbor_links(group=None) -> None:
     _LINKS.pop(_links_key(group), None)
 
 
-def _p2p(sends, send_to: Optional[int], recvs, recv_from: Optional[int], group):
+def _p2p(sends, send_to: Optional[int], recvs, recv_from: Optional[int], group, use_links: bool = True):
     """One batched point-to-point step: every tensor of ``sends`` goes to ``send_to``, every buffer of
     ``recvs`` is filled from ``recv_from`` (either side may be absent at the ends of the chain).  Returns
     the pending work handles; the caller waits when it needs the data, so whatever it launches in
     between runs beside the transfer.  Peers issue their sends and receives in the same order.  With
     neighbour links open (``open_neighbor_links``) the sends and the receives go out as one batch each on
-    the communicator of their pair."""
+    the communicator of their pair (``use_links=False`` keeps a step on ``group``'s own)."""
     rank = dist.get_rank(group)
-    links = _LINKS.get(_links_key(group)) or {}
+    links = (_LINKS.get(_links_key(group)) or {}) if use_links else {}
     out_link = links.get(frozenset((rank, send_to))) if send_to is not None else None
     in_link = links.get(frozenset((rank, recv_from))) if recv_from is not None else None
     send_ops, recv_ops = [], []
@@ -119,74 +128,136 @@ def _wait(works) -> None:
         work.wait()
 
 
-def _assemble_halo(ctx, k: Tensor, v: Tensor, halo: int, ids: Optional[Tensor], group):
-    """[previous rank's last ``halo`` tokens ‖ own tokens] for K, V and the segment ids; what the backward
-    needs to know about the exchange is left on ``ctx``."""
+def _halo_routes(rank: int, world: int, halo: int, lengths: Optional[Sequence[int]]):
+    """Where this rank's halo comes from and which ranks it feeds.  Returns two dictionaries
+    ``hop -> rows``: rows received from rank ``rank - hop`` and rows sent to rank ``rank + hop``.
+    Without ``lengths`` (every slice holds at least ``halo`` tokens) that is the previous rank and the
+    next one.  With the slice lengths of all ranks a slice may be shorter than the halo, which then
+    reaches back over as many ranks as it takes (nearest first)."""
+    def sources_of(r: int):
+        out, need = {}, halo
+        for s in range(r - 1, -1, -1):
+            take = need if lengths is None else min(need, int(lengths[s]))
+            if take > 0:
+                out[r - s] = take
+            need -= take
+            if need <= 0 or lengths is None:
+                break
+        return out
+    sources = sources_of(rank)
+    feeds = {}
+    for d in range(rank + 1, world):
+        rows = sources_of(d).get(d - rank)
+        if rows:
+            feeds[d - rank] = rows
+        if lengths is None:
+            break
+    return sources, feeds
+
+
+def _assemble_halo(ctx, k: Tensor, v: Tensor, halo: int, ids: Optional[Tensor], group, lengths=None):
+    """[the ``halo`` tokens before this rank's slice ‖ own tokens] for K, V and the segment ids; what the
+    backward needs to know about the exchange is left on ``ctx``."""
     rank, world = _world(group)
-    nxt = rank + 1 if rank + 1 < world else None
-    prv = rank - 1 if rank > 0 else None
-    n_prev = halo if prv is not None else 0
-    ctx.group, ctx.halo, ctx.n_prev, ctx.nxt, ctx.prv = group, halo, n_prev, nxt, prv
+    sources, feeds = _halo_routes(rank, world, halo, lengths)
+    n_prev = sum(sources.values())
+    # rows of the farthest source first: offset of every source's rows in the assembled buffer
+    offsets, off = {}, 0
+    for hop in sorted(sources, reverse=True):
+        offsets[hop] = off
+        off += sources[hop]
+    ctx.group, ctx.n_prev, ctx.sources, ctx.feeds, ctx.offsets = group, n_prev, sources, feeds, offsets
     tensors = [k, v] + ([ids] if ids is not None else [])
     out = [t.new_empty((t.shape[0], n_prev + t.shape[1], *t.shape[2:])) for t in tensors]
     # a slice along the token axis is one block of memory only for a batch of one: otherwise the
-    # halo lands in a buffer of its own first
+    # halo lands in buffers of its own first
     direct = k.shape[0] == 1
-    landing = [o[:, :n_prev] if direct else o.new_empty((o.shape[0], n_prev, *o.shape[2:])) for o in out]
-    works = _p2p([t[:, -halo:] for t in tensors], nxt, landing, prv, group)
+    landing, works = {}, []
+    for hop in sorted(set(sources) | set(feeds)):           # the same order on every rank
+        rows_in, rows_out = sources.get(hop), feeds.get(hop)
+        if rows_in:
+            lo = offsets[hop]
+            landing[hop] = [o[:, lo:lo + rows_in] if direct else o.new_empty((o.shape[0], rows_in, *o.shape[2:]))
+                            for o in out]
+        works += _p2p([t[:, -rows_out:] for t in tensors] if rows_out else [], rank + hop if rows_out else None,
+                      landing.get(hop, []), rank - hop if rows_in else None, group)
     for o, t in zip(out, tensors):
         o[:, n_prev:].copy_(t)
     _wait(works)
-    if not direct and n_prev:
-        for o, l in zip(out, landing):
-            o[:, :n_prev].copy_(l)
+    if not direct:
+        for hop, bufs in landing.items():
+            lo = offsets[hop]
+            for o, l in zip(out, bufs):
+                o[:, lo:lo + sources[hop]].copy_(l)
     return out[0], out[1], (out[2] if ids is not None else None)
 
 
-class _HaloAssemble(torch.autograd.Function):
-    """(k, v) of this rank -> (k_all, v_all, ids_all): the last ``halo`` tokens of the previous rank's K / V
-    (and segment ids) in front of this rank's own, in one buffer each.  The attention op then sees a
-    query slice that is shorter than its keys and right-aligned to them, which is the reference's own
-    short-Q contract (tests/_reference.py:47-49): no previous-K/V arguments, no concatenation inside
-    the op.  One batched exchange carries K, V and ids; this rank's own K / V are copied into place while
-    it is in flight.
+def _return_halo_gradients(ctx, grads):
+    """Start the halo rows' gradients on their way back to the ranks that own those tokens and post the
+    receives for the gradients of the rows this rank fed to others.  Returns (works, own, received):
+    ``own`` are the views of this rank's own rows, ``received`` maps hop -> buffers to add to their tails."""
+    rank = dist.get_rank(ctx.group)
+    works, received = [], {}
+    for hop in sorted(set(ctx.sources) | set(ctx.feeds)):
+        rows_in, rows_out = ctx.sources.get(hop), ctx.feeds.get(hop)
+        sends = []
+        if rows_in:
+            lo = ctx.offsets[hop]
+            sends = [g[:, lo:lo + rows_in] for g in grads]
+        if rows_out:
+            received[hop] = [g.new_empty((g.shape[0], rows_out, *g.shape[2:])) for g in grads]
+        works += _p2p(sends, rank - hop if rows_in else None, received.get(hop, []), rank + hop if rows_out else None,
+                      ctx.group)
+    return works, [g[:, ctx.n_prev:] for g in grads], received
 
-    Backward: the gradient of the halo rows travels back to the previous rank and is added to the tail
-    of its dK / dV (the reference's ``dprev_k / dprev_v`` seam, docs/sliding_window_attention.md:78-79).
+
+def _add_returned_gradients(own, received) -> None:
+    for bufs in received.values():
+        for g, r in zip(own, bufs):
+            g[:, -r.shape[1]:] += r          # the gradients are the calling function's alone: updated in place
+
+
+class _HaloAssemble(torch.autograd.Function):
+    """(k, v) of this rank -> (k_all, v_all, ids_all): the ``halo`` tokens before this rank's slice (K / V and
+    segment ids of the previous rank, or ranks) in front of this rank's own, in one buffer each.  The
+    attention op then sees a query slice that is shorter than its keys and right-aligned to them, which is
+    the reference's own short-Q contract (tests/_reference.py:47-49): no previous-K/V arguments, no
+    concatenation inside the op.  One batched exchange per neighbour carries K, V and ids; this rank's own
+    K / V are copied into place while it is in flight.
+
+    Backward: the gradient of the halo rows travels back to the ranks that own them and is added to the
+    tail of their dK / dV (the reference's ``dprev_k / dprev_v`` seam, docs/sliding_window_attention.md:78-79).
     K and V pass through this node on every rank, so every rank takes part in that exchange whether
     or not it received a halo itself."""
 
     @staticmethod
-    def forward(ctx, k: Tensor, v: Tensor, halo: int, ids: Optional[Tensor], group):
-        k_all, v_all, ids_all = _assemble_halo(ctx, k, v, halo, ids, group)
+    def forward(ctx, k: Tensor, v: Tensor, halo: int, ids: Optional[Tensor], group, lengths):
+        k_all, v_all, ids_all = _assemble_halo(ctx, k, v, halo, ids, group, lengths)
         if ids_all is not None:
             ctx.mark_non_differentiable(ids_all)
         return k_all, v_all, ids_all
 
     @staticmethod
     def backward(ctx, dk_all: Tensor, dv_all: Tensor, _ids):
-        halo, n_prev, nxt, prv, group = ctx.halo, ctx.n_prev, ctx.nxt, ctx.prv, ctx.group
-        grads = [dk_all, dv_all]
-        recv = [g.new_empty((g.shape[0], halo, *g.shape[2:])) for g in grads] if nxt is not None else []
-        works = _p2p([g[:, :n_prev] for g in grads], prv, recv, nxt, group)
-        own = [g[:, n_prev:] for g in grads]
+        works, own, received = _return_halo_gradients(ctx, [dk_all, dv_all])
         _wait(works)
-        for g, r in zip(own, recv):
-            g[:, -halo:] += r            # the gradients are this function's alone: updated in place
-        return own[0], own[1], None, None, None
+        _add_returned_gradients(own, received)
+        return own[0], own[1], None, None, None, None
 
 
 class _ShardedLocalAttention(torch.autograd.Function):
     """The halo exchange and this package's kernels as one autograd node, so that the backward can order
     its kernels around the exchange: dK / dV first, the halo rows' gradients start their way back to the
-    previous rank, the dQ kernel runs meanwhile, and only then does this rank wait for the gradients coming
-    from the next rank.  (With the exchange in a node of its own, ``_HaloAssemble``, it can only start after
-    the whole attention backward.)  Level 0, the library's own ops; everything else takes the generic path."""
+    ranks that own them, the dQ kernel runs meanwhile, and only then does this rank wait for the gradients
+    coming from the ranks it fed.  (With the exchange in a node of its own, ``_HaloAssemble``, it can only
+    start after the whole attention backward.)  Level 0, the library's own ops; everything else takes the
+    generic path."""
 
     @staticmethod
-    def forward(ctx, q: Tensor, k: Tensor, v: Tensor, kind: str, span: int, scale: float, ids: Optional[Tensor], group):
+    def forward(ctx, q: Tensor, k: Tensor, v: Tensor, kind: str, span: int, scale: float, ids: Optional[Tensor], group,
+                lengths):
         from .ops import _core
-        k_all, v_all, ids_all = _assemble_halo(ctx, k, v, span, ids, group)     # leaves halo, n_prev, nxt, prv on ctx
+        k_all, v_all, ids_all = _assemble_halo(ctx, k, v, span, ids, group, lengths)   # leaves the routes on ctx
         q_ids = None if ids_all is None else ids_all[:, ids_all.shape[1] - q.shape[1]:]
         support = _core.Support(kind, span)
         y, lse, _, plan = _core.forward(q, k_all, v_all, support, scale, None, None, q_ids, ids_all, return_plan=True)
@@ -198,47 +269,52 @@ class _ShardedLocalAttention(torch.autograd.Function):
     def backward(ctx, dy: Tensor):
         from . import _lib, _native
         q, k_all, v_all, y, lse, plan = ctx.saved_tensors
-        halo, n_prev, nxt, prv, group = ctx.halo, ctx.n_prev, ctx.nxt, ctx.prv, ctx.group
         call = _native.BackwardCall(dy, q, k_all, v_all, y, lse, plan, ctx.scale)
         call.run(_lib.BWD_PHASE_PRE | _lib.BWD_PHASE_DKV)
-        grads = [call.dk, call.dv]
-        recv = [g.new_empty((g.shape[0], halo, *g.shape[2:])) for g in grads] if nxt is not None else []
-        works = _p2p([g[:, :n_prev] for g in grads], prv, recv, nxt, group)
+        works, own, received = _return_halo_gradients(ctx, [call.dk, call.dv])
         call.run(_lib.BWD_PHASE_DQ)                     # beside the exchange
-        own = [g[:, n_prev:] for g in grads]
         _wait(works)
-        for g, r in zip(own, recv):
-            g[:, -halo:] += r
-        return call.dq, own[0], own[1], None, None, None, None, None
+        _add_returned_gradients(own, received)
+        return call.dq, own[0], own[1], None, None, None, None, None, None
 
 
-def _sequence_parallel_local(op, q, k, v, span, scale, segment_idx, group, op_kwargs, kind):
+def _sequence_parallel_local(op, q, k, v, span, scale, segment_idx, group, op_kwargs, kind, lengths=None):
+    if lengths is not None:
+        rank, world = _world(group)
+        lengths = tuple(int(n) for n in lengths)
+        if len(lengths) != world or min(lengths) <= 0 or lengths[rank] != k.shape[1]:
+            raise ValueError("slice_lengths must give the positive slice length of every rank, this rank's included")
     if op is None and not op_kwargs and q.is_cuda:
         s = float(scale) if scale is not None else q.shape[-1] ** -0.5
-        return _ShardedLocalAttention.apply(q, k, v, kind, span, s, segment_idx, group)
+        return _ShardedLocalAttention.apply(q, k, v, kind, span, s, segment_idx, group, lengths)
     if op is None:
         from . import ops
         op = ops.flash_swa if kind == "window" else ops.flash_sca
-    k_all, v_all, ids_all = _HaloAssemble.apply(k, v, span, segment_idx, group)
+    k_all, v_all, ids_all = _HaloAssemble.apply(k, v, span, segment_idx, group, lengths)
     return op(q, k_all, v_all, span, scale, segment_idx=ids_all, **op_kwargs)
 
 
 def sequence_parallel_flash_swa(q: Tensor, k: Tensor, v: Tensor, window_size: int, scale: Optional[float] = None,
                                 *, segment_idx: Optional[Tensor] = None, group=None,
-                                op: Optional[Callable] = None, **op_kwargs) -> Tensor:
+                                op: Optional[Callable] = None, slice_lengths: Optional[Sequence[int]] = None,
+                                **op_kwargs) -> Tensor:
     """Sliding-window attention over a sequence split contiguously across the ranks of ``group``.
 
-    ``q``, ``k``, ``v`` (and ``segment_idx`` ``[B, L_local]``, global ids) are this rank's slice; every
-    rank's slice must hold at least ``window_size`` tokens so that the halo comes from one neighbour.
-    Differentiable: dK / dV of the halo return to the rank that owns those tokens.
+    ``q``, ``k``, ``v`` (and ``segment_idx`` ``[B, L_local]``, global ids) are this rank's slice.  The slices
+    need not be equally long (the first ``window_size`` rows of a sequence see fewer keys, so equal work
+    means a longer first slice).  Without ``slice_lengths`` every rank's slice must hold at least
+    ``window_size`` tokens, so that the halo comes from one neighbour; with the slice lengths of all ranks
+    (the same list on every rank) a slice may be shorter and the halo is collected from as many preceding
+    ranks as it takes.  Differentiable: dK / dV of the halo return to the ranks that own those tokens.
     """
     if window_size <= 0:
         if op is None:
             from .ops import flash_swa as op
         return op(q, k, v, window_size, scale, segment_idx=segment_idx, **op_kwargs)
-    if k.shape[1] < window_size:
-        raise ValueError("every rank's slice must be at least window_size tokens long")
-    return _sequence_parallel_local(op, q, k, v, window_size, scale, segment_idx, group, op_kwargs, "window")
+    if slice_lengths is None and k.shape[1] < window_size:
+        raise ValueError("every rank's slice must be at least window_size tokens long (or pass slice_lengths)")
+    return _sequence_parallel_local(op, q, k, v, window_size, scale, segment_idx, group, op_kwargs, "window",
+                                    slice_lengths)
 
 
 def sequence_parallel_flash_sca(q: Tensor, k: Tensor, v: Tensor, chunk_size: int, scale: Optional[float] = None,
@@ -321,7 +397,8 @@ def _merge_rows(acc: Tuple[Tensor, Tensor], y: Tensor, lse: Tensor, start: int) 
 
 class _RingCausal(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q: Tensor, k: Tensor, v: Tensor, scale: float, group, kernels, zigzag: bool = False):
+    def forward(ctx, q: Tensor, k: Tensor, v: Tensor, scale: float, group, kernels, zigzag: bool = False,
+                use_links: bool = False):
         rank, world = _world(group)
         half = q.shape[1] // 2
         send_to, recv_from = (rank + 1) % world, (rank - 1) % world
@@ -343,7 +420,7 @@ class _RingCausal(torch.autograd.Function):
             if t + 1 < world:
                 # prefetch the next block while this one is computed
                 nxt_k, nxt_v = torch.empty_like(blk_k), torch.empty_like(blk_v)
-                pending = _p2p([blk_k, blk_v], send_to, [nxt_k, nxt_v], recv_from, group)
+                pending = _p2p([blk_k, blk_v], send_to, [nxt_k, nxt_v], recv_from, group, use_links)
             if zigzag and t > 0:
                 if t <= rank:   # an earlier rank's block: its first chunk lies before both local chunks
                     y_t, lse_t = kernels.forward(q, blk_k[:, :half], blk_v[:, :half], scale, causal=False)
@@ -360,7 +437,7 @@ class _RingCausal(torch.autograd.Function):
         y32, lse = acc
         y = y32.to(q.dtype)
         ctx.save_for_backward(q, k, v, y, lse)
-        ctx.scale, ctx.group, ctx.kernels, ctx.zigzag = scale, group, kernels, zigzag
+        ctx.scale, ctx.group, ctx.kernels, ctx.zigzag, ctx.use_links = scale, group, kernels, zigzag, use_links
         return y
 
     @staticmethod
@@ -386,7 +463,7 @@ class _RingCausal(torch.autograd.Function):
             kv_works = []
             if t + 1 < world:
                 nxt_k, nxt_v = torch.empty_like(blk_k), torch.empty_like(blk_v)
-                kv_works = _p2p([blk_k, blk_v], send_to, [nxt_k, nxt_v], recv_from, group)
+                kv_works = _p2p([blk_k, blk_v], send_to, [nxt_k, nxt_v], recv_from, group, ctx.use_links)
             dk_t = dv_t = None
             rows = slice(None)
             if zigzag and t > 0:
@@ -414,7 +491,7 @@ class _RingCausal(torch.autograd.Function):
                 dv_acc[:, rows] += dv_t
             # pass the accumulator on (the last step brings it home) and ask for the next one
             recv_dk, recv_dv = torch.empty_like(dk_acc), torch.empty_like(dv_acc)
-            works = _p2p([dk_acc, dv_acc], send_to, [recv_dk, recv_dv], recv_from, group)
+            works = _p2p([dk_acc, dv_acc], send_to, [recv_dk, recv_dv], recv_from, group, ctx.use_links)
             sent.append((dk_acc, dv_acc))
             acc_in = (works, recv_dk, recv_dv)
             _wait(kv_works)
@@ -422,17 +499,23 @@ class _RingCausal(torch.autograd.Function):
                 blk_k, blk_v = nxt_k, nxt_v
         _wait(acc_in[0])
         dk_home, dv_home = acc_in[1], acc_in[2]
-        return dq.to(q.dtype), dk_home.to(k.dtype), dv_home.to(v.dtype), None, None, None, None
+        return dq.to(q.dtype), dk_home.to(k.dtype), dv_home.to(v.dtype), None, None, None, None, None
 
 
 def ring_causal_flash_attn(q: Tensor, k: Tensor, v: Tensor, scale: Optional[float] = None, *, group=None,
-                           kernels=None, layout: str = "contiguous") -> Tensor:
+                           kernels=None, layout: str = "contiguous", use_links: bool = False) -> Tensor:
     """Causal attention over a sequence split across ranks (equal slice lengths, no segment metadata):
     ring of K/V blocks, partial outputs merged by log-sum-exp, differentiable.
 
     ``layout="contiguous"``: rank r holds positions [r * n, (r + 1) * n).  ``layout="zigzag"``: rank r holds
     the positions ``zigzag_indices(length, r, world)`` (an even slice length), which balances the causal
-    work: every rank computes half a block at every step."""
+    work: every rank computes half a block at every step.
+
+    ``use_links``: send the blocks over the neighbour links (``open_neighbor_links``) instead of ``group``'s own
+    communicator.  Off by default: NCCL connects two ranks for point-to-point traffic at their first
+    transfer, with both of them present, and in a ring every rank would be waiting for its successor at that
+    moment.  Turn it on once the links have carried a chain exchange (a sharded window or chunk call), which
+    connects the pairs one after the other; the wrap-around pair then connects at the ring's first step."""
     if q.shape[1] != k.shape[1]:
         raise ValueError("ring attention needs equal query and key slice lengths")
     if layout not in ("contiguous", "zigzag"):
@@ -440,4 +523,4 @@ def ring_causal_flash_attn(q: Tensor, k: Tensor, v: Tensor, scale: Optional[floa
     if layout == "zigzag" and q.shape[1] % 2:
         raise ValueError("the zig-zag layout needs an even slice length")
     s = float(scale) if scale is not None else q.shape[-1] ** -0.5
-    return _RingCausal.apply(q, k, v, s, group, kernels or NativeBlockKernels, layout == "zigzag")
+    return _RingCausal.apply(q, k, v, s, group, kernels or NativeBlockKernels, layout == "zigzag", bool(use_links))
