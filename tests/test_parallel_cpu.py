@@ -179,6 +179,29 @@ def _run_ranks(mode, world):
         assert max(results.values()) < 1e-10, dict(results)
 
 
+def test_halo_routes():
+    """Which ranks a halo comes from and goes to: the neighbours without slice lengths, as many preceding
+    ranks as the halo needs with them (nearest first), nothing before rank 0."""
+    from xattn_b200.parallel import _halo_routes
+    assert _halo_routes(0, 4, 7, None) == ({}, {1: 7})
+    assert _halo_routes(2, 4, 7, None) == ({1: 7}, {1: 7})
+    assert _halo_routes(3, 4, 7, None) == ({1: 7}, {})
+    lengths = [5888] + [3840] * 7
+    assert _halo_routes(0, 8, 4096, lengths) == ({}, {1: 4096, 2: 256})
+    assert _halo_routes(1, 8, 4096, lengths) == ({1: 4096}, {1: 3840, 2: 256})
+    assert _halo_routes(4, 8, 4096, lengths) == ({1: 3840, 2: 256}, {1: 3840, 2: 256})
+    assert _halo_routes(7, 8, 4096, lengths) == ({1: 3840, 2: 256}, {})
+    # every row a rank receives is a row another rank sends
+    for lengths, halo in (([18, 10, 10, 10], 13), ([3, 3, 3, 3, 30], 8), ([40, 2, 2], 5)):
+        world = len(lengths)
+        routes = [_halo_routes(r, world, halo, lengths) for r in range(world)]
+        for r, (sources, _) in enumerate(routes):
+            assert sum(sources.values()) == min(halo, sum(lengths[:r]))
+            for hop, rows in sources.items():
+                assert routes[r - hop][1][hop] == rows
+        assert sum(sum(f.values()) for _, f in routes) == sum(sum(s_.values()) for s_, _ in routes)
+
+
 def test_halo_requires_long_enough_slices():
     from xattn_b200 import parallel as P
     q = torch.zeros(1, 4, 1, 8)
