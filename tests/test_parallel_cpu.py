@@ -179,6 +179,94 @@ def _run_ranks(mode, world):
         assert max(results.values()) < 1e-10, dict(results)
 
 
+# ---- the native autograd node, on CPU ------------------------------------------------------------------
+# ``_ShardedLocalAttention`` (halo exchange + this package's kernels as one node, dK / dV before dQ) only runs
+# on GPUs.  Its exchange logic is driven here with the two calls it makes into the CUDA layer replaced by
+# the oracle: what is checked is which rows travel where and where the returned gradients are added.
+
+def _native_node_worker(rank, world, port, lengths, span, results):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import attention_oracle as O
+        from xattn_b200 import _native, parallel as P
+        from xattn_b200.ops import _core
+        calls = {}
+
+        def fake_forward(q, k_all, v_all, support, scale, prev_k, prev_v, q_ids, k_ids, *, return_plan=False, **kw):
+            y = O.attention(q, k_all, v_all, visibility=support.kind, span=support.span, scale=scale,
+                            q_segment_idx=q_ids, k_segment_idx=k_ids)
+            plan = torch.zeros(1, dtype=torch.int32)
+            calls[id(plan)] = (support, q_ids, k_ids)
+            return y, torch.zeros(1), None, plan
+
+        class FakeBackwardCall:
+            def __init__(self, dy, q, k_all, v_all, y, lse, plan, scale):
+                support, q_ids, k_ids = calls[id(plan)]
+                with torch.enable_grad():          # an autograd backward runs with gradients off
+                    leaves = [t.detach().clone().requires_grad_() for t in (q, k_all, v_all)]
+                    out = O.attention(*leaves, visibility=support.kind, span=support.span, scale=scale,
+                                      q_segment_idx=q_ids, k_segment_idx=k_ids)
+                    self._grads = torch.autograd.grad(out, leaves, dy)
+                self.dq = self.dk = self.dv = None
+                self.phases = []
+
+            def run(self, phases=0):
+                self.phases.append(phases)
+                if phases & 4:
+                    self.dk, self.dv = self._grads[1].clone(), self._grads[2].clone()
+                if phases & 2:
+                    self.dq = self._grads[0].clone()
+
+        _core.forward, _native.BackwardCall = fake_forward, FakeBackwardCall
+        torch.manual_seed(0)
+        B, L, Hq, Hkv, D = 1, sum(lengths), 4, 2, 8
+        q = torch.randn(B, L, Hq, D, dtype=torch.float64)
+        k = torch.randn(B, L, Hkv, D, dtype=torch.float64)
+        v = torch.randn(B, L, Hkv, D, dtype=torch.float64)
+        dy = torch.randn(B, L, Hq, D, dtype=torch.float64)
+        ids = (torch.arange(L) // 19).expand(B, -1).contiguous()
+        sl = slice(sum(lengths[:rank]), sum(lengths[:rank + 1]))
+        ql, kl, vl = (t[:, sl].clone().requires_grad_() for t in (q, k, v))
+        y = P._ShardedLocalAttention.apply(ql, kl, vl, "window", span, D ** -0.5, ids[:, sl], None, tuple(lengths))
+        grads = torch.autograd.grad(y, (ql, kl, vl), dy[:, sl])
+        ref_leaves = [t.clone().requires_grad_() for t in (q, k, v)]
+        y_ref = O.attention(*ref_leaves, q_segment_idx=ids, k_segment_idx=ids, visibility="window", span=span)
+        g_ref = torch.autograd.grad(y_ref, ref_leaves, dy)
+        errs = [(y - y_ref[:, sl]).abs().max().item()]
+        errs += [(g - r[:, sl]).abs().max().item() for g, r in zip(grads, g_ref)]
+        results[rank] = max(errs)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("lengths,span", (((24, 24), 7), ((21, 13, 14), 7), ((18, 10, 10, 10), 13)),
+                         ids=("two-ranks", "uneven", "two-hop"))
+def test_native_sharded_node_exchanges(lengths, span):
+    world = len(lengths)
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as manager:
+        for attempt in range(2):
+            results = manager.dict()
+            port = _free_port()
+            procs = [ctx.Process(target=_native_node_worker, args=(r, world, port, lengths, span, results))
+                     for r in range(world)]
+            for p in procs:
+                p.start()
+            for p in procs:
+                p.join(timeout=300)
+            for p in procs:
+                if p.is_alive():
+                    p.kill()
+            if all(p.exitcode == 0 for p in procs) or attempt == 1:
+                break
+        for p in procs:
+            assert p.exitcode == 0, f"rank exited with {p.exitcode}"
+        assert len(results) == world
+        assert max(results.values()) < 1e-10, dict(results)
+
+
 def test_halo_routes():
     """Which ranks a halo comes from and goes to: the neighbours without slice lengths, as many preceding
     ranks as the halo needs with them (nearest first), nothing before rank 0."""
