@@ -806,6 +806,26 @@ def run_other(args, w, world, rank, dev):
         dist.destroy_process_group()
 
 
+def window_slice_bounds(S, world, window, equal=False, shortest=None):
+    """Row boundaries of the ranks' contiguous slices of a causal sliding-window workload: about equal
+    numbers of visible pairs per slice (the first ``window`` rows of the sequence see fewer keys, so with
+    equal slices rank 0 has less to do than everybody else), boundaries on multiples of 128 rows, every
+    slice at least ``shortest`` rows long (default: one window, so that the halo comes from the previous
+    rank alone; half a window makes the halo reach two ranks back).  Where that cannot be had (eight ranks
+    over 32768 rows with a window of 4096: an equal slice IS one window), or with ``equal``, equal slices."""
+    import bisect
+    even = [r * (S // world) for r in range(world + 1)]
+    if equal or world == 1:
+        return even
+    cum, acc = [], 0
+    for i in range(S):
+        acc += min(i, window) + 1
+        cum.append(acc)
+    cand = [0] + [min(S, (bisect.bisect_left(cum, acc * r / world) + 1 + 64) // 128 * 128) for r in range(1, world)] + [S]
+    least = max(window if shortest is None else shortest, 128)
+    return cand if all(b - a >= least for a, b in zip(cand, cand[1:])) else even
+
+
 def measure_sharded(args, w, world, rank, dev, with_e2e, steps, ring_links=False):
     """One sequence of S tokens split over the ranks of the current process group, total work fixed:
     configs[2] (sliding window, contiguous slices, K/V halo exchange) or the causal ring (zig-zag
@@ -824,25 +844,9 @@ def measure_sharded(args, w, world, rank, dev, with_e2e, steps, ring_links=False
     S, D, window = w["S"], w["D"], w.get("window", 0)
     if S % (2 * world) or S // world < window:
         raise SystemExit("sequence length must split into even slices of at least one window")
-    n = S // world
-    # Window workload: contiguous slices with about equal numbers of visible pairs (the first `window` rows
-    # of the sequence see fewer keys, so with equal slices rank 0 has less to do than everybody else),
-    # boundaries on multiples of 128 rows, every slice at least one window long (the halo comes from the
-    # previous rank alone).  Where that cannot be had (eight ranks: an equal slice IS one window) the slices
-    # stay equal.
-    bounds = [r * n for r in range(world + 1)]
-    if not ring and world > 1:
-        cum, acc = [], 0
-        for i in range(S):
-            acc += min(i, window) + 1
-            cum.append(acc)
-        import bisect
-        cand = [0] + [min(S, (bisect.bisect_left(cum, acc * r / world) + 1 + 64) // 128 * 128) for r in range(1, world)] + [S]
-        # XATTN_BENCH_EQUAL_SLICES=1 keeps the slices equal; XATTN_BENCH_SHORT_SLICES=1 also accepts slices down to
-        # half a window, whose halo then reaches two ranks back (slice_lengths below)
-        shortest = window // 2 if os.environ.get("XATTN_BENCH_SHORT_SLICES") else window
-        if all(b - a >= max(shortest, 128) for a, b in zip(cand, cand[1:])) and not os.environ.get("XATTN_BENCH_EQUAL_SLICES"):
-            bounds = cand
+    bounds = ([r * (S // world) for r in range(world + 1)] if ring else
+              window_slice_bounds(S, world, window, equal=bool(os.environ.get("XATTN_BENCH_EQUAL_SLICES")),
+                                  shortest=window // 2 if os.environ.get("XATTN_BENCH_SHORT_SLICES") else window))
     lengths = [b - a for a, b in zip(bounds, bounds[1:])]
     g = torch.Generator().manual_seed(2)
     draw = lambda *shape: torch.randn(shape, generator=g, dtype=torch.float32).to(torch.bfloat16)

@@ -131,3 +131,25 @@ def test_value_group_entry_checks_layout():
         _softdelta_value_groups(q, k, torch.zeros(1, 4, 1, 16), torch.zeros(1, 4, 2))
     with pytest.raises(ValueError, match=r"\[B, Lq, H, C, 1\]"):
         _softdelta_value_groups(q, k, torch.zeros(1, 4, 1, 2, 8), torch.zeros(1, 4, 2, 3, 1))
+
+
+def test_bench_window_slices_balance_the_work():
+    """bench.py cuts the sharded window workload into slices of equal work where every slice can hold a window."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location("bench", os.path.join(os.path.dirname(os.path.dirname(__file__)), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    S, window = 32768, 4096
+    assert bench.window_slice_bounds(S, 1, window) == [0, S]
+    assert bench.window_slice_bounds(S, 2, window) == [0, 17408, S]
+    assert bench.window_slice_bounds(S, 4, window) == [0, 9728, 17408, 25088, S]
+    assert bench.window_slice_bounds(S, 8, window) == [r * 4096 for r in range(9)]          # a slice is one window
+    assert bench.window_slice_bounds(S, 4, window, equal=True) == [r * 8192 for r in range(5)]
+    short = bench.window_slice_bounds(S, 8, window, shortest=window // 2)
+    assert [b - a for a, b in zip(short, short[1:])] == [5888] + [3840] * 7
+    work = lambda a, b: sum(min(i, window) + 1 for i in range(a, b))
+    for world in (2, 4):
+        bounds = bench.window_slice_bounds(S, world, window)
+        shares = [work(a, b) for a, b in zip(bounds, bounds[1:])]
+        assert max(shares) / (sum(shares) / world) < 1.01
